@@ -1,0 +1,152 @@
+/*
+ * nanopd_b200 — C ABI of the paged-attention hot path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, 64-bit sizes/strides counted in
+ * ELEMENTS, a dtype code and a CUDA stream handle (cudaStream_t passed as void*;
+ * NULL = the legacy default stream).  Calls are asynchronous on that stream, never
+ * synchronise the device, allocate nothing, and return NPD_OK or an NPD_ERR_* code;
+ * npd_last_error() then gives a message for the calling thread.  Nothing here
+ * terminates the process (the reference's CHECK_KERNEL does:
+ * nanoPD/paged_attention/csrc/utils/cuda_utils.h:18-29).
+ *
+ * The Python module `paged_kernels` shipped with this library binds these symbols
+ * with ctypes and exposes the reference's op signatures on top of them.
+ */
+#ifndef NANOPD_B200_H
+#define NANOPD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- codes ------------------------------------------------------------------ */
+#define NPD_OK               0
+#define NPD_ERR_INVALID_ARG  1   /* shape / alignment / NULL pointer                      */
+#define NPD_ERR_UNSUPPORTED  2   /* dtype, head_dim, block_size or group outside the set  */
+#define NPD_ERR_CUDA         3   /* a CUDA runtime / driver call failed                   */
+#define NPD_ERR_WORKSPACE    4   /* workspace missing or smaller than *_workspace_bytes   */
+
+#define NPD_DTYPE_F16   0
+#define NPD_DTYPE_BF16  1
+#define NPD_DTYPE_F32   2   /* accepted by npd_kv_store only (the payload is opaque there) */
+
+/* Bits of the device-side status word (first int32 of a decode/prefill workspace, or
+ * the `status` argument of npd_kv_store / npd_kv_migrate).  Kernels OR bits in; they
+ * never fault or spin without bound.  Read and clear it with npd_read_status().      */
+#define NPD_STATUS_BAD_BLOCK_ID   1   /* a block-table entry outside [0, num_blocks); the access was skipped */
+#define NPD_STATUS_BAD_POSITION   2   /* a position / seq_len beyond the table's capacity; clamped or skipped */
+#define NPD_STATUS_WAIT_TIMEOUT   4   /* a bounded wait on an in-kernel barrier ran out                       */
+
+/* Flags of npd_paged_decode_attention */
+#define NPD_DECODE_SKIP_MERGE     1   /* diagnostic: run only the streaming kernel (split sequences stay unmerged) */
+
+int         npd_version(void);
+const char *npd_last_error(void);
+
+/* Copies the int32 status word at `status_dev` to the host, clears it on the device,
+ * and waits for `stream`.  Returns the word in *out.                                  */
+int npd_read_status(int32_t *status_dev, int32_t *out, void *stream);
+
+/* ---- (1) paged KV store ---------------------------------------------------------
+ * Replaces paged_kv_store (nanoPD/paged_attention/csrc/kvstore/paged_kv_store.h:23-27,
+ * paged_kv_store_ops.cu:7-50, paged_kv_store_kernel.cu:16-58).
+ * For token t and kv head h:
+ *   cache[block_tables[t*bt_row_stride + positions[t]/block_size], h, positions[t]%block_size, :]
+ *       = src[h, t, :]                        for K and for V.
+ * k_cache/v_cache: [num_blocks, num_kv_heads, block_size, head_dim], the last three
+ * dims contiguous, blocks `cache_block_stride` elements apart.
+ * k_src/v_src: element (h, t, d) at h*src_head_stride + t*src_token_stride + d.
+ * block_tables: int32, one row per token (bt_row_stride may be 0 for a shared row).
+ * head_dim*elem must be a multiple of 16 bytes; all base pointers 16-byte aligned.
+ * `status` (device int32, may be NULL) receives NPD_STATUS_* bits.                     */
+int npd_kv_store(void *k_cache, void *v_cache, const void *k_src, const void *v_src,
+                 const int32_t *block_tables, const int32_t *positions,
+                 int64_t num_tokens, int64_t num_kv_heads, int64_t head_dim,
+                 int64_t block_size, int64_t num_blocks, int64_t max_blocks_per_seq,
+                 int64_t cache_block_stride, int64_t src_head_stride,
+                 int64_t src_token_stride, int64_t bt_row_stride,
+                 int dtype, int32_t *status, void *stream);
+
+/* ---- (2) paged decode attention -------------------------------------------------
+ * Replaces paged_attention_forward (nanoPD/paged_attention/csrc/attention/paged_attention.h:24-34,
+ * paged_attention_ops.cu:7-59, paged_attention_kernel.cu:39-151) and the split-K pair
+ * (csrc/paged_attention_optimized/paged_attention_optimized_ops.cu:20-112).
+ *   out[s, h, :] = softmax(scale * q[s, h, :] . K_s^T) . V_s
+ * over the first seq_lens[s] tokens of the pages block_tables[s, :]; the kv head of
+ * q head h is h / (num_q_heads / num_kv_heads).  out, q: [num_seqs, num_q_heads,
+ * head_dim] contiguous.  Caches as in npd_kv_store.  fp32 accumulation throughout.
+ * Supported: dtype f16/bf16, head_dim in {64,128,256}, block_size in {8,16,32},
+ * num_q_heads/num_kv_heads <= 32.  A sequence with seq_lens[s] == 0 gets a zero row.
+ * `workspace` is caller-owned device memory of at least
+ * npd_decode_workspace_bytes(...) bytes, 256-byte aligned, ZEROED ONCE before first
+ * use and then only touched by this library; its first int32 is the status word.
+ * Two calls that may overlap on the GPU need two workspaces.                           */
+size_t npd_decode_workspace_bytes(int64_t num_seqs, int64_t num_q_heads,
+                                  int64_t num_kv_heads, int64_t head_dim, int device);
+int npd_paged_decode_attention(void *out, const void *q, const void *k_cache,
+                               const void *v_cache, const int32_t *block_tables,
+                               const int32_t *seq_lens, float scale,
+                               int64_t num_seqs, int64_t num_q_heads, int64_t num_kv_heads,
+                               int64_t head_dim, int64_t block_size,
+                               int64_t max_blocks_per_seq, int64_t num_blocks,
+                               int64_t cache_block_stride, int64_t bt_row_stride,
+                               int dtype, void *workspace, size_t workspace_bytes,
+                               int flags, void *stream);
+
+/* ---- (3) chunked-prefill causal attention over paged K/V ------------------------
+ * Replaces the prefill branch of ModelRunner.paged_forward
+ * (nanoPD/engine/model_runner.py:152-169: dense -inf mask + repeat_interleave +
+ * scaled_dot_product_attention) and, unlike it, reads earlier chunks from the pages.
+ * For chunk c (c < num_chunks) with n = chunk_tokens[c] queries starting at row
+ * chunk_q_offset[c] of q/out and absolute position chunk_start[c]:
+ *   query i attends to keys 0 .. chunk_start[c] + i of the pages
+ *   block_tables[c*bt_row_stride + ...]; the chunk's own K/V must already be stored.
+ * q, out: [total_q_tokens, num_q_heads, head_dim] contiguous.  The three chunk arrays
+ * are HOST int32 arrays (the scheduler knows them; nanoPD/engine/engine.py:68-90).
+ * Supported: f16/bf16, head_dim 128, block_size 16/32.                                  */
+size_t npd_prefill_workspace_bytes(int64_t total_q_tokens, int64_t num_q_heads,
+                                   int64_t num_kv_heads, int64_t head_dim, int device);
+int npd_paged_prefill_attention(void *out, const void *q, const void *k_cache,
+                                const void *v_cache, const int32_t *block_tables,
+                                const int32_t *chunk_q_offset_host,
+                                const int32_t *chunk_tokens_host,
+                                const int32_t *chunk_start_host,
+                                int64_t num_chunks, float scale,
+                                int64_t num_q_heads, int64_t num_kv_heads, int64_t head_dim,
+                                int64_t block_size, int64_t max_blocks_per_seq,
+                                int64_t num_blocks, int64_t cache_block_stride,
+                                int64_t bt_row_stride, int dtype,
+                                void *workspace, size_t workspace_bytes,
+                                int flags, void *stream);
+
+/* ---- (4) KV page migration ------------------------------------------------------
+ * Replaces transfer_kv's per-block copy_ loop (nanoPD/workers/kv_transfer.py:69-83):
+ *   for i < num_pairs, for every layer l:
+ *     dst_k[l, dst_blocks[i]] = src_k[l, src_blocks[i]]     (and the same for V)
+ * Pools are [num_layers, num_blocks, block_elems] with `*_layer_stride` and
+ * `*_block_stride` in elements; block_elems*elem_bytes must be a multiple of 16.
+ * src_blocks/dst_blocks are DEVICE int32 arrays resident on the device the kernel runs
+ * on (the current device).  Either pool may live on a peer GPU whose memory is mapped
+ * into the current device (peer access enabled, or an IPC mapping); the copy is a
+ * plain load/store kernel, so no copy engine or NCCL call is involved.
+ * `max_ctas` caps the grid (0 = one CTA per SM) so a side-stream migration leaves SMs
+ * to the compute stream.                                                               */
+int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
+                   const int32_t *src_blocks, const int32_t *dst_blocks, int64_t num_pairs,
+                   int64_t num_layers, int64_t block_elems, int elem_bytes,
+                   int64_t src_layer_stride, int64_t src_block_stride, int64_t src_num_blocks,
+                   int64_t dst_layer_stride, int64_t dst_block_stride, int64_t dst_num_blocks,
+                   int max_ctas, int32_t *status, void *stream);
+
+/* Enables peer access from the current device to `peer_device` (idempotent).
+ * Stands in for the driver-side mapping torch's copy_ sets up in the reference
+ * (nanoPD/workers/kv_transfer.py:6-14 only probes can_device_access_peer).              */
+int npd_enable_peer_access(int peer_device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NANOPD_B200_H */

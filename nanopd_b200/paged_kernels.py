@@ -1,0 +1,311 @@
+"""Drop-in for the reference's ``paged_kernels`` extension module, on top of the C ABI.
+
+``paged_attention_forward`` and ``paged_kv_store`` keep the positional signatures the
+reference binds (nanoPD/paged_attention/csrc/attention/paged_attention_bindings.cpp:6-14,
+nanoPD/paged_attention/csrc/kvstore/paged_kv_store_bindings.cpp:4-11), so
+``ModelRunner.paged_forward`` (nanoPD/engine/model_runner.py:94,146,189,270) can import this
+module unchanged.  ``paged_prefill_attention`` and ``paged_kv_migrate`` are additions.
+
+Everything launches asynchronously on the current stream of the tensors' device and
+returns ``None``; argument errors raise ``RuntimeError`` like the reference's TORCH_CHECKs.
+Device-side anomalies (an out-of-range block id, a length beyond the table) never fault:
+the kernels skip the access and set a status word that :func:`check_status` reads.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+
+_DTYPE_CODE = {torch.float16: _lib.NPD_DTYPE_F16, torch.bfloat16: _lib.NPD_DTYPE_BF16,
+               torch.float32: _lib.NPD_DTYPE_F32}
+
+_C = _lib.load()   # raises ImportError when the CUDA library is missing: no fallback path
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+# ---------------------------------------------------------------------------
+# Per-(device, stream) workspace.  The reference's split-K op allocates three temporaries
+# and syncs on every call (paged_attention_optimized_ops.cu:43-57); here one zeroed buffer
+# per device and stream is kept and grown on demand.  Several Python threads, each bound
+# to its own GPU, may call in concurrently (nanoPD/router/central_scheduler.py:132-135).
+# ---------------------------------------------------------------------------
+_ws_lock = threading.Lock()
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, stream_handle: int, nbytes: int) -> torch.Tensor:
+    key = (device.index, stream_handle)
+    with _ws_lock:
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            carry = 0
+            if ws is not None:
+                carry = int(ws[:4].view(torch.int32).item())
+            ws = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
+            if carry:
+                ws[:4].view(torch.int32).fill_(carry)
+            _workspaces[key] = ws
+        return ws
+
+
+def check_status(device=None, raise_on_error: bool = True) -> int:
+    """Reads (and clears) the device-side status words of ``device`` (default: current).
+
+    Returns the OR of the NPD_STATUS_* bits seen since the last call; raises RuntimeError
+    for a non-zero word unless ``raise_on_error`` is false.  Synchronises the streams involved.
+    """
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    bits = 0
+    with _ws_lock:
+        items = [(k, w) for k, w in _workspaces.items() if k[0] == idx]
+    with torch.cuda.device(idx):
+        for (_, stream_handle), ws in items:
+            out = ctypes.c_int32(0)
+            _lib.check(_C.npd_read_status(ws.data_ptr(), ctypes.byref(out), stream_handle))
+            bits |= out.value
+    if bits and raise_on_error:
+        names = [n for n, b in (("bad block id", 1), ("bad position / seq_len", 2), ("wait time-out", 4)) if bits & b]
+        raise RuntimeError("nanopd_b200 device status: " + ", ".join(names))
+    return bits
+
+
+def _stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _cache_geometry(cache: torch.Tensor, name: str):
+    _require(cache.dim() == 4, f"{name} must be [num_blocks, num_kv_heads, block_size, head_dim]")
+    nb, hkv, bs, d = cache.shape
+    _require(cache.stride(3) == 1 and cache.stride(2) == d and cache.stride(1) == bs * d,
+             f"{name}: the last three dims must be contiguous")
+    return nb, hkv, bs, d, cache.stride(0)
+
+
+# ---------------------------------------------------------------------------
+# (1) KV store
+# ---------------------------------------------------------------------------
+def paged_kv_store(k_cache, v_cache, k_src, v_src, block_tables, positions) -> None:
+    """Scatter new K/V rows into their block slots, in place.
+
+    Same contract as the reference op (nanoPD/paged_attention/csrc/kvstore/paged_kv_store.h:23-27,
+    paged_kv_store_ops.cu:7-50): caches ``[blocks, Hkv, B, D]``, sources ``[Hkv, T, D]``,
+    ``block_tables`` int32 ``[T, max_blk]`` with one row per token (a stride-0 ``expand`` of a
+    single row is accepted as is), ``positions`` int32 ``[T]`` absolute positions.
+
+    The call shape the reference's own tests still use is accepted too
+    (tests/test_paged_kernels.py:280,311): sources ``[1, Hkv, T, D]``, a 1-D block table of
+    the sequence and an ``int`` start position, meaning token ``t`` sits at ``start + t``.
+    """
+    _require(k_src.is_cuda, "k src is must be on CUDA")
+    _require(v_src.is_cuda, "v src is must be on CUDA")
+    if k_src.dim() == 4 and k_src.size(0) == 1:
+        k_src, v_src = k_src[0], v_src[0]
+    _require(k_src.dim() == 3, "k_src must be [num_kv_heads, num_tokens, head_dim]")
+    _require(v_src.shape == k_src.shape, "k_src and v_src must have the same shape")
+    _require(k_cache.is_cuda and v_cache.is_cuda and k_cache.device == k_src.device == v_cache.device,
+             "caches and sources must be on the same CUDA device")
+    dev = k_src.device
+    hkv, T, d = k_src.shape
+    if isinstance(positions, int):
+        positions = torch.arange(positions, positions + T, dtype=torch.int32, device=dev)
+    if block_tables.dim() == 1:
+        block_tables = block_tables.unsqueeze(0).expand(T, -1)
+    _require(block_tables.dtype == torch.int32 and positions.dtype == torch.int32,
+             "block_tables and positions must be int32")
+    _require(block_tables.dim() == 2 and block_tables.size(0) == T and positions.dim() == 1 and positions.numel() == T,
+             "block_tables must be [num_tokens, max_blocks] and positions [num_tokens]")
+    _require(block_tables.device == dev and positions.device == dev, "index tensors must be on the cache device")
+    _require(k_cache.dtype == v_cache.dtype == k_src.dtype == v_src.dtype, "cache and source dtypes differ")
+    _require(k_cache.dtype in _DTYPE_CODE, f"unsupported dtype {k_cache.dtype}")
+    nb, chkv, bs, cd, cstride = _cache_geometry(k_cache, "k_cache")
+    _require(_cache_geometry(v_cache, "v_cache") == (nb, chkv, bs, cd, cstride), "k_cache and v_cache layouts differ")
+    _require(chkv == hkv and cd == d, "source heads / head_dim do not match the cache")
+    _require(k_src.stride(2) == 1 and v_src.stride() == k_src.stride(), "sources need a contiguous last dim and equal strides")
+    if block_tables.stride(1) != 1 and block_tables.size(1) > 1:
+        block_tables = block_tables.contiguous()
+    if positions.stride(0) != 1:
+        positions = positions.contiguous()
+    if T == 0:
+        return
+    handle = _stream_handle(dev)
+    ws = _workspace(dev, handle, 256)
+    with torch.cuda.device(dev):
+        _lib.check(_C.npd_kv_store(
+            k_cache.data_ptr(), v_cache.data_ptr(), k_src.data_ptr(), v_src.data_ptr(),
+            block_tables.data_ptr(), positions.data_ptr(),
+            T, hkv, d, bs, nb, block_tables.size(1),
+            cstride, k_src.stride(0), k_src.stride(1), block_tables.stride(0),
+            _DTYPE_CODE[k_cache.dtype], ws.data_ptr(), handle))
+
+
+# ---------------------------------------------------------------------------
+# (2) decode attention
+# ---------------------------------------------------------------------------
+def paged_attention_forward(out, query, key_cache, value_cache, block_tables, seq_lens,
+                            scale: float, block_size: int, max_num_blocks_per_seq: int,
+                            _flags: int = 0) -> None:
+    """``out[s, h] = softmax(scale * q[s, h] . K_s^T) . V_s`` over paged K/V, written in place.
+
+    Same contract as the reference op (nanoPD/paged_attention/csrc/attention/paged_attention.h:24-34,
+    paged_attention_ops.cu:7-59): ``out``/``query`` ``[S, Hq, D]`` contiguous, caches
+    ``[blocks, Hkv, B, D]``, ``block_tables`` int32 ``[S, max_num_blocks_per_seq]`` zero padded,
+    ``seq_lens`` int32 ``[S]``; int64 index tensors raise RuntimeError as they do there
+    (pinned by tests/test_paged_kernels.py:218-227).  As in the reference's pointer math
+    (paged_attention_kernel.cu:72), row ``s`` of a contiguous table starts at
+    ``s * max_num_blocks_per_seq``.
+    """
+    _require(query.is_cuda, "query is must be on CUDA")
+    _require(query.dim() == 3, "query must be [num seqs, num_heads, head_size]")
+    _require(key_cache.dim() == 4, "key_cache must be [num_blocks, num_kv_heads, block_size, head_size]")
+    _require(block_tables.dtype == torch.int32, "block_tables must be int32")
+    _require(seq_lens.dtype == torch.int32, "seq_lens must be int32")
+    dev = query.device
+    S, hq, d = query.shape
+    _require(out.shape == query.shape and out.dtype == query.dtype and out.device == dev,
+             "out must match query in shape, dtype and device")
+    _require(query.is_contiguous() and out.is_contiguous(), "query and out must be contiguous")
+    _require(query.dtype in (torch.float16, torch.bfloat16),
+             f"paged_attention_forward supports float16 and bfloat16, got {query.dtype}")
+    _require(key_cache.dtype == query.dtype and value_cache.dtype == query.dtype, "cache dtype differs from query")
+    _require(key_cache.device == dev and value_cache.device == dev and block_tables.device == dev
+             and seq_lens.device == dev, "all tensors must be on the query's device")
+    nb, hkv, bs, cd, cstride = _cache_geometry(key_cache, "key_cache")
+    _require(_cache_geometry(value_cache, "value_cache") == (nb, hkv, bs, cd, cstride),
+             "key_cache and value_cache layouts differ")
+    _require(cd == d, "head_size of query and cache differ")
+    _require(int(block_size) == bs, f"block_size argument {block_size} != cache block size {bs}")
+    _require(hq % hkv == 0, "num_heads must be a multiple of num_kv_heads")
+    _require(seq_lens.dim() == 1 and seq_lens.numel() == S and seq_lens.stride(0) == 1, "seq_lens must be contiguous [S]")
+    max_blk = int(max_num_blocks_per_seq)
+    _require(max_blk >= 1, "max_num_blocks_per_seq must be positive")
+    if block_tables.dim() == 2 and block_tables.stride(1) == 1 and not block_tables.is_contiguous():
+        row_stride = block_tables.stride(0)          # a row-strided view: honour it
+        _require(block_tables.size(1) >= max_blk, "block_tables rows shorter than max_num_blocks_per_seq")
+    else:
+        _require(block_tables.is_contiguous(), "block_tables must be contiguous")
+        row_stride = max_blk                         # the reference's flat indexing
+        _require(block_tables.numel() >= S * max_blk, "block_tables smaller than num_seqs * max_num_blocks_per_seq")
+    if S == 0:
+        return
+    handle = _stream_handle(dev)
+    with torch.cuda.device(dev):
+        need = _C.npd_decode_workspace_bytes(S, hq, hkv, d, dev.index)
+        ws = _workspace(dev, handle, need)
+        _lib.check(_C.npd_paged_decode_attention(
+            out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+            block_tables.data_ptr(), seq_lens.data_ptr(), float(scale),
+            S, hq, hkv, d, bs, max_blk, nb, cstride, row_stride,
+            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(), int(_flags), handle))
+
+
+# ---------------------------------------------------------------------------
+# (3) chunked-prefill attention over paged K/V
+# ---------------------------------------------------------------------------
+def paged_prefill_attention(out, query, key_cache, value_cache, block_tables,
+                            chunk_q_offsets: Sequence[int], chunk_tokens: Sequence[int],
+                            chunk_starts: Sequence[int], scale: float, block_size: int,
+                            max_num_blocks_per_seq: int) -> None:
+    """Causal attention of prompt chunks over their paged K/V (the chunk's own rows included).
+
+    Replaces the prefill branch of ``paged_forward`` (nanoPD/engine/model_runner.py:152-169).
+    ``query``/``out`` are ``[total_tokens, Hq, D]`` with the chunks packed one after another;
+    chunk ``c`` occupies rows ``chunk_q_offsets[c] : + chunk_tokens[c]``, its first token sits
+    at absolute position ``chunk_starts[c]`` and row ``c`` of ``block_tables`` (int32
+    ``[num_chunks, max_num_blocks_per_seq]``) names its pages.  Store the chunk's K/V with
+    :func:`paged_kv_store` first, as the caller does (model_runner.py:132-150).
+    """
+    _require(query.is_cuda and query.dim() == 3, "query must be a CUDA tensor [tokens, num_heads, head_size]")
+    _require(block_tables.dtype == torch.int32 and block_tables.dim() == 2, "block_tables must be int32 [chunks, max_blk]")
+    dev = query.device
+    total, hq, d = query.shape
+    nchunks = len(chunk_tokens)
+    _require(len(chunk_q_offsets) == nchunks and len(chunk_starts) == nchunks and block_tables.size(0) == nchunks,
+             "one offset, token count, start position and table row per chunk")
+    _require(out.shape == query.shape and out.dtype == query.dtype and query.is_contiguous() and out.is_contiguous(),
+             "out must match query; both contiguous")
+    _require(query.dtype in (torch.float16, torch.bfloat16), f"unsupported dtype {query.dtype}")
+    nb, hkv, bs, cd, cstride = _cache_geometry(key_cache, "key_cache")
+    _require(_cache_geometry(value_cache, "value_cache") == (nb, hkv, bs, cd, cstride), "cache layouts differ")
+    _require(cd == d and int(block_size) == bs and key_cache.dtype == query.dtype == value_cache.dtype,
+             "cache does not match query")
+    _require(block_tables.stride(1) == 1 or block_tables.size(1) == 1, "block_tables rows must be contiguous")
+    max_blk = int(max_num_blocks_per_seq)
+    _require(1 <= max_blk <= block_tables.size(1), "max_num_blocks_per_seq out of range")
+    for off, n, start in zip(chunk_q_offsets, chunk_tokens, chunk_starts):
+        _require(n >= 0 and off >= 0 and off + n <= total and start >= 0, "chunk outside the query tensor")
+        _require(start + n <= max_blk * bs, "chunk reaches beyond its block table")
+    if nchunks == 0 or total == 0:
+        return
+    arr = ctypes.c_int32 * nchunks
+    handle = _stream_handle(dev)
+    with torch.cuda.device(dev):
+        need = _C.npd_prefill_workspace_bytes(total, hq, hkv, d, dev.index)
+        ws = _workspace(dev, handle, need)
+        _lib.check(_C.npd_paged_prefill_attention(
+            out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+            block_tables.data_ptr(), arr(*chunk_q_offsets), arr(*chunk_tokens), arr(*chunk_starts),
+            nchunks, float(scale), hq, hkv, d, bs, max_blk, nb, cstride, block_tables.stride(0),
+            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(), 0, handle))
+
+
+# ---------------------------------------------------------------------------
+# (4) KV page migration
+# ---------------------------------------------------------------------------
+def _pool_geometry(pool: torch.Tensor, name: str):
+    _require(pool.dim() == 5, f"{name} must be [layers, blocks, num_kv_heads, block_size, head_dim]")
+    L, nb = pool.shape[:2]
+    block_elems = pool.shape[2] * pool.shape[3] * pool.shape[4]
+    _require(pool[0, 0].is_contiguous(), f"{name}: a block must be contiguous")
+    return L, nb, block_elems, pool.stride(0), pool.stride(1)
+
+
+def paged_kv_migrate(src_k, src_v, dst_k, dst_v, src_blocks, dst_blocks=None, max_ctas: int = 0) -> None:
+    """Copy blocks ``src_blocks[i] -> dst_blocks[i]`` of every layer between two 5-D pools.
+
+    One kernel on the current stream of the CURRENT device, which must be able to address
+    both pools (same device, or peer access enabled — see ``kv_transfer.transfer_kv``).
+    ``src_blocks``/``dst_blocks``: int32 tensors on the current device (or Python lists,
+    which are copied there).  ``max_ctas`` caps the grid so a side-stream migration leaves
+    SMs to compute.
+    """
+    dev = torch.device("cuda", torch.cuda.current_device())
+    L, snb, belems, sls, sbs = _pool_geometry(src_k, "src_k")
+    _require(_pool_geometry(src_v, "src_v") == (L, snb, belems, sls, sbs), "src_k and src_v layouts differ")
+    L2, dnb, belems2, dls, dbs = _pool_geometry(dst_k, "dst_k")
+    _require(_pool_geometry(dst_v, "dst_v") == (L2, dnb, belems2, dls, dbs), "dst_k and dst_v layouts differ")
+    _require(L == L2 and belems == belems2 and src_k.dtype == dst_k.dtype == src_v.dtype == dst_v.dtype,
+             "source and destination pools differ in layers, block shape or dtype")
+    if not torch.is_tensor(src_blocks):
+        src_blocks = torch.tensor(list(src_blocks), dtype=torch.int32, device=dev)
+    if dst_blocks is None:
+        dst_blocks = src_blocks
+    elif not torch.is_tensor(dst_blocks):
+        dst_blocks = torch.tensor(list(dst_blocks), dtype=torch.int32, device=dev)
+    _require(src_blocks.dtype == torch.int32 and dst_blocks.dtype == torch.int32, "block lists must be int32")
+    _require(src_blocks.device == dev and dst_blocks.device == dev, "block lists must live on the current device")
+    _require(src_blocks.numel() == dst_blocks.numel() and src_blocks.is_contiguous() and dst_blocks.is_contiguous(),
+             "block lists must be contiguous and of equal length")
+    n = src_blocks.numel()
+    if n == 0:
+        return
+    handle = _stream_handle(dev)
+    ws = _workspace(dev, handle, 256)
+    _lib.check(_C.npd_kv_migrate(
+        src_k.data_ptr(), src_v.data_ptr(), dst_k.data_ptr(), dst_v.data_ptr(),
+        src_blocks.data_ptr(), dst_blocks.data_ptr(), n, L, belems, src_k.element_size(),
+        sls, sbs, snb, dls, dbs, dnb, int(max_ctas), ws.data_ptr(), handle))
+
+
+def enable_peer_access(peer_device: int) -> None:
+    """Map ``peer_device``'s memory into the current device (idempotent)."""
+    _lib.check(_C.npd_enable_peer_access(int(peer_device)))

@@ -1,0 +1,71 @@
+"""Shared fixtures.  Tests marked ``gpu`` need a B200 and call the CUDA path through the
+C ABI; everything else runs on the CPU (oracle vs. golden vectors, host logic, symbol export)."""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+# max-abs tolerances against the fp32-accumulated oracle
+TOL = {torch.float16: 2e-3, torch.bfloat16: 1e-2}
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+def _from_bits(a: np.ndarray, bf16: bool) -> torch.Tensor:
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if t.dtype == torch.int16:
+        return t.view(torch.bfloat16 if bf16 else torch.float16)
+    return t
+
+
+def load_decode_cases():
+    """The reference-generated decode cases of tests/golden/decode_reference_cases.npz."""
+    z = np.load(GOLDEN / "decode_reference_cases.npz")
+    cases = []
+    for name in z["names"].tolist():
+        bf16 = bool(z[f"{name}/is_bf16"])
+        cases.append(dict(
+            name=name,
+            dtype=torch.bfloat16 if bf16 else torch.float16,
+            q=_from_bits(z[f"{name}/q"], bf16), k=_from_bits(z[f"{name}/k"], bf16),
+            v=_from_bits(z[f"{name}/v"], bf16),
+            block_tables=torch.from_numpy(z[f"{name}/block_tables"]),
+            seq_lens=torch.from_numpy(z[f"{name}/seq_lens"]),
+            scale=float(z[f"{name}/scale"]),
+            ref_out=_from_bits(z[f"{name}/ref_out"], bf16),
+            out_fp32=torch.from_numpy(z[f"{name}/out_fp32"])))
+    return cases
+
+
+@pytest.fixture(scope="session")
+def decode_cases():
+    return load_decode_cases()
+
+
+@pytest.fixture()
+def kernels():
+    """The drop-in module; importing it loads the CUDA library (no fallback)."""
+    import paged_kernels
+    yield paged_kernels
+    if torch.cuda.is_available():
+        # every GPU test must leave the device-side status word clean
+        assert paged_kernels.check_status(raise_on_error=False) == 0
