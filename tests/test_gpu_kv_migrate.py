@@ -1,0 +1,96 @@
+"""GPU: KV page migration through the C ABI — bit-exact against the oracle."""
+import pytest
+import torch
+
+from nanopd_b200 import kv_transfer
+from oracle import paged_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _pools(L, nb, Hkv, B, D, dtype, device, seed):
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(L, nb, Hkv, B, D, generator=g).to(dtype)
+    v = torch.randn(L, nb, Hkv, B, D, generator=g).to(dtype)
+    return k, v, k.to(device), v.to(device)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("max_ctas", [0, 4])
+def test_same_ids_like_the_reference(kernels, dtype, max_ctas):
+    """transfer_kv with equal ids on both sides (kv_transfer.py:73-79), both pools on one GPU."""
+    L, nb, Hkv, B, D = 4, 24, 8, 16, 128
+    sk, sv, dsk, dsv = _pools(L, nb, Hkv, B, D, dtype, "cuda:0", 0)
+    dk, dv, ddk, ddv = _pools(L, nb, Hkv, B, D, dtype, "cuda:0", 1)
+    table = [5, 17, 3, 22, 0]
+    path = kv_transfer.transfer_kv(dsk, dsv, ddk, ddv, table, max_ctas=max_ctas)
+    assert path == "p2p"
+    paged_oracle.kv_migrate(sk, sv, dk, dv, table)
+    torch.cuda.synchronize()
+    assert torch.equal(ddk.cpu(), dk) and torch.equal(ddv.cpu(), dv)
+
+
+def test_different_ids_and_side_stream(kernels):
+    L, nb, Hkv, B, D = 3, 16, 2, 16, 64
+    sk, sv, dsk, dsv = _pools(L, nb, Hkv, B, D, torch.float16, "cuda:0", 2)
+    dk = torch.zeros(L, 9, Hkv, B, D, dtype=torch.float16)
+    dv = torch.zeros_like(dk)
+    ddk, ddv = dk.to("cuda:0"), dv.to("cuda:0")
+    stream = torch.cuda.Stream(device="cuda:0")
+    stream.wait_stream(torch.cuda.current_stream())
+    kv_transfer.transfer_kv(dsk, dsv, ddk, ddv, [1, 15, 7], stream=stream, dst_block_table=[8, 0, 4])
+    ev = torch.cuda.Event()
+    stream.record_event(ev)          # completion as in DecodeWorker.receive_kv_async
+    ev.synchronize()
+    paged_oracle.kv_migrate(sk, sv, dk, dv, [1, 15, 7], [8, 0, 4])
+    assert torch.equal(ddk.cpu(), dk) and torch.equal(ddv.cpu(), dv)
+    torch.cuda.synchronize()
+
+
+def test_request_sized_migration_roundtrip(kernels):
+    """A 2048-token request at the Qwen3-8B layout (36 layers, 128 blocks of 32 KiB per layer and tensor):
+    migrate there and back, the pool must be unchanged (round-trip property)."""
+    L, nb, Hkv, B, D = 36, 160, 8, 16, 128
+    src_k = torch.randn(L, nb, Hkv, B, D, device="cuda:0").bfloat16()
+    src_v = torch.randn(L, nb, Hkv, B, D, device="cuda:0").bfloat16()
+    mid_k, mid_v = torch.zeros_like(src_k), torch.zeros_like(src_v)
+    back_k, back_v = torch.zeros_like(src_k), torch.zeros_like(src_v)
+    ids = torch.randperm(nb)[:128].tolist()
+    there = torch.randperm(nb)[:128].tolist()
+    kv_transfer.transfer_kv(src_k, src_v, mid_k, mid_v, ids, dst_block_table=there)
+    kv_transfer.transfer_kv(mid_k, mid_v, back_k, back_v, there, dst_block_table=ids)
+    torch.cuda.synchronize()
+    sel = torch.tensor(ids, device="cuda:0")
+    assert torch.equal(back_k[:, sel], src_k[:, sel]) and torch.equal(back_v[:, sel], src_v[:, sel])
+    rest = torch.ones(nb, dtype=torch.bool, device="cuda:0")
+    rest[sel] = False
+    assert torch.count_nonzero(back_k[:, rest]) == 0
+
+
+def test_bad_block_id_is_skipped(kernels):
+    L, nb, Hkv, B, D = 2, 4, 2, 16, 64
+    sk, sv, dsk, dsv = _pools(L, nb, Hkv, B, D, torch.float16, "cuda:0", 3)
+    ddk, ddv = torch.zeros_like(dsk), torch.zeros_like(dsv)
+    kv_transfer.transfer_kv(dsk, dsv, ddk, ddv, [1, 99])
+    assert kernels.check_status(raise_on_error=False) == 1
+    assert torch.equal(ddk[:, 1], dsk[:, 1]) and torch.count_nonzero(ddk[:, [0, 2, 3]]) == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_to_peer_pull_over_nvlink(kernels):
+    """Prefill pool on cuda:0, decode pool on cuda:1, pulled by a kernel on cuda:1's stream.
+    Plain peer loads only."""
+    L, nb, Hkv, B, D = 4, 32, 8, 16, 128
+    sk, sv, dsk, dsv = _pools(L, nb, Hkv, B, D, torch.bfloat16, "cuda:0", 4)
+    ddk = torch.zeros(L, nb, Hkv, B, D, dtype=torch.bfloat16, device="cuda:1")
+    ddv = torch.zeros_like(ddk)
+    torch.cuda.synchronize("cuda:0")
+    stream = torch.cuda.Stream(device="cuda:1")
+    table = [3, 30, 11, 12]
+    assert kv_transfer.transfer_kv(dsk, dsv, ddk, ddv, table, stream=stream) == "p2p"
+    stream.synchronize()
+    dk, dv = torch.zeros_like(sk), torch.zeros_like(sv)
+    paged_oracle.kv_migrate(sk, sv, dk, dv, table)
+    assert torch.equal(ddk.cpu(), dk) and torch.equal(ddv.cpu(), dv)
+    with torch.cuda.device(1):
+        assert kernels.check_status(raise_on_error=False) == 0
