@@ -96,6 +96,33 @@ int npd_paged_decode_attention(void *out, const void *q, const void *k_cache,
                                int dtype, void *workspace, size_t workspace_bytes,
                                int flags, void *stream);
 
+/* ---- (2b) decode attention without a caller workspace ----------------------------
+ * No counterpart in the reference.  Same arithmetic and arguments as
+ * npd_paged_decode_attention, for hosts that cannot allocate device memory when they call:
+ * a worker whose HBM went entirely to the KV pool and weights at start-up, a step loop
+ * that forbids allocation after initialisation, a foreign runtime binding this ABI with no
+ * device allocator (cudaMalloc/cudaFree would also stall the whole device).  The scratch is a
+ * 20 MiB device array inside the library image (npd_decode_static_scratch_bytes()); every
+ * GPU that loads the library holds it until the process exits.  The call allocates and
+ * frees nothing.  Shapes whose scratch need (npd_decode_workspace_bytes) exceeds the array
+ * are refused with NPD_ERR_WORKSPACE; on a B200 every supported shape fits.
+ * The FIRST call on each device looks up the array's device address (one
+ * cudaGetSymbolAddress, with that device current) — make that call before any stream
+ * capture begins.  All calls on a device share the one array, which keeps the previous
+ * call's contents; the status word is cleared at the start of each call, the rest is
+ * written before it is read.  Two calls that can overlap on the GPU (different streams)
+ * race on it: serialise them, or give the concurrent ones the workspace variant.
+ * `status_out` (device int32, may be NULL) receives this call's NPD_STATUS_* bits.         */
+size_t npd_decode_static_scratch_bytes(void);
+int npd_paged_decode_attention_static(void *out, const void *q, const void *k_cache,
+                                      const void *v_cache, const int32_t *block_tables,
+                                      const int32_t *seq_lens, float scale,
+                                      int64_t num_seqs, int64_t num_q_heads, int64_t num_kv_heads,
+                                      int64_t head_dim, int64_t block_size,
+                                      int64_t max_blocks_per_seq, int64_t num_blocks,
+                                      int64_t cache_block_stride, int64_t bt_row_stride,
+                                      int dtype, int32_t *status_out, int flags, void *stream);
+
 /* ---- (3) chunked-prefill causal attention over paged K/V ------------------------
  * Replaces the prefill branch of ModelRunner.paged_forward
  * (nanoPD/engine/model_runner.py:152-169: dense -inf mask + repeat_interleave +

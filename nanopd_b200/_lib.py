@@ -25,6 +25,10 @@ SIGNATURES = {
     "npd_paged_decode_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                            c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                            c_int64, c_int64, c_int, c_void_p, c_size_t, c_int, c_void_p]),
+    "npd_decode_static_scratch_bytes": (c_size_t, []),
+    "npd_paged_decode_attention_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                                  c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                                  c_int64, c_int64, c_int, c_void_p, c_int, c_void_p]),
     "npd_prefill_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "npd_paged_prefill_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),

@@ -25,6 +25,7 @@
 //     (zero fill) and flagged — nothing can fault.
 //
 // Algorithmic bytes per launch: sum(len_s)*2*Hkv*D*e + 2*S*Hq*D*e + sum(ceil(len_s/B))*4 + 4*S.
+#include <atomic>
 #include <cstdlib>
 
 #include "npd_common.cuh"
@@ -747,5 +748,74 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
                  : dispatch_decode<__nv_bfloat16>(static_cast<int>(head_dim), wp.nt, p, tk, tv, ls, merge, st);
         if (rc != NPD_OK) return rc;
     }
+    return NPD_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate device memory
+// ---------------------------------------------------------------------------
+// Some hosts of this library cannot hand it a workspace: a decode worker that gave all free
+// HBM to the KV block pool and the weights at start-up, a step loop with a "no allocation
+// after initialisation" rule, or a foreign-language runtime binding the C ABI without a device
+// allocator of its own (and cudaMalloc / cudaFree would stall every stream of the device
+// anyway).  For them the scratch below is part of the library image: every GPU that loads the
+// library holds these 20 MiB until the process exits.  It is large enough for every supported
+// shape on a B200 (148 SMs x 8 workers x 2 partial records of at most 8320 B, plus the header).
+#define NPD_STATIC_SCRATCH_BYTES (20u << 20)
+static __device__ __align__(256) unsigned char g_decode_static_scratch[NPD_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// In host code `g_decode_static_scratch` is only a stand-in for the device array; the device
+// address has to be asked for, once per device, with that device current.
+int static_scratch_address(void **ptr_out) {
+    static std::atomic<void *> resolved[64];
+    int dev = -1;
+    NPD_CUDA_TRY(cudaGetDevice(&dev));
+    NPD_REQUIRE(dev >= 0 && dev < 64, NPD_ERR_UNSUPPORTED, "static scratch: device index %d out of range", dev);
+    void *ptr = resolved[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
+        NPD_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+        NPD_REQUIRE(ptr != nullptr, NPD_ERR_CUDA, "static scratch: cudaGetSymbolAddress returned NULL");
+        resolved[dev].store(ptr, std::memory_order_release);
+    }
+    *ptr_out = ptr;
+    return NPD_OK;
+}
+
+}  // namespace
+
+extern "C" size_t npd_decode_static_scratch_bytes(void) { return NPD_STATIC_SCRATCH_BYTES; }
+
+extern "C" int npd_paged_decode_attention_static(void *out, const void *q, const void *k_cache,
+                                                 const void *v_cache, const int32_t *block_tables,
+                                                 const int32_t *seq_lens, float scale, int64_t num_seqs,
+                                                 int64_t num_q_heads, int64_t num_kv_heads, int64_t head_dim,
+                                                 int64_t block_size, int64_t max_blocks_per_seq,
+                                                 int64_t num_blocks, int64_t cache_block_stride,
+                                                 int64_t bt_row_stride, int dtype, int32_t *status_out,
+                                                 int flags, void *stream) {
+    int dev = 0;
+    NPD_CUDA_TRY(cudaGetDevice(&dev));
+    const size_t need = npd_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim, dev);
+    NPD_REQUIRE(need != 0, NPD_ERR_INVALID_ARG, "decode attention (static scratch): non-positive dimension");
+    NPD_REQUIRE(need <= NPD_STATIC_SCRATCH_BYTES, NPD_ERR_WORKSPACE,
+                "decode attention (static scratch): this shape needs %zu bytes of scratch, the built-in array "
+                "holds %u; use npd_paged_decode_attention with a caller-owned workspace",
+                need, (unsigned)NPD_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    const int rc_addr = static_scratch_address(&scratch);   // first call on a device: resolves the symbol
+    if (rc_addr != NPD_OK) return rc_addr;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left.  Only the status word must start at zero;
+    // the tile prefix and the partial records are written before they are read.
+    NPD_CUDA_TRY(cudaMemsetAsync(scratch, 0, sizeof(int32_t), st));
+    const int rc = npd_paged_decode_attention(out, q, k_cache, v_cache, block_tables, seq_lens, scale, num_seqs,
+                                              num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
+                                              num_blocks, cache_block_stride, bt_row_stride, dtype, scratch,
+                                              NPD_STATIC_SCRATCH_BYTES, flags, st);
+    if (rc != NPD_OK) return rc;
+    if (status_out != nullptr)
+        NPD_CUDA_TRY(cudaMemcpyAsync(status_out, scratch, sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
     return NPD_OK;
 }
