@@ -222,6 +222,12 @@ def run_gpu_arm(args):
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
+    if args.profile:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_run": True, "steps": steps, "batch": S, "attention_bytes_per_launch": attn_bytes}))
+        return 0
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -334,6 +340,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--profile", action="store_true",
+                    help="only warm up and run the timed step loop (for short ncu captures); prints no bench line")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
