@@ -48,27 +48,35 @@ static EncodeTiledFn resolve_encode_tiled() {
     return reinterpret_cast<EncodeTiledFn>(fn);
 }
 
-int encode_cache_tensor_map(CUtensorMap *map, const void *base, int dtype, int64_t head_dim,
-                            int64_t rows_per_block, int64_t num_blocks,
-                            int64_t block_stride_elems, int box_rows) {
+int encode_tiled_3d(CUtensorMap *map, const void *base, int dtype, const uint64_t dims[3],
+                    const uint64_t strides_bytes[2], const uint32_t box[3]) {
     EncodeTiledFn encode = resolve_encode_tiled();
     NPD_REQUIRE(encode != nullptr, NPD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    NPD_REQUIRE(aligned16(base), NPD_ERR_INVALID_ARG, "cache base pointer must be 16-byte aligned");
-    NPD_REQUIRE((block_stride_elems * 2) % 16 == 0, NPD_ERR_INVALID_ARG,
-                "cache block stride must be a multiple of 16 bytes");
-    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows_per_block),
-                                static_cast<cuuint64_t>(num_blocks)};
-    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2u,
-                                   static_cast<cuuint64_t>(block_stride_elems) * 2u};
-    const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 1u};
+    NPD_REQUIRE(aligned16(base), NPD_ERR_INVALID_ARG, "tensor base pointer must be 16-byte aligned");
+    NPD_REQUIRE(strides_bytes[0] % 16 == 0 && strides_bytes[1] % 16 == 0, NPD_ERR_INVALID_ARG,
+                "tensor strides must be multiples of 16 bytes");
+    const cuuint64_t gdims[3] = {dims[0], dims[1], dims[2]};
+    const cuuint64_t gstrides[2] = {strides_bytes[0], strides_bytes[1]};
+    const cuuint32_t gbox[3] = {box[0], box[1], box[2]};
     const cuuint32_t estr[3] = {1u, 1u, 1u};
     const CUtensorMapDataType dt =
         dtype == NPD_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = encode(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr,
+    CUresult r = encode(map, dt, 3, const_cast<void *>(base), gdims, gstrides, gbox, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     NPD_REQUIRE(r == CUDA_SUCCESS, NPD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return NPD_OK;
+}
+
+int encode_cache_tensor_map(CUtensorMap *map, const void *base, int dtype, int64_t head_dim,
+                            int64_t rows_per_block, int64_t num_blocks,
+                            int64_t block_stride_elems, int box_rows) {
+    const uint64_t dims[3] = {static_cast<uint64_t>(head_dim), static_cast<uint64_t>(rows_per_block),
+                              static_cast<uint64_t>(num_blocks)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(head_dim) * 2u,
+                                 static_cast<uint64_t>(block_stride_elems) * 2u};
+    const uint32_t box[3] = {64u, static_cast<uint32_t>(box_rows), 1u};
+    return encode_tiled_3d(map, base, dtype, dims, strides, box);
 }
 
 }  // namespace npd

@@ -1,11 +1,491 @@
-// Kernel 3 placeholder so the library exports every declared symbol while the kernel is built.
+// Kernel 3: chunked-prefill causal attention over paged K/V on the 5th-generation tensor cores.
+//
+// One CTA computes a 128-row query tile for one kv head: the rows are TQ = 128/G consecutive
+// query tokens of a chunk times the G q heads that share the kv head (token-major), so every
+// K/V tile read from the pages serves the whole group.  Keys are walked in tiles of 128
+// (8 pages of 16 tokens) from position 0 up to the tile's last query position — earlier chunks
+// are read from the pages like any other key, which the reference's prefill branch does not do
+// (nanoPD/engine/model_runner.py:125-127,152-168 attends to the current chunk only).
+//
+// Warp roles (192 threads):
+//   warps 0-3  softmax + accumulate: thread i owns row i == TMEM lane i (no shuffles needed)
+//   warp  4    TMA producer: Q tile once, then K/V tiles into a 2-stage shared-memory ring
+//              (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA operand layout)
+//   warp  5    TMEM allocation and the single thread that issues tcgen05.mma
+// Per key tile:  S = Q.K^T  (tcgen05.mma, fp32 accumulator in TMEM columns 0-127)
+//                P = exp2(S*scale - m) rounded to the input type, written to shared memory in the
+//                    K-major swizzled layout (masking only on tiles that touch the diagonal)
+//                PV = P.V   (tcgen05.mma with V as the MN-major B operand, TMEM columns 128-255)
+//                O  = O*alpha + PV  in fp32 registers of the row's thread.
+// Completion of MMAs is tracked with tcgen05.commit on mbarriers; every wait is bounded and an
+// abort flag lets all roles leave together, after which TMEM is released.
+//
+// Algorithmic flops per chunk: 4*Hq*D*(n*start + n(n+1)/2)  (causal; masked work not counted).
 #include "npd_common.cuh"
+
+namespace {
+
+using namespace npd;
+
+constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays)
+constexpr int kRows = 128;         // UMMA M
+constexpr int kKeys = 128;         // keys per tile (UMMA N of the score MMA)
+constexpr int kD = 128;            // head_dim
+constexpr int kThreads = 192;
+constexpr int kHalfBytes = kRows * 128;             // one 64-element half of a 128-row operand tile
+constexpr int kTileBytes = 2 * kHalfBytes;          // 32 KiB: Q, K, V or P tile
+constexpr int kStages = 2;
+constexpr int kTmemCols = 256;
+constexpr long long kWaitCycles = 4000000000LL;
+
+struct PrefillParams {
+    void *out;
+    const int32_t *block_tables;
+    int32_t *status;
+    float scale_log2;
+    int num_chunks;
+    int num_q_heads, num_kv_heads, group;
+    int tq;                 // query tokens per tile = 128 / group (floor)
+    int block_size;
+    int max_blocks_per_seq;
+    int num_blocks;
+    long long bt_row_stride;
+    int chunk_q_offset[kMaxChunks];
+    int chunk_tokens[kMaxChunks];
+    int chunk_start[kMaxChunks];
+    int tile_prefix[kMaxChunks + 1];   // exclusive prefix of ceil(chunk_tokens / tq)
+};
+
+// ---- tcgen05 wrappers ---------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base + i).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (version 1, 128-byte swizzle, 8-row groups 1024 B apart).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand: 64-element atoms `lbo_bytes` apart along MN, 8-row groups 1024 B apart along K.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t lbo_bytes) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | (64ull << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulate, A/B of type `fmt` (0 = f16, 1 = bf16), M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_major, uint32_t M, uint32_t N) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+// Bounded, abortable mbarrier wait shared by all roles.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                              int32_t *status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            atomicOr(status, NPD_STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+
+struct alignas(8) SmemCtrl {
+    uint64_t q_full;
+    uint64_t kv_full[kStages];
+    uint64_t kv_empty[kStages];
+    uint64_t s_full;
+    uint64_t p_full;
+    uint64_t o_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
+                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+    uint8_t *sbase = smem_raw + pad;
+    uint8_t *q_tile = sbase;                                   // 32 KiB
+    uint8_t *kv_ring = sbase + kTileBytes;                     // kStages x (K 32 KiB + V 32 KiB)
+    uint8_t *p_tile = kv_ring + kStages * 2 * kTileBytes;      // 32 KiB
+    SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(p_tile + kTileBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- which tile is mine ----
+    const int h = blockIdx.x % p.num_kv_heads;
+    const int tile_rank = blockIdx.x / p.num_kv_heads;
+    int c = 0;
+    while (c + 1 < p.num_chunks && p.tile_prefix[c + 1] <= tile_rank) ++c;
+    const int tiles_in_chunk = p.tile_prefix[c + 1] - p.tile_prefix[c];
+    // later tiles of a chunk see more keys: hand them out first
+    const int m_tile = tiles_in_chunk - 1 - (tile_rank - p.tile_prefix[c]);
+    const int n_tok = p.chunk_tokens[c], start = p.chunk_start[c], qoff = p.chunk_q_offset[c];
+    const int t0 = m_tile * p.tq;
+    const int tq_valid = min(p.tq, n_tok - t0);
+    const int kv_end = start + t0 + tq_valid;                 // keys [0, kv_end) are visible to the tile
+    const int num_kv_tiles = (kv_end + kKeys - 1) / kKeys;
+    const int ctx_end = start + n_tok;                        // keys written so far for this sequence
+    const int npages = (ctx_end + p.block_size - 1) / p.block_size;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&ctrl->q_full), 1);
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->kv_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&ctrl->s_full), 1);
+        mbar_init(smem_u32(&ctrl->p_full), 128);
+        mbar_init(smem_u32(&ctrl->o_full), 1);
+        ctrl->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctrl->tmem_base;
+    volatile int *abort_flag = &ctrl->abort_flag;
+
+    if (warp == 4) {
+        // =========================== TMA producer ===========================
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            // Q tile: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch
+            const uint32_t qbar = smem_u32(&ctrl->q_full);
+            mbar_expect_tx(qbar, static_cast<uint32_t>(2 * p.tq * p.group * 128));
+            for (int hf = 0; hf < 2; ++hf)
+                tma_load_3d(smem_u32(q_tile + hf * kHalfBytes), &tm_q, qbar, hf * 64, h * p.group, qoff + t0);
+
+            const int32_t *table = p.block_tables + (long long)c * p.bt_row_stride;
+            for (int j = 0; j < num_kv_tiles; ++j) {
+                const int stage = j % kStages;
+                if (j >= kStages) {
+                    if (!wait_or_abort(smem_u32(&ctrl->kv_empty[stage]), ((j / kStages) - 1) & 1, abort_flag, p.status))
+                        break;
+                }
+                uint8_t *k_tile = kv_ring + (size_t)stage * 2 * kTileBytes;
+                uint8_t *v_tile = k_tile + kTileBytes;
+                const uint32_t bar = smem_u32(&ctrl->kv_full[stage]);
+                const int key0 = j * kKeys;
+                // 16-key row groups that hold at least one written key; the rest is never loaded
+                int ngroups = 0;
+                for (int gidx = 0; gidx < kKeys / 16; ++gidx) ngroups += (key0 + gidx * 16 < ctx_end) ? 1 : 0;
+                mbar_expect_tx(bar, static_cast<uint32_t>(ngroups * 4 * 16 * 128));
+                for (int gidx = 0; gidx < ngroups; ++gidx) {
+                    const int key = key0 + gidx * 16;
+                    const int page = key / p.block_size;
+                    const int sub = (key % p.block_size) / 16;
+                    int id = page < npages ? __ldg(table + page) : -1;
+                    if (id < 0 || id >= p.num_blocks) {
+                        atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
+                        id = p.num_blocks;            // out of bounds for the tensor map: zero fill
+                    }
+                    const int row = h * p.block_size + sub * 16;
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const uint32_t off = static_cast<uint32_t>(hf * kHalfBytes + gidx * 16 * 128);
+                        tma_load_3d(smem_u32(k_tile) + off, &tm_k, bar, hf * 64, row, id);
+                        tma_load_3d(smem_u32(v_tile) + off, &tm_v, bar, hf * 64, row, id);
+                    }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // =========================== MMA issuer ===========================
+        if (lane == 0) {
+            constexpr uint32_t fmt = Elem<T>::kDtype == NPD_DTYPE_BF16 ? 1u : 0u;
+            constexpr uint32_t idesc_s = instr_desc(fmt, 0u, kRows, kKeys);
+            constexpr uint32_t idesc_pv = instr_desc(fmt, 1u, kRows, kD);
+            const uint32_t q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
+            const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+            bool ok = wait_or_abort(smem_u32(&ctrl->q_full), 0, abort_flag, p.status);
+            for (int j = 0; ok && j < num_kv_tiles; ++j) {
+                const int stage = j % kStages;
+                const uint32_t k_addr = smem_u32(kv_ring + (size_t)stage * 2 * kTileBytes);
+                const uint32_t v_addr = k_addr + kTileBytes;
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->kv_full[stage]), (j / kStages) & 1, abort_flag, p.status))) break;
+                tc_fence_after();
+                // ---- S = Q . K^T : 8 k-steps of 16 elements; a step advances 32 B inside the swizzle atom
+#pragma unroll
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    tc_mma_f16(tmem_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(smem_u32(&ctrl->s_full));
+                // ---- wait for P (and for S to be drained), then PV = P . V
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->p_full), j & 1, abort_flag, p.status))) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kKeys / 16; ++ks) {
+                    const uint32_t a_off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;   // P is K-major over keys
+                    const uint32_t b_off = ks * 16 * 128;                            // 16 keys = two 8-row groups
+                    tc_mma_f16(tmem_o, desc_k_major(p_addr + a_off), desc_mn_major(v_addr + b_off, kHalfBytes),
+                               idesc_pv, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(smem_u32(&ctrl->kv_empty[stage]));   // K and V of this stage are free again
+                tc_commit(smem_u32(&ctrl->o_full));            // PV is in TMEM
+            }
+        }
+    } else {
+        // =========================== softmax + accumulate (warps 0-3) ===========================
+        const int row = warp * 32 + lane;                       // == TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
+        const bool row_valid = tq_idx < tq_valid;
+        const int pos = start + t0 + tq_idx;                    // last visible key of this row
+        float o[kD];
+#pragma unroll
+        for (int i = 0; i < kD; ++i) o[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+
+        for (int j = 0; ok && j < num_kv_tiles; ++j) {
+            const int stage = j % kStages;
+            const int key0 = j * kKeys;
+            // V rows at or past ctx_end were never written (or never loaded): clear them so that
+            // P = 0 there cannot meet a NaN.  Needs the tile to have landed first.
+            if (key0 + kKeys > ctx_end) {
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->kv_full[stage]), (j / kStages) & 1, abort_flag, p.status))) break;
+                uint8_t *v_tile = kv_ring + (size_t)stage * 2 * kTileBytes + kTileBytes;
+                const int first = max(ctx_end - key0, 0);
+                const int cnt = (kKeys - first) * 16;            // 16-byte pieces: 2 halves x 8 per row
+                for (int idx = threadIdx.x; idx < cnt; idx += 128) {
+                    const int r = first + idx / 16, piece = idx % 16;
+                    *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kHalfBytes + r * 128 + ((piece & 7) << 4)) =
+                        make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async_smem();
+            }
+            if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full), j & 1, abort_flag, p.status))) break;
+            tc_fence_after();
+
+            const bool need_mask = key0 + kKeys - 1 > start + t0;   // tile reaches past the first row's diagonal
+            // ---- pass 1: row maximum ----
+            float mx = -INFINITY;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                float s[32];
+                tmem_ld32(tmem + lane_base + cc * 32, s);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float x = (!need_mask || key0 + cc * 32 + i <= pos) ? s[i] : -INFINITY;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            const float alpha = fast_exp2(m_run - m_new);        // 0 on the first tile (m_run = -inf)
+            m_run = m_new;
+            // ---- pass 2: probabilities -> shared memory (K-major, 128-byte swizzle) ----
+            float lsum = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                float s[32];
+                tmem_ld32(tmem + lane_base + cc * 32, s);
+                tmem_wait_ld();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const bool v0 = !need_mask || key0 + cc * 32 + i <= pos;
+                    const bool v1 = !need_mask || key0 + cc * 32 + i + 1 <= pos;
+                    const float p0 = v0 ? fast_exp2(s[i] * p.scale_log2 - m_new) : 0.f;
+                    const float p1 = v1 ? fast_exp2(s[i + 1] * p.scale_log2 - m_new) : 0.f;
+                    lsum += p0 + p1;
+                    packed[i >> 1] = Elem<T>::pack2(p0, p1);
+                }
+                // 32 keys = 4 pieces of 16 B; key column cc*32 lies in half cc/2, pieces (cc&1)*4 ..
+                uint8_t *prow = p_tile + (cc >> 1) * kHalfBytes + row * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int piece = (cc & 1) * 4 + q4;
+                    *reinterpret_cast<uint4 *>(prow + ((piece ^ (row & 7)) << 4)) =
+                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                }
+            }
+            l_run = l_run * alpha + lsum;
+            fence_proxy_async_smem();        // P (and any cleared V rows) visible to the tensor core
+            tc_fence_before();               // our TMEM reads of S precede the next score MMA
+            mbar_arrive(smem_u32(&ctrl->p_full));
+
+            // ---- O = O*alpha + PV ----
+            if (!(ok = wait_or_abort(smem_u32(&ctrl->o_full), j & 1, abort_flag, p.status))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                float pv[32];
+                tmem_ld32(tmem + lane_base + 128 + cc * 32, pv);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[cc * 32 + i] = o[cc * 32 + i] * alpha + pv[i];
+            }
+            tc_fence_before();
+        }
+
+        if (ok && row_valid && row < p.tq * p.group) {
+            const float inv = 1.f / l_run;
+            T *dst = static_cast<T *>(p.out) +
+                     ((long long)(qoff + t0 + tq_idx) * p.num_q_heads + (long long)h * p.group + hg) * kD;
+#pragma unroll
+            for (int i = 0; i < kD; i += 8) {
+                uint4 w;
+                w.x = Elem<T>::pack2(o[i] * inv, o[i + 1] * inv);
+                w.y = Elem<T>::pack2(o[i + 2] * inv, o[i + 3] * inv);
+                w.z = Elem<T>::pack2(o[i + 4] * inv, o[i + 5] * inv);
+                w.w = Elem<T>::pack2(o[i + 6] * inv, o[i + 7] * inv);
+                *reinterpret_cast<uint4 *>(dst + i) = w;
+            }
+        }
+    }
+
+    // ---- teardown: everyone meets, then the allocating warp releases TMEM ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+}  // namespace
 
 extern "C" size_t npd_prefill_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int) { return 256; }
 
-extern "C" int npd_paged_prefill_attention(void *, const void *, const void *, const void *, const int32_t *,
-                                           const int32_t *, const int32_t *, const int32_t *, int64_t, float,
-                                           int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                                           int, void *, size_t, int, void *) {
-    return npd::fail(NPD_ERR_UNSUPPORTED, "npd_paged_prefill_attention: not built yet");
+extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void *k_cache, const void *v_cache,
+                                           const int32_t *block_tables, const int32_t *chunk_q_offset_host,
+                                           const int32_t *chunk_tokens_host, const int32_t *chunk_start_host,
+                                           int64_t num_chunks, float scale, int64_t num_q_heads, int64_t num_kv_heads,
+                                           int64_t head_dim, int64_t block_size, int64_t max_blocks_per_seq,
+                                           int64_t num_blocks, int64_t cache_block_stride, int64_t bt_row_stride,
+                                           int dtype, void *workspace, size_t workspace_bytes, int flags,
+                                           void *stream) {
+    (void)flags;
+    NPD_REQUIRE(dtype == NPD_DTYPE_F16 || dtype == NPD_DTYPE_BF16, NPD_ERR_UNSUPPORTED,
+                "prefill attention supports float16 and bfloat16 only (dtype code %d)", dtype);
+    NPD_REQUIRE(head_dim == kD, NPD_ERR_UNSUPPORTED, "prefill attention: head_dim %lld is not 128", (long long)head_dim);
+    NPD_REQUIRE(block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
+                "prefill attention: block_size %lld not in {16,32}", (long long)block_size);
+    NPD_REQUIRE(num_chunks >= 0 && num_q_heads > 0 && num_kv_heads > 0 && max_blocks_per_seq > 0 && num_blocks > 0,
+                NPD_ERR_INVALID_ARG, "prefill attention: non-positive dimension");
+    NPD_REQUIRE(num_q_heads % num_kv_heads == 0, NPD_ERR_INVALID_ARG,
+                "prefill attention: num_q_heads is not a multiple of num_kv_heads");
+    const int group = static_cast<int>(num_q_heads / num_kv_heads);
+    NPD_REQUIRE(group <= 128, NPD_ERR_UNSUPPORTED, "prefill attention: more than 128 q heads per kv head");
+    if (num_chunks == 0) return NPD_OK;
+    NPD_REQUIRE(out && q && k_cache && v_cache && block_tables && chunk_q_offset_host && chunk_tokens_host &&
+                    chunk_start_host,
+                NPD_ERR_INVALID_ARG, "prefill attention: NULL pointer");
+    NPD_REQUIRE(workspace != nullptr && workspace_bytes >= 256, NPD_ERR_WORKSPACE,
+                "prefill attention: workspace of at least 256 bytes needed (status word)");
+    NPD_REQUIRE(npd::aligned16(out) && npd::aligned16(q), NPD_ERR_INVALID_ARG, "prefill attention: q/out alignment");
+    NPD_REQUIRE(num_blocks < INT32_MAX && max_blocks_per_seq * block_size < INT32_MAX, NPD_ERR_INVALID_ARG,
+                "prefill attention: dimension exceeds int32");
+
+    int64_t total_tokens = 0;
+    for (int64_t i = 0; i < num_chunks; ++i) {
+        NPD_REQUIRE(chunk_tokens_host[i] >= 0 && chunk_start_host[i] >= 0 && chunk_q_offset_host[i] >= 0,
+                    NPD_ERR_INVALID_ARG, "prefill attention: negative chunk field");
+        NPD_REQUIRE((int64_t)chunk_start_host[i] + chunk_tokens_host[i] <= max_blocks_per_seq * block_size,
+                    NPD_ERR_INVALID_ARG, "prefill attention: chunk %lld reaches beyond its block table", (long long)i);
+        const int64_t end = (int64_t)chunk_q_offset_host[i] + chunk_tokens_host[i];
+        if (end > total_tokens) total_tokens = end;
+    }
+    if (total_tokens == 0) return NPD_OK;
+
+    const int tq = kRows / group;
+    CUtensorMap tq_map, tk, tv;
+    {
+        const uint64_t dims[3] = {(uint64_t)head_dim, (uint64_t)num_q_heads, (uint64_t)total_tokens};
+        const uint64_t strides[2] = {(uint64_t)head_dim * 2u, (uint64_t)num_q_heads * head_dim * 2u};
+        const uint32_t box[3] = {64u, (uint32_t)group, (uint32_t)tq};
+        const int rc = npd::encode_tiled_3d(&tq_map, q, dtype, dims, strides, box);
+        if (rc != NPD_OK) return rc;
+    }
+    int rc = npd::encode_cache_tensor_map(&tk, k_cache, dtype, head_dim, num_kv_heads * block_size, num_blocks,
+                                          cache_block_stride, 16);
+    if (rc != NPD_OK) return rc;
+    rc = npd::encode_cache_tensor_map(&tv, v_cache, dtype, head_dim, num_kv_heads * block_size, num_blocks,
+                                      cache_block_stride, 16);
+    if (rc != NPD_OK) return rc;
+
+    const size_t smem = 1024 + (size_t)kTileBytes * (2 + 2 * kStages) + sizeof(SmemCtrl) + 64;
+    auto kern = dtype == NPD_DTYPE_F16 ? paged_prefill_kernel<__half> : paged_prefill_kernel<__nv_bfloat16>;
+    NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int64_t c0 = 0; c0 < num_chunks; c0 += kMaxChunks) {
+        const int nc = static_cast<int>(num_chunks - c0 < kMaxChunks ? num_chunks - c0 : kMaxChunks);
+        PrefillParams p;
+        p.out = out;
+        p.block_tables = block_tables + c0 * bt_row_stride;
+        p.status = static_cast<int32_t *>(workspace);
+        p.scale_log2 = scale * 1.4426950408889634f;
+        p.num_chunks = nc;
+        p.num_q_heads = static_cast<int>(num_q_heads);
+        p.num_kv_heads = static_cast<int>(num_kv_heads);
+        p.group = group;
+        p.tq = tq;
+        p.block_size = static_cast<int>(block_size);
+        p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
+        p.num_blocks = static_cast<int>(num_blocks);
+        p.bt_row_stride = bt_row_stride;
+        p.tile_prefix[0] = 0;
+        for (int i = 0; i < nc; ++i) {
+            p.chunk_q_offset[i] = chunk_q_offset_host[c0 + i];
+            p.chunk_tokens[i] = chunk_tokens_host[c0 + i];
+            p.chunk_start[i] = chunk_start_host[c0 + i];
+            p.tile_prefix[i + 1] = p.tile_prefix[i] + (p.chunk_tokens[i] + tq - 1) / tq;
+        }
+        const long long grid = (long long)p.tile_prefix[nc] * num_kv_heads;
+        if (grid == 0) continue;
+        NPD_REQUIRE(grid < INT32_MAX, NPD_ERR_INVALID_ARG, "prefill attention: too many tiles");
+        kern<<<static_cast<unsigned>(grid), kThreads, smem, st>>>(p, tq_map, tk, tv);
+        NPD_CUDA_TRY(cudaGetLastError());
+    }
+    return NPD_OK;
 }
