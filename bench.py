@@ -65,51 +65,64 @@ def measured_peak_gbs():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while a timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """Samples nvidia-smi clocks and throttle reasons; keeps the samples taken inside the timed window.
+
+    nvidia-smi needs a few hundred milliseconds to start, so the sampler is started well before
+    the timed region and the samples are filtered by their own timestamps afterwards."""
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu_index), "-lms", "100"],
+                 "-i", str(self.gpu_index), "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
 
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except Exception:
             self.proc.kill()
             out = ""
-        sm, mx, reasons = [], [], set()
+        import datetime
+        rows = []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.splitlines():
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 9:
+            if len(parts) < 10:
                 continue
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[2]), float(parts[3]), float(parts[4]),
+                             [n for n, v in zip(names, parts[6:10]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        inside = [r for r in rows if self.t_begin is not None and self.t_begin - 0.05 <= r[0] <= self.t_end + 0.05]
+        use = inside if inside else rows
+        reasons = sorted({n for r in use for n in r[4]})
+        return {"sm_mhz": statistics.median(r[1] for r in use) if use else None,
+                "sm_max_mhz": max(r[2] for r in use) if use else None,
+                "power_w_max": max(r[3] for r in use) if use else None,
+                "samples": len(use), "samples_in_timed_window": len(inside), "reasons": reasons}
 
 
 # ---------------------------------------------------------------------------
@@ -177,6 +190,89 @@ def run_reference_arm(args):
     return 0
 
 
+
+# ---------------------------------------------------------------------------
+# Secondary workload: configuration 3, chunked prefill over paged K/V (tensor-core bound)
+# ---------------------------------------------------------------------------
+def measured_peak_tflops():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured (MEASURED_PEAKS.json, cuBLAS bf16 burst)"
+        except Exception:
+            pass
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+def prefill_flops(chunks, Hq, D):
+    return sum(4 * Hq * D * (c.num_tokens * c.start_position + c.num_tokens * (c.num_tokens + 1) // 2) for c in chunks)
+
+
+def build_prefill_call(mixed, chunks, dev):
+    """Packs the given chunks for one paged_prefill_attention call."""
+    max_blk = max(c.block_table.numel() for c in chunks)
+    bt = torch.zeros(len(chunks), max_blk, dtype=torch.int32, device=dev)
+    for i, c in enumerate(chunks):
+        bt[i, :c.block_table.numel()] = c.block_table
+    q = torch.cat([c.query for c in chunks]).contiguous()
+    offsets, tokens, starts, off = [], [], [], 0
+    for c in chunks:
+        offsets.append(off), tokens.append(c.num_tokens), starts.append(c.start_position)
+        off += c.num_tokens
+    return q, bt, offsets, tokens, starts
+
+
+def run_prefill_workload(args, paged_kernels, dev, timed):
+    """All 512-token chunks of configuration 3's four prompts in one call (a whole chunked prefill
+    of the prompts for one layer), and one mixed step: one chunk per prompt + the 128 decode sequences."""
+    m = workloads.make_config3(device=dev, seed=args.seed)
+    d = m.decode
+    Hq, D, B = d.num_q_heads, d.head_dim, d.block_size
+    for c in m.chunks:      # the chunks' K/V rows go into the pages first, as the caller does
+        n = c.num_tokens
+        pos = torch.arange(c.start_position, c.start_position + n, dtype=torch.int32, device=dev)
+        paged_kernels.paged_kv_store(d.k_cache, d.v_cache, c.k_new, c.v_new, c.block_table.unsqueeze(0).expand(n, -1), pos)
+    q, bt, offs, toks, starts = build_prefill_call(m, m.chunks, dev)
+    out = torch.empty_like(q)
+    fn_all = lambda: paged_kernels.paged_prefill_attention(out, q, d.k_cache, d.v_cache, bt, offs, toks, starts,
+                                                           d.scale, B, bt.size(1))
+    for _ in range(3):
+        fn_all()
+    steps = max(3, min(args.steps, 20))
+    if args.profile:
+        for _ in range(2):
+            fn_all()
+        torch.cuda.synchronize()
+        return {"profile_run": True, "flops_per_launch": prefill_flops(m.chunks, Hq, D)}
+    ms_all = timed(fn_all, steps)
+    flops_all = prefill_flops(m.chunks, Hq, D)
+    # mixed step: the last chunk of every prompt + decode batch
+    last = [c for i, c in enumerate(m.chunks) if i + 1 == len(m.chunks) or m.chunks[i + 1].start_position == 0]
+    q2, bt2, offs2, toks2, starts2 = build_prefill_call(m, last, dev)
+    out2 = torch.empty_like(q2)
+    dec_out = torch.empty_like(d.query)
+    seq_lens = d.seq_lens_after_store.contiguous()
+
+    def mixed_step():
+        paged_kernels.paged_prefill_attention(out2, q2, d.k_cache, d.v_cache, bt2, offs2, toks2, starts2, d.scale, B, bt2.size(1))
+        paged_kernels.paged_kv_store(d.k_cache, d.v_cache, d.k_new, d.v_new, d.block_tables, d.positions)
+        paged_kernels.paged_attention_forward(dec_out, d.query, d.k_cache, d.v_cache, d.block_tables, seq_lens,
+                                              d.scale, B, d.max_blocks)
+    for _ in range(3):
+        mixed_step()
+    ms_mixed = timed(mixed_step, steps)
+    ms_last = timed(lambda: paged_kernels.paged_prefill_attention(out2, q2, d.k_cache, d.v_cache, bt2, offs2, toks2,
+                                                                  starts2, d.scale, B, bt2.size(1)), steps)
+    peak, src = measured_peak_tflops()
+    tf = flops_all / (ms_all * 1e-3) / 1e12
+    return {"prompt_lens": m.prompt_lens, "chunks": len(m.chunks), "flops_all_chunks": flops_all,
+            "all_chunks_ms": round(ms_all, 4), "tflops": round(tf, 1), "peak_tflops": peak, "peak_source": src,
+            "frac_of_peak": round(tf / peak, 4),
+            "last_chunks_ms": round(ms_last, 4),
+            "last_chunks_tflops": round(prefill_flops(last, Hq, D) / (ms_last * 1e-3) / 1e12, 1),
+            "mixed_step_ms": round(ms_mixed, 4),
+            "mixed_step": "last 512-token chunk of each of 4 prompts + store + decode attention of 128 sequences"}
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -190,6 +286,30 @@ def run_gpu_arm(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     steps, warmup = args.steps, max(3, args.warmup)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    def timed(fn, n):
+        """n calls of fn between two events on the current stream; returns ms per call."""
+        replicas.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        replicas.barrier()
+        return e0.elapsed_time(e1) / n
+
+    if args.workload == "prefill":
+        res = run_prefill_workload(args, paged_kernels, dev, timed)
+        res["device_status"] = paged_kernels.check_status(dev, raise_on_error=False)
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"workload": "cfg3 chunked prefill (secondary, not the headline metric)", **res}), flush=True)
+        return 0
 
     b = workloads.make_config2(device=dev, seed=args.seed + rank, batch=args.batch)
     S, Hq, Hkv, D, B = b.query.size(0), b.num_q_heads, b.num_kv_heads, b.head_dim, b.block_size
@@ -206,19 +326,6 @@ def run_gpu_arm(args):
         paged_kernels.paged_attention_forward(out, b.query, b.k_cache, b.v_cache, b.block_tables, seq_lens,
                                               b.scale, B, max_blk)
 
-    def timed(fn, n):
-        """n calls of fn between two events on the current stream; returns ms per call."""
-        replicas.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        replicas.barrier()
-        return e0.elapsed_time(e1) / n
-
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
@@ -227,11 +334,11 @@ def run_gpu_arm(args):
             step()
         torch.cuda.synchronize()
         print(json.dumps({"profile_run": True, "steps": steps, "batch": S, "attention_bytes_per_launch": attn_bytes}))
+        if rank == 0:
+            sampler.stop()
         return 0
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler.mark_begin()
     ms_step = timed(step, steps)
     # the streaming kernel alone (merge skipped): the launch the roofline is quoted on
     ms_stream = timed(lambda: paged_kernels.paged_attention_forward(
@@ -242,16 +349,24 @@ def run_gpu_arm(args):
         b.k_cache, b.v_cache, b.k_new, b.v_new, b.block_tables, positions), steps)
 
     # ---- end to end through the public op with HOST buffers ----
-    host = {k: v.cpu().pin_memory() for k, v in dict(q=b.query, k_new=b.k_new, v_new=b.v_new,
-                                                    bt=b.block_tables, pos=positions, sl=seq_lens).items()}
-    dbuf = {k: torch.empty_like(v, device=dev) for k, v in host.items()}
+    # All of the step's host inputs live in ONE pinned staging buffer and cross PCIe in ONE copy; the
+    # device-side tensors the ops receive are views of its device twin.
+    parts = dict(q=b.query, k_new=b.k_new, v_new=b.v_new, bt=b.block_tables, pos=positions, sl=seq_lens)
+    sizes = {k: (v.numel() * v.element_size() + 255) // 256 * 256 for k, v in parts.items()}
+    h2d = sum(sizes.values())
+    stage_host = torch.empty(h2d, dtype=torch.uint8).pin_memory()
+    stage_dev = torch.empty(h2d, dtype=torch.uint8, device=dev)
+    dbuf, off = {}, 0
+    for k, v in parts.items():
+        nbytes = v.numel() * v.element_size()
+        stage_host[off:off + nbytes].copy_(v.contiguous().view(-1).view(torch.uint8).cpu())
+        dbuf[k] = stage_dev[off:off + nbytes].view(v.dtype).view(v.shape)
+        off += sizes[k]
     out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = out_host.numel() * out_host.element_size()
 
     def e2e_step():
-        for k in host:
-            dbuf[k].copy_(host[k], non_blocking=True)
+        stage_dev.copy_(stage_host, non_blocking=True)
         paged_kernels.paged_kv_store(b.k_cache, b.v_cache, dbuf["k_new"], dbuf["v_new"], dbuf["bt"], dbuf["pos"])
         paged_kernels.paged_attention_forward(out, dbuf["q"], b.k_cache, b.v_cache, dbuf["bt"], dbuf["sl"],
                                               b.scale, B, max_blk)
@@ -261,6 +376,7 @@ def run_gpu_arm(args):
     for _ in range(3):
         e2e_step()
     ms_e2e = timed(e2e_step, steps)
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
 
     status = paged_kernels.check_status(dev, raise_on_error=False)
@@ -293,6 +409,12 @@ def run_gpu_arm(args):
             del pool_k, pool_v, dst_k, dst_v
         except Exception as exc:  # noqa: BLE001
             extras["migrate_error"] = str(exc)[:200]
+        try:
+            del stage_dev, dbuf
+            torch.cuda.empty_cache()
+            extras["prefill_cfg3"] = run_prefill_workload(args, paged_kernels, dev, timed)
+        except Exception as exc:  # noqa: BLE001
+            extras["prefill_error"] = str(exc)[:200]
         # CPU baseline on a bounded sample of the same workload
         bc = workloads.DecodeBatch(**{f: (getattr(b, f).cpu() if torch.is_tensor(getattr(b, f)) else getattr(b, f))
                                       for f in b.__dataclass_fields__})
@@ -335,11 +457,13 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+                    help="decode = the headline configuration 2 (default); prefill = configuration 3's chunked prefill")
     ap.add_argument("--profile", action="store_true",
                     help="only warm up and run the timed step loop (for short ncu captures); prints no bench line")
     args = ap.parse_args()
