@@ -28,14 +28,15 @@ namespace {
 using namespace npd;
 
 constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays)
-constexpr int kRows = 128;         // UMMA M
+constexpr int kRows = 128;         // UMMA M: rows of one query tile
 constexpr int kKeys = 128;         // keys per tile (UMMA N of the score MMA)
 constexpr int kD = 128;            // head_dim
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA
 constexpr int kHalfBytes = kRows * 128;             // one 64-element half of a 128-row operand tile
-constexpr int kTileBytes = 2 * kHalfBytes;          // 32 KiB: Q, K, V or P tile
+constexpr int kTileBytes = 2 * kHalfBytes;          // 32 KiB: a Q, K or V tile
 constexpr int kStages = 2;
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; P_X aliases S_X
+constexpr float kRescaleThreshold = 8.f;   // log2 units: O is rescaled only when a row max grows by more
 constexpr long long kWaitCycles = 4000000000LL;
 
 struct PrefillParams {
@@ -45,7 +46,7 @@ struct PrefillParams {
     float scale_log2;
     int num_chunks;
     int num_q_heads, num_kv_heads, group;
-    int tq;                 // query tokens per tile = 128 / group (floor)
+    int tq;                 // query tokens per 128-row tile = 128 / group (floor)
     int block_size;
     int max_blocks_per_seq;
     int num_blocks;
@@ -53,7 +54,7 @@ struct PrefillParams {
     int chunk_q_offset[kMaxChunks];
     int chunk_tokens[kMaxChunks];
     int chunk_start[kMaxChunks];
-    int tile_prefix[kMaxChunks + 1];   // exclusive prefix of ceil(chunk_tokens / tq)
+    int cta_prefix[kMaxChunks + 1];   // exclusive prefix of ceil(chunk_tokens / (2*tq)): CTAs per kv head
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------
@@ -72,13 +73,24 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]   (A: 128 lanes x K/2 columns of packed 16-bit pairs, K-major)
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base + i).
@@ -95,7 +107,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    const uint32_t *r = reinterpret_cast<const uint32_t *>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptors (version 1, 128-byte swizzle, 8-row groups 1024 B apart).
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
@@ -129,11 +162,11 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 
 struct alignas(8) SmemCtrl {
     uint64_t q_full;
-    uint64_t kv_full[kStages];
-    uint64_t kv_empty[kStages];
-    uint64_t s_full;
-    uint64_t p_full;
-    uint64_t o_full;
+    uint64_t k_full[kStages], k_empty[kStages];
+    uint64_t v_full[kStages], v_empty[kStages];
+    uint64_t s_full[2];     // score tile of query tile X is in TMEM
+    uint64_t p_full[2];     // probabilities of query tile X are in TMEM (128 arrivals)
+    uint64_t pv_done[2];    // the PV MMAs of query tile X for the current key tile have completed
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -146,42 +179,51 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
     uint8_t *sbase = smem_raw + pad;
-    uint8_t *q_tile = sbase;                                   // 32 KiB
-    uint8_t *kv_ring = sbase + kTileBytes;                     // kStages x (K 32 KiB + V 32 KiB)
-    uint8_t *p_tile = kv_ring + kStages * 2 * kTileBytes;      // 32 KiB
-    SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(p_tile + kTileBytes);
+    uint8_t *q_tiles = sbase;                                   // 2 x 32 KiB (query tiles A and B)
+    uint8_t *k_ring = q_tiles + 2 * kTileBytes;                 // kStages x 32 KiB
+    uint8_t *v_ring = k_ring + kStages * kTileBytes;            // kStages x 32 KiB
+    SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStages * kTileBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // ---- which tile is mine ----
+    // ---- which pair of query tiles is mine ----
     const int h = blockIdx.x % p.num_kv_heads;
-    const int tile_rank = blockIdx.x / p.num_kv_heads;
+    const int rank = blockIdx.x / p.num_kv_heads;
     int c = 0;
-    while (c + 1 < p.num_chunks && p.tile_prefix[c + 1] <= tile_rank) ++c;
-    const int tiles_in_chunk = p.tile_prefix[c + 1] - p.tile_prefix[c];
+    while (c + 1 < p.num_chunks && p.cta_prefix[c + 1] <= rank) ++c;
+    const int ctas_in_chunk = p.cta_prefix[c + 1] - p.cta_prefix[c];
     // later tiles of a chunk see more keys: hand them out first
-    const int m_tile = tiles_in_chunk - 1 - (tile_rank - p.tile_prefix[c]);
+    const int pair = ctas_in_chunk - 1 - (rank - p.cta_prefix[c]);
     const int n_tok = p.chunk_tokens[c], start = p.chunk_start[c], qoff = p.chunk_q_offset[c];
-    const int t0 = m_tile * p.tq;
-    const int tq_valid = min(p.tq, n_tok - t0);
-    const int kv_end = start + t0 + tq_valid;                 // keys [0, kv_end) are visible to the tile
-    const int num_kv_tiles = (kv_end + kKeys - 1) / kKeys;
     const int ctx_end = start + n_tok;                        // keys written so far for this sequence
     const int npages = (ctx_end + p.block_size - 1) / p.block_size;
+    int tok0[2], tq_valid[2], ntiles[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        tok0[x] = (2 * pair + x) * p.tq;
+        tq_valid[x] = max(0, min(p.tq, n_tok - tok0[x]));
+        // keys [0, start + tok0 + tq_valid) are visible to the tile
+        ntiles[x] = tq_valid[x] > 0 ? (start + tok0[x] + tq_valid[x] + kKeys - 1) / kKeys : 0;
+    }
+    const int n_kv = max(ntiles[0], ntiles[1]);
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&ctrl->q_full), 1);
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->kv_empty[i]), 1);
+            mbar_init(smem_u32(&ctrl->k_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->k_empty[i]), 1);
+            mbar_init(smem_u32(&ctrl->v_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->v_empty[i]), 1);
         }
-        mbar_init(smem_u32(&ctrl->s_full), 1);
-        mbar_init(smem_u32(&ctrl->p_full), 128);
-        mbar_init(smem_u32(&ctrl->o_full), 1);
+        for (int x = 0; x < 2; ++x) {
+            mbar_init(smem_u32(&ctrl->s_full[x]), 1);
+            mbar_init(smem_u32(&ctrl->p_full[x]), 128);
+            mbar_init(smem_u32(&ctrl->pv_done[x]), 1);
+        }
         ctrl->abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
         tmem_relinquish();
     }
@@ -191,194 +233,261 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     const uint32_t tmem = ctrl->tmem_base;
     volatile int *abort_flag = &ctrl->abort_flag;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // =========================== TMA producer ===========================
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
-            // Q tile: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch
+            // Query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch
             const uint32_t qbar = smem_u32(&ctrl->q_full);
-            mbar_expect_tx(qbar, static_cast<uint32_t>(2 * p.tq * p.group * 128));
-            for (int hf = 0; hf < 2; ++hf)
-                tma_load_3d(smem_u32(q_tile + hf * kHalfBytes), &tm_q, qbar, hf * 64, h * p.group, qoff + t0);
-
+            const int nq = (tq_valid[0] > 0 ? 1 : 0) + (tq_valid[1] > 0 ? 1 : 0);
+            mbar_expect_tx(qbar, static_cast<uint32_t>(nq * 2 * p.tq * p.group * 128));
+            for (int x = 0; x < 2; ++x) {
+                if (tq_valid[x] <= 0) continue;
+                for (int hf = 0; hf < 2; ++hf)
+                    tma_load_3d(smem_u32(q_tiles + x * kTileBytes + hf * kHalfBytes), &tm_q, qbar, hf * 64,
+                                h * p.group, qoff + tok0[x]);
+            }
             const int32_t *table = p.block_tables + (long long)c * p.bt_row_stride;
-            for (int j = 0; j < num_kv_tiles; ++j) {
+            for (int j = 0; j < n_kv; ++j) {
                 const int stage = j % kStages;
-                if (j >= kStages) {
-                    if (!wait_or_abort(smem_u32(&ctrl->kv_empty[stage]), ((j / kStages) - 1) & 1, abort_flag, p.status))
-                        break;
-                }
-                uint8_t *k_tile = kv_ring + (size_t)stage * 2 * kTileBytes;
-                uint8_t *v_tile = k_tile + kTileBytes;
-                const uint32_t bar = smem_u32(&ctrl->kv_full[stage]);
+                const uint32_t par = ((j / kStages) - 1) & 1;
                 const int key0 = j * kKeys;
-                // 16-key row groups that hold at least one written key; the rest is never loaded
+                // 16-key row groups holding at least one written key; the rest is never loaded
                 int ngroups = 0;
-                for (int gidx = 0; gidx < kKeys / 16; ++gidx) ngroups += (key0 + gidx * 16 < ctx_end) ? 1 : 0;
-                mbar_expect_tx(bar, static_cast<uint32_t>(ngroups * 4 * 16 * 128));
-                for (int gidx = 0; gidx < ngroups; ++gidx) {
-                    const int key = key0 + gidx * 16;
-                    const int page = key / p.block_size;
-                    const int sub = (key % p.block_size) / 16;
-                    int id = page < npages ? __ldg(table + page) : -1;
-                    if (id < 0 || id >= p.num_blocks) {
+                for (int gi = 0; gi < kKeys / 16; ++gi) ngroups += (key0 + gi * 16 < ctx_end) ? 1 : 0;
+                int ids[kKeys / 16];
+#pragma unroll
+                for (int gi = 0; gi < kKeys / 16; ++gi) {
+                    const int page = (key0 + gi * 16) / p.block_size;
+                    int id = (gi < ngroups && page < npages) ? __ldg(table + page) : 0;
+                    if (gi < ngroups && (id < 0 || id >= p.num_blocks)) {
                         atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
                         id = p.num_blocks;            // out of bounds for the tensor map: zero fill
                     }
-                    const int row = h * p.block_size + sub * 16;
-                    for (int hf = 0; hf < 2; ++hf) {
-                        const uint32_t off = static_cast<uint32_t>(hf * kHalfBytes + gidx * 16 * 128);
-                        tma_load_3d(smem_u32(k_tile) + off, &tm_k, bar, hf * 64, row, id);
-                        tma_load_3d(smem_u32(v_tile) + off, &tm_v, bar, hf * 64, row, id);
+                    ids[gi] = id;
+                }
+                const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
+                // ---- K tile ----
+                if (j >= kStages && !wait_or_abort(smem_u32(&ctrl->k_empty[stage]), par, abort_flag, p.status)) break;
+                {
+                    const uint32_t bar = smem_u32(&ctrl->k_full[stage]);
+                    const uint32_t dst = smem_u32(k_ring + (size_t)stage * kTileBytes);
+                    mbar_expect_tx(bar, bytes);
+#pragma unroll
+                    for (int gi = 0; gi < kKeys / 16; ++gi) {
+                        if (gi >= ngroups) break;
+                        const int row = h * p.block_size + ((key0 + gi * 16) % p.block_size);
+                        tma_load_3d(dst + gi * 2048, &tm_k, bar, 0, row, ids[gi]);
+                        tma_load_3d(dst + kHalfBytes + gi * 2048, &tm_k, bar, 64, row, ids[gi]);
+                    }
+                }
+                // ---- V tile ----
+                if (j >= kStages && !wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status)) break;
+                {
+                    const uint32_t bar = smem_u32(&ctrl->v_full[stage]);
+                    const uint32_t dst = smem_u32(v_ring + (size_t)stage * kTileBytes);
+                    mbar_expect_tx(bar, bytes);
+#pragma unroll
+                    for (int gi = 0; gi < kKeys / 16; ++gi) {
+                        if (gi >= ngroups) break;
+                        const int row = h * p.block_size + ((key0 + gi * 16) % p.block_size);
+                        tma_load_3d(dst + gi * 2048, &tm_v, bar, 0, row, ids[gi]);
+                        tma_load_3d(dst + kHalfBytes + gi * 2048, &tm_v, bar, 64, row, ids[gi]);
                     }
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
             constexpr uint32_t fmt = Elem<T>::kDtype == NPD_DTYPE_BF16 ? 1u : 0u;
             constexpr uint32_t idesc_s = instr_desc(fmt, 0u, kRows, kKeys);
             constexpr uint32_t idesc_pv = instr_desc(fmt, 1u, kRows, kD);
-            const uint32_t q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
-            const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+            const uint32_t q_addr = smem_u32(q_tiles);
             bool ok = wait_or_abort(smem_u32(&ctrl->q_full), 0, abort_flag, p.status);
-            for (int j = 0; ok && j < num_kv_tiles; ++j) {
-                const int stage = j % kStages;
-                const uint32_t k_addr = smem_u32(kv_ring + (size_t)stage * 2 * kTileBytes);
-                const uint32_t v_addr = k_addr + kTileBytes;
-                if (!(ok = wait_or_abort(smem_u32(&ctrl->kv_full[stage]), (j / kStages) & 1, abort_flag, p.status))) break;
-                tc_fence_after();
-                // ---- S = Q . K^T : 8 k-steps of 16 elements; a step advances 32 B inside the swizzle atom
+
+            // S_X(j) = Q_X . K(j)^T : 8 k-steps of 16 elements; a step advances 32 B inside the swizzle atom
+            auto issue_s = [&](int x, int j) {
+                const uint32_t k_addr = smem_u32(k_ring + (size_t)(j % kStages) * kTileBytes);
+                const uint32_t qa = q_addr + x * kTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    tc_mma_f16(tmem_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
+                    tc_mma_ss(tmem + x * 128, desc_k_major(qa + off), desc_k_major(k_addr + off), idesc_s,
+                              ks > 0 ? 1u : 0u);
                 }
-                tc_commit(smem_u32(&ctrl->s_full));
-                // ---- wait for P (and for S to be drained), then PV = P . V
-                if (!(ok = wait_or_abort(smem_u32(&ctrl->p_full), j & 1, abort_flag, p.status))) break;
-                tc_fence_after();
+                tc_commit(smem_u32(&ctrl->s_full[x]));
+            };
+            // O_X (+)= P_X(j) . V(j) : P from TMEM (packed pairs, 8 columns per 16 keys), V MN-major from smem
+            auto issue_pv = [&](int x, int j) {
+                const uint32_t v_addr = smem_u32(v_ring + (size_t)(j % kStages) * kTileBytes);
 #pragma unroll
-                for (int ks = 0; ks < kKeys / 16; ++ks) {
-                    const uint32_t a_off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;   // P is K-major over keys
-                    const uint32_t b_off = ks * 16 * 128;                            // 16 keys = two 8-row groups
-                    tc_mma_f16(tmem_o, desc_k_major(p_addr + a_off), desc_mn_major(v_addr + b_off, kHalfBytes),
-                               idesc_pv, ks > 0 ? 1u : 0u);
+                for (int ks = 0; ks < kKeys / 16; ++ks)
+                    tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8,
+                              desc_mn_major(v_addr + ks * 2048, kHalfBytes), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(smem_u32(&ctrl->pv_done[x]));
+            };
+
+            if (ok && n_kv > 0) {
+                ok = wait_or_abort(smem_u32(&ctrl->k_full[0]), 0, abort_flag, p.status);
+                if (ok) {
+                    tc_fence_after();
+                    if (ntiles[0] > 0) issue_s(0, 0);
+                    if (ntiles[1] > 0) issue_s(1, 0);
+                    tc_commit(smem_u32(&ctrl->k_empty[0]));
                 }
-                tc_commit(smem_u32(&ctrl->kv_empty[stage]));   // K and V of this stage are free again
-                tc_commit(smem_u32(&ctrl->o_full));            // PV is in TMEM
+            }
+            for (int j = 0; ok && j < n_kv; ++j) {
+                const int stage = j % kStages;
+                const uint32_t par = (j / kStages) & 1;
+                const bool more = j + 1 < n_kv;
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), par, abort_flag, p.status))) break;
+                if (more && !(ok = wait_or_abort(smem_u32(&ctrl->k_full[(j + 1) % kStages]), ((j + 1) / kStages) & 1,
+                                                 abort_flag, p.status)))
+                    break;
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    if (j < ntiles[x]) {
+                        if (!(ok = wait_or_abort(smem_u32(&ctrl->p_full[x]), j & 1, abort_flag, p.status))) break;
+                        tc_fence_after();
+                        issue_pv(x, j);
+                        if (j + 1 < ntiles[x]) issue_s(x, j + 1);   // P_X(j) is consumed before S_X(j+1) lands (in order)
+                    }
+                }
+                if (!ok) break;
+                tc_commit(smem_u32(&ctrl->v_empty[stage]));
+                if (more) tc_commit(smem_u32(&ctrl->k_empty[(j + 1) % kStages]));
             }
         }
     } else {
-        // =========================== softmax + accumulate (warps 0-3) ===========================
-        const int row = warp * 32 + lane;                       // == TMEM lane
-        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        // =========================== softmax + correction + epilogue (warps 0-7) ===========================
+        const int x = warp >> 2;                                 // query tile A or B
+        const int wq = warp & 3;                                 // TMEM lane quarter this warp may touch
+        const int row = wq * 32 + lane;                          // == TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+        const uint32_t t_s = tmem + x * 128 + lane_base;         // scores, later the packed probabilities
+        const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
-        const bool row_valid = tq_idx < tq_valid;
-        const int pos = start + t0 + tq_idx;                    // last visible key of this row
-        float o[kD];
-#pragma unroll
-        for (int i = 0; i < kD; ++i) o[i] = 0.f;
+        const int pos = start + tok0[x] + tq_idx;                // last visible key of this row
+        const int my_tiles = ntiles[x];
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
 
-        for (int j = 0; ok && j < num_kv_tiles; ++j) {
+        for (int j = 0; ok && j < my_tiles; ++j) {
             const int stage = j % kStages;
             const int key0 = j * kKeys;
-            // V rows at or past ctx_end were never written (or never loaded): clear them so that
-            // P = 0 there cannot meet a NaN.  Needs the tile to have landed first.
+            // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
+            // there cannot meet a NaN.  Both softmax groups do it (idempotent) before releasing their P.
             if (key0 + kKeys > ctx_end) {
-                if (!(ok = wait_or_abort(smem_u32(&ctrl->kv_full[stage]), (j / kStages) & 1, abort_flag, p.status))) break;
-                uint8_t *v_tile = kv_ring + (size_t)stage * 2 * kTileBytes + kTileBytes;
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (j / kStages) & 1, abort_flag, p.status))) break;
+                uint8_t *v_tile = v_ring + (size_t)stage * kTileBytes;
                 const int first = max(ctx_end - key0, 0);
                 const int cnt = (kKeys - first) * 16;            // 16-byte pieces: 2 halves x 8 per row
-                for (int idx = threadIdx.x; idx < cnt; idx += 128) {
+                for (int idx = threadIdx.x & 127; idx < cnt; idx += 128) {
                     const int r = first + idx / 16, piece = idx % 16;
                     *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kHalfBytes + r * 128 + ((piece & 7) << 4)) =
                         make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async_smem();
             }
-            if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full), j & 1, abort_flag, p.status))) break;
+            if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x]), j & 1, abort_flag, p.status))) break;
             tc_fence_after();
 
-            const bool need_mask = key0 + kKeys - 1 > start + t0;   // tile reaches past the first row's diagonal
+            const bool need_mask = key0 + kKeys - 1 > start + tok0[x];   // tile reaches past the first row's diagonal
             // ---- pass 1: row maximum ----
             float mx = -INFINITY;
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
                 float s[32];
-                tmem_ld32(tmem + lane_base + cc * 32, s);
+                tmem_ld32(t_s + cc * 32, s);
                 tmem_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const float x = (!need_mask || key0 + cc * 32 + i <= pos) ? s[i] : -INFINITY;
-                    mx = fmaxf(mx, x);
+                    const float v = (!need_mask || key0 + cc * 32 + i <= pos) ? s[i] : -INFINITY;
+                    mx = fmaxf(mx, v);
                 }
             }
-            const float m_new = fmaxf(m_run, mx * p.scale_log2);
-            const float alpha = fast_exp2(m_run - m_new);        // 0 on the first tile (m_run = -inf)
-            m_run = m_new;
-            // ---- pass 2: probabilities -> shared memory (K-major, 128-byte swizzle) ----
+            const float m_new = mx * p.scale_log2;
+            if (j == 0) {
+                m_run = m_new;                                  // key 0 is visible to every row: finite
+            } else {
+                // Lazy correction: O (in TMEM) and l are rescaled only when some row's maximum grew by more
+                // than 2^8; otherwise the stale maximum keeps every probability below 256, exactly cancelled
+                // by the final division.
+                const bool grow = m_new > m_run + kRescaleThreshold;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
+                    if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (j - 1) & 1, abort_flag, p.status))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        float o[32];
+                        tmem_ld32(t_o + cc * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                        tmem_st32(t_o + cc * 32, o);
+                    }
+                    tmem_wait_st();
+                    if (grow) {
+                        l_run *= alpha;
+                        m_run = m_new;
+                    }
+                }
+            }
+            // ---- pass 2: probabilities, packed in pairs, over the score columns already read ----
             float lsum = 0.f;
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
                 float s[32];
-                tmem_ld32(tmem + lane_base + cc * 32, s);
+                tmem_ld32(t_s + cc * 32, s);
                 tmem_wait_ld();
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const bool v0 = !need_mask || key0 + cc * 32 + i <= pos;
                     const bool v1 = !need_mask || key0 + cc * 32 + i + 1 <= pos;
-                    const float p0 = v0 ? fast_exp2(s[i] * p.scale_log2 - m_new) : 0.f;
-                    const float p1 = v1 ? fast_exp2(s[i + 1] * p.scale_log2 - m_new) : 0.f;
+                    const float p0 = v0 ? fast_exp2(s[i] * p.scale_log2 - m_run) : 0.f;
+                    const float p1 = v1 ? fast_exp2(s[i + 1] * p.scale_log2 - m_run) : 0.f;
                     lsum += p0 + p1;
                     packed[i >> 1] = Elem<T>::pack2(p0, p1);
                 }
-                // 32 keys = 4 pieces of 16 B; key column cc*32 lies in half cc/2, pieces (cc&1)*4 ..
-                uint8_t *prow = p_tile + (cc >> 1) * kHalfBytes + row * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int piece = (cc & 1) * 4 + q4;
-                    *reinterpret_cast<uint4 *>(prow + ((piece ^ (row & 7)) << 4)) =
-                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-                }
+                tmem_st16(t_s + cc * 16, packed);
             }
-            l_run = l_run * alpha + lsum;
-            fence_proxy_async_smem();        // P (and any cleared V rows) visible to the tensor core
-            tc_fence_before();               // our TMEM reads of S precede the next score MMA
-            mbar_arrive(smem_u32(&ctrl->p_full));
-
-            // ---- O = O*alpha + PV ----
-            if (!(ok = wait_or_abort(smem_u32(&ctrl->o_full), j & 1, abort_flag, p.status))) break;
-            tc_fence_after();
-#pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                float pv[32];
-                tmem_ld32(tmem + lane_base + 128 + cc * 32, pv);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[cc * 32 + i] = o[cc * 32 + i] * alpha + pv[i];
-            }
-            tc_fence_before();
+            l_run += lsum;
+            tmem_wait_st();
+            tc_fence_before();               // P is in TMEM, S has been read: the MMA warp may go on
+            mbar_arrive(smem_u32(&ctrl->p_full[x]));
         }
 
-        if (ok && row_valid && row < p.tq * p.group) {
-            const float inv = 1.f / l_run;
-            T *dst = static_cast<T *>(p.out) +
-                     ((long long)(qoff + t0 + tq_idx) * p.num_q_heads + (long long)h * p.group + hg) * kD;
+        // ---- epilogue: O / l -> out ----
+        if (ok && my_tiles > 0) {
+            ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (my_tiles - 1) & 1, abort_flag, p.status);
+            if (ok) {
+                tc_fence_after();
+                const bool store = tq_idx < tq_valid[x] && row < p.tq * p.group;
+                const float inv = 1.f / l_run;
+                T *dst = static_cast<T *>(p.out) +
+                         ((long long)(qoff + tok0[x] + tq_idx) * p.num_q_heads + (long long)h * p.group + hg) * kD;
 #pragma unroll
-            for (int i = 0; i < kD; i += 8) {
-                uint4 w;
-                w.x = Elem<T>::pack2(o[i] * inv, o[i + 1] * inv);
-                w.y = Elem<T>::pack2(o[i + 2] * inv, o[i + 3] * inv);
-                w.z = Elem<T>::pack2(o[i + 4] * inv, o[i + 5] * inv);
-                w.w = Elem<T>::pack2(o[i + 6] * inv, o[i + 7] * inv);
-                *reinterpret_cast<uint4 *>(dst + i) = w;
+                for (int cc = 0; cc < 4; ++cc) {
+                    float o[32];
+                    tmem_ld32(t_o + cc * 32, o);
+                    tmem_wait_ld();
+                    if (store) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w;
+                            w.x = Elem<T>::pack2(o[i] * inv, o[i + 1] * inv);
+                            w.y = Elem<T>::pack2(o[i + 2] * inv, o[i + 3] * inv);
+                            w.z = Elem<T>::pack2(o[i + 4] * inv, o[i + 5] * inv);
+                            w.w = Elem<T>::pack2(o[i + 6] * inv, o[i + 7] * inv);
+                            *reinterpret_cast<uint4 *>(dst + cc * 32 + i) = w;
+                        }
+                    }
+                }
             }
         }
     }
@@ -386,7 +495,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     // ---- teardown: everyone meets, then the allocating warp releases TMEM ----
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
@@ -453,7 +562,7 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                                       cache_block_stride, 16);
     if (rc != NPD_OK) return rc;
 
-    const size_t smem = 1024 + (size_t)kTileBytes * (2 + 2 * kStages) + sizeof(SmemCtrl) + 64;
+    const size_t smem = 1024 + (size_t)kTileBytes * (2 + 2 * kStages) + sizeof(SmemCtrl) + 64;   // 2 Q + K ring + V ring
     auto kern = dtype == NPD_DTYPE_F16 ? paged_prefill_kernel<__half> : paged_prefill_kernel<__nv_bfloat16>;
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
@@ -474,14 +583,14 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
         p.num_blocks = static_cast<int>(num_blocks);
         p.bt_row_stride = bt_row_stride;
-        p.tile_prefix[0] = 0;
+        p.cta_prefix[0] = 0;
         for (int i = 0; i < nc; ++i) {
             p.chunk_q_offset[i] = chunk_q_offset_host[c0 + i];
             p.chunk_tokens[i] = chunk_tokens_host[c0 + i];
             p.chunk_start[i] = chunk_start_host[c0 + i];
-            p.tile_prefix[i + 1] = p.tile_prefix[i] + (p.chunk_tokens[i] + tq - 1) / tq;
+            p.cta_prefix[i + 1] = p.cta_prefix[i] + (p.chunk_tokens[i] + 2 * tq - 1) / (2 * tq);
         }
-        const long long grid = (long long)p.tile_prefix[nc] * num_kv_heads;
+        const long long grid = (long long)p.cta_prefix[nc] * num_kv_heads;
         if (grid == 0) continue;
         NPD_REQUIRE(grid < INT32_MAX, NPD_ERR_INVALID_ARG, "prefill attention: too many tiles");
         kern<<<static_cast<unsigned>(grid), kThreads, smem, st>>>(p, tq_map, tk, tv);
