@@ -129,6 +129,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 
 // Shared-memory matrix descriptors (version 1, 128-byte swizzle, 8-row groups 1024 B apart).
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
@@ -395,21 +400,28 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x]), j & 1, abort_flag, p.status))) break;
             tc_fence_after();
 
-            const bool need_mask = key0 + kKeys - 1 > start + tok0[x];   // tile reaches past the first row's diagonal
-            // ---- pass 1: row maximum ----
-            float mx = -INFINITY;
+            // The whole score row (128 fp32) stays in registers from here to the packed store: one TMEM read.
+            float sc[4][32];
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                float s[32];
-                tmem_ld32(t_s + cc * 32, s);
-                tmem_wait_ld();
+            for (int cc = 0; cc < 4; ++cc) tmem_ld32(t_s + cc * 32, sc[cc]);
+            tmem_wait_ld();
+            if (key0 + kKeys - 1 > start + tok0[x]) {   // only tiles that reach past the first row's diagonal
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float v = (!need_mask || key0 + cc * 32 + i <= pos) ? s[i] : -INFINITY;
-                    mx = fmaxf(mx, v);
-                }
+                for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + cc * 32 + i > pos) sc[cc][i] = -INFINITY;
             }
-            const float m_new = mx * p.scale_log2;
+            // ---- row maximum (three-input max) ----
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    mx0 = fmax3(mx0, sc[cc][i], sc[cc][i + 1]);
+                    mx1 = fmax3(mx1, sc[cc][i + 2], sc[cc][i + 3]);
+                }
+            const float m_new = fmaxf(mx0, mx1) * p.scale_log2;
             if (j == 0) {
                 m_run = m_new;                                  // key 0 is visible to every row: finite
             } else {
@@ -421,7 +433,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
                     if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (j - 1) & 1, abort_flag, p.status))) break;
                     tc_fence_after();
-#pragma unroll
+#pragma unroll 1
                     for (int cc = 0; cc < 4; ++cc) {
                         float o[32];
                         tmem_ld32(t_o + cc * 32, o);
@@ -437,25 +449,23 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     }
                 }
             }
-            // ---- pass 2: probabilities, packed in pairs, over the score columns already read ----
-            float lsum = 0.f;
+            // ---- probabilities in place (masked scores are -inf -> 0), packed in pairs over the score columns ----
+            float lsum0 = 0.f, lsum1 = 0.f;
+            const float neg_m = -m_run;
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
-                float s[32];
-                tmem_ld32(t_s + cc * 32, s);
-                tmem_wait_ld();
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const bool v0 = !need_mask || key0 + cc * 32 + i <= pos;
-                    const bool v1 = !need_mask || key0 + cc * 32 + i + 1 <= pos;
-                    const float p0 = v0 ? fast_exp2(s[i] * p.scale_log2 - m_run) : 0.f;
-                    const float p1 = v1 ? fast_exp2(s[i + 1] * p.scale_log2 - m_run) : 0.f;
-                    lsum += p0 + p1;
+                    const float p0 = fast_exp2(fmaf(sc[cc][i], p.scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(sc[cc][i + 1], p.scale_log2, neg_m));
+                    lsum0 += p0;
+                    lsum1 += p1;
                     packed[i >> 1] = Elem<T>::pack2(p0, p1);
                 }
                 tmem_st16(t_s + cc * 16, packed);
             }
+            const float lsum = lsum0 + lsum1;
             l_run += lsum;
             tmem_wait_st();
             tc_fence_before();               // P is in TMEM, S has been read: the MMA warp may go on
