@@ -31,7 +31,7 @@ constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
 constexpr int kKeys = 128;         // keys per tile (UMMA N of the score MMA)
 constexpr int kD = 128;            // head_dim
-constexpr int kThreads = 320;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA
+constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA, 10-11 idle (register donors)
 constexpr int kHalfBytes = kRows * 128;             // one 64-element half of a 128-row operand tile
 constexpr int kTileBytes = 2 * kHalfBytes;          // 32 KiB: a Q, K or V tile
 constexpr int kStages = 2;
@@ -55,6 +55,9 @@ struct PrefillParams {
     int chunk_tokens[kMaxChunks];
     int chunk_start[kMaxChunks];
     int cta_prefix[kMaxChunks + 1];   // exclusive prefix of ceil(chunk_tokens / (2*tq)): CTAs per kv head
+#ifdef NPD_PREFILL_TRACE
+    long long *trace;
+#endif
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------
@@ -165,6 +168,26 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     return true;
 }
 
+// Optional phase tracing for performance work (compiled out unless NPD_PREFILL_TRACE is defined):
+// the CTA with blockIdx.x == 0 appends (tag, key tile, clock) triples to the workspace after its header.
+#ifdef NPD_PREFILL_TRACE
+#define NPD_TRACE(role, tag, j)                                                                   \
+    do {                                                                                          \
+        if (blockIdx.x == NPD_PREFILL_TRACE && p.trace) {                                         \
+            long long *t_ = p.trace + (role) * 4096;                                              \
+            const int n_ = static_cast<int>(t_[0]);                                               \
+            if (n_ < 1300) {                                                                      \
+                t_[1 + 3 * n_] = (tag);                                                           \
+                t_[2 + 3 * n_] = (j);                                                             \
+                t_[3 + 3 * n_] = clock64();                                                       \
+                t_[0] = n_ + 1;                                                                   \
+            }                                                                                     \
+        }                                                                                         \
+    } while (0)
+#else
+#define NPD_TRACE(role, tag, j) do { } while (0)
+#endif
+
 struct alignas(8) SmemCtrl {
     uint64_t q_full;
     uint64_t k_full[kStages], k_empty[kStages];
@@ -201,7 +224,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     const int pair = ctas_in_chunk - 1 - (rank - p.cta_prefix[c]);
     const int n_tok = p.chunk_tokens[c], start = p.chunk_start[c], qoff = p.chunk_q_offset[c];
     const int ctx_end = start + n_tok;                        // keys written so far for this sequence
-    const int npages = (ctx_end + p.block_size - 1) / p.block_size;
     int tok0[2], tq_valid[2], ntiles[2];
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
@@ -238,8 +260,14 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     const uint32_t tmem = ctrl->tmem_base;
     volatile int *abort_flag = &ctrl->abort_flag;
 
+    // Register re-allocation between warpgroups (first statement of every role): the two softmax groups
+    // keep a whole 128-wide score row in registers, the third group (TMA, MMA, two idle warps) needs few.
     if (warp == 8) {
-        // =========================== TMA producer ===========================
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        // =========================== TMA producer (whole warp issues) ===========================
+        // A K or V tile is 16 boxes of 2 KiB (8 groups of 16 keys x 2 halves of 64 elements).  Lanes
+        // 0-15 issue the K boxes and lanes 16-31 the V boxes, each lane looking up its own block id one
+        // tile ahead, so neither the table reads nor the serial issue of 32 copies sit on the critical path.
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
@@ -254,57 +282,61 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     tma_load_3d(smem_u32(q_tiles + x * kTileBytes + hf * kHalfBytes), &tm_q, qbar, hf * 64,
                                 h * p.group, qoff + tok0[x]);
             }
-            const int32_t *table = p.block_tables + (long long)c * p.bt_row_stride;
-            for (int j = 0; j < n_kv; ++j) {
-                const int stage = j % kStages;
-                const uint32_t par = ((j / kStages) - 1) & 1;
-                const int key0 = j * kKeys;
-                // 16-key row groups holding at least one written key; the rest is never loaded
-                int ngroups = 0;
-                for (int gi = 0; gi < kKeys / 16; ++gi) ngroups += (key0 + gi * 16 < ctx_end) ? 1 : 0;
-                int ids[kKeys / 16];
-#pragma unroll
-                for (int gi = 0; gi < kKeys / 16; ++gi) {
-                    const int page = (key0 + gi * 16) / p.block_size;
-                    int id = (gi < ngroups && page < npages) ? __ldg(table + page) : 0;
-                    if (gi < ngroups && (id < 0 || id >= p.num_blocks)) {
-                        atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
-                        id = p.num_blocks;            // out of bounds for the tensor map: zero fill
-                    }
-                    ids[gi] = id;
-                }
-                const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
-                // ---- K tile ----
-                if (j >= kStages && !wait_or_abort(smem_u32(&ctrl->k_empty[stage]), par, abort_flag, p.status)) break;
-                {
-                    const uint32_t bar = smem_u32(&ctrl->k_full[stage]);
-                    const uint32_t dst = smem_u32(k_ring + (size_t)stage * kTileBytes);
-                    mbar_expect_tx(bar, bytes);
-#pragma unroll
-                    for (int gi = 0; gi < kKeys / 16; ++gi) {
-                        if (gi >= ngroups) break;
-                        const int row = h * p.block_size + ((key0 + gi * 16) % p.block_size);
-                        tma_load_3d(dst + gi * 2048, &tm_k, bar, 0, row, ids[gi]);
-                        tma_load_3d(dst + kHalfBytes + gi * 2048, &tm_k, bar, 64, row, ids[gi]);
-                    }
-                }
-                // ---- V tile ----
-                if (j >= kStages && !wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status)) break;
-                {
-                    const uint32_t bar = smem_u32(&ctrl->v_full[stage]);
-                    const uint32_t dst = smem_u32(v_ring + (size_t)stage * kTileBytes);
-                    mbar_expect_tx(bar, bytes);
-#pragma unroll
-                    for (int gi = 0; gi < kKeys / 16; ++gi) {
-                        if (gi >= ngroups) break;
-                        const int row = h * p.block_size + ((key0 + gi * 16) % p.block_size);
-                        tma_load_3d(dst + gi * 2048, &tm_v, bar, 0, row, ids[gi]);
-                        tma_load_3d(dst + kHalfBytes + gi * 2048, &tm_v, bar, 64, row, ids[gi]);
-                    }
+        }
+        const int32_t *table = p.block_tables + (long long)c * p.bt_row_stride;
+        const int is_v = lane >> 4, gi = (lane >> 1) & 7, hf = lane & 1;
+        const CUtensorMap *tm = is_v ? &tm_v : &tm_k;
+        auto lookup = [&](int j) {
+            const int key = j * kKeys + gi * 16;
+            int id = 0;
+            if (j < n_kv && key < ctx_end) {
+                id = __ldg(table + key / p.block_size);
+                if (id < 0 || id >= p.num_blocks) {
+                    atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
+                    id = p.num_blocks;                // out of bounds for the tensor map: zero fill
                 }
             }
+            return id;
+        };
+        int id_next = lookup(0);
+        bool ok = true;
+        for (int j = 0; j < n_kv; ++j) {
+            const int stage = j % kStages;
+            const uint32_t par = ((j / kStages) - 1) & 1;
+            const int key0 = j * kKeys;
+            const int id = id_next;
+            id_next = lookup(j + 1);
+            // 16-key row groups holding at least one written key; the rest is never loaded
+            int ngroups = 0;
+            for (int g2 = 0; g2 < kKeys / 16; ++g2) ngroups += (key0 + g2 * 16 < ctx_end) ? 1 : 0;
+            const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
+            const int row = h * p.block_size + ((key0 + gi * 16) % p.block_size);
+            const uint32_t off = static_cast<uint32_t>(hf * kHalfBytes + gi * 2048);
+            // ---- K tile (lanes 0-15) ----
+            if (j >= kStages) ok = wait_or_abort(smem_u32(&ctrl->k_empty[stage]), par, abort_flag, p.status);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            if (lane == 0) {
+                NPD_TRACE(0, 1, j);
+                mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
+            }
+            __syncwarp();
+            if (!is_v && gi < ngroups)
+                tma_load_3d(smem_u32(k_ring + (size_t)stage * kTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
+                            hf * 64, row, id);
+            // ---- V tile (lanes 16-31) ----
+            if (j >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            if (lane == 0) {
+                NPD_TRACE(0, 2, j);
+                mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
+            }
+            __syncwarp();
+            if (is_v && gi < ngroups)
+                tma_load_3d(smem_u32(v_ring + (size_t)stage * kTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
+                            hf * 64, row, id);
         }
     } else if (warp == 9) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         // =========================== MMA issuer ===========================
         if (lane == 0) {
             constexpr uint32_t fmt = Elem<T>::kDtype == NPD_DTYPE_BF16 ? 1u : 0u;
@@ -313,26 +345,36 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             const uint32_t q_addr = smem_u32(q_tiles);
             bool ok = wait_or_abort(smem_u32(&ctrl->q_full), 0, abort_flag, p.status);
 
-            // S_X(j) = Q_X . K(j)^T : 8 k-steps of 16 elements; a step advances 32 B inside the swizzle atom
+            // Descriptors are built once; a k-step only adds a constant to the start-address field
+            // (16 elements = 32 B inside the swizzle atom, the second half of the tile 16 KiB further on).
+            static_assert(kStages == 2, "descriptor selection below assumes two stages");
+            const uint64_t q_desc0 = desc_k_major(q_addr), q_desc1 = desc_k_major(q_addr + kTileBytes);
+            const uint64_t k_desc0 = desc_k_major(smem_u32(k_ring)), k_desc1 = desc_k_major(smem_u32(k_ring + kTileBytes));
+            const uint64_t v_desc0 = desc_mn_major(smem_u32(v_ring), kHalfBytes);
+            const uint64_t v_desc1 = desc_mn_major(smem_u32(v_ring + kTileBytes), kHalfBytes);
+            // S_X(j) = Q_X . K(j)^T : 8 k-steps of 16 elements
             auto issue_s = [&](int x, int j) {
-                const uint32_t k_addr = smem_u32(k_ring + (size_t)(j % kStages) * kTileBytes);
-                const uint32_t qa = q_addr + x * kTileBytes;
+                const uint64_t qd = x ? q_desc1 : q_desc0, kd = (j & 1) ? k_desc1 : k_desc0;
+                const uint32_t d = tmem + x * 128;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    tc_mma_ss(tmem + x * 128, desc_k_major(qa + off), desc_k_major(k_addr + off), idesc_s,
-                              ks > 0 ? 1u : 0u);
+                    const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
+                    tc_mma_ss(d, qd + off, kd + off, idesc_s, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(smem_u32(&ctrl->s_full[x]));
+                NPD_TRACE(1, 10 + x, j);
             };
             // O_X (+)= P_X(j) . V(j) : P from TMEM (packed pairs, 8 columns per 16 keys), V MN-major from smem
+            // (16 keys = two 8-row groups = 2 KiB further on)
             auto issue_pv = [&](int x, int j) {
-                const uint32_t v_addr = smem_u32(v_ring + (size_t)(j % kStages) * kTileBytes);
+                const uint64_t vd = (j & 1) ? v_desc1 : v_desc0;
+                const uint32_t d = tmem + 256 + x * 128, a = tmem + x * 128;
 #pragma unroll
                 for (int ks = 0; ks < kKeys / 16; ++ks)
-                    tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8,
-                              desc_mn_major(v_addr + ks * 2048, kHalfBytes), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    tc_mma_ts(d, a + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
+                              (j > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(smem_u32(&ctrl->pv_done[x]));
+                NPD_TRACE(1, 20 + x, j);
             };
 
             if (ok && n_kv > 0) {
@@ -355,7 +397,9 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     if (j < ntiles[x]) {
+                        NPD_TRACE(1, 30 + x, j);
                         if (!(ok = wait_or_abort(smem_u32(&ctrl->p_full[x]), j & 1, abort_flag, p.status))) break;
+                        NPD_TRACE(1, 40 + x, j);
                         tc_fence_after();
                         issue_pv(x, j);
                         if (j + 1 < ntiles[x]) issue_s(x, j + 1);   // P_X(j) is consumed before S_X(j+1) lands (in order)
@@ -366,7 +410,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (more) tc_commit(smem_u32(&ctrl->k_empty[(j + 1) % kStages]));
             }
         }
+    } else if (warp >= 10) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // =========================== softmax + correction + epilogue (warps 0-7) ===========================
         const int x = warp >> 2;                                 // query tile A or B
         const int wq = warp & 3;                                 // TMEM lane quarter this warp may touch
@@ -397,14 +444,17 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 fence_proxy_async_smem();
             }
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 1, j);
             if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x]), j & 1, abort_flag, p.status))) break;
             tc_fence_after();
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 2, j);
 
             // The whole score row (128 fp32) stays in registers from here to the packed store: one TMEM read.
             float sc[4][32];
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) tmem_ld32(t_s + cc * 32, sc[cc]);
             tmem_wait_ld();
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 3, j);
             if (key0 + kKeys - 1 > start + tok0[x]) {   // only tiles that reach past the first row's diagonal
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc)
@@ -449,6 +499,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     }
                 }
             }
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 4, j);
             // ---- probabilities in place (masked scores are -inf -> 0), packed in pairs over the score columns ----
             float lsum0 = 0.f, lsum1 = 0.f;
             const float neg_m = -m_run;
@@ -467,9 +518,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             }
             const float lsum = lsum0 + lsum1;
             l_run += lsum;
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 5, j);
             tmem_wait_st();
             tc_fence_before();               // P is in TMEM, S has been read: the MMA warp may go on
             mbar_arrive(smem_u32(&ctrl->p_full[x]));
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 6, j);
         }
 
         // ---- epilogue: O / l -> out ----
@@ -593,6 +646,10 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
         p.num_blocks = static_cast<int>(num_blocks);
         p.bt_row_stride = bt_row_stride;
+#ifdef NPD_PREFILL_TRACE
+        p.trace = workspace_bytes >= 256 + 4 * 4096 * sizeof(long long)
+                      ? reinterpret_cast<long long *>(static_cast<uint8_t *>(workspace) + 256) : nullptr;
+#endif
         p.cta_prefix[0] = 0;
         for (int i = 0; i < nc; ++i) {
             p.chunk_q_offset[i] = chunk_q_offset_host[c0 + i];
