@@ -29,13 +29,17 @@ using namespace npd;
 
 constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays)
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
-constexpr int kKeys = 128;         // keys per tile (UMMA N of the score MMA)
+constexpr int kKeys = 64;          // keys per tile (UMMA N of the score MMA, K extent of the PV MMA)
 constexpr int kD = 128;            // head_dim
 constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA, 10-11 idle (register donors)
-constexpr int kHalfBytes = kRows * 128;             // one 64-element half of a 128-row operand tile
-constexpr int kTileBytes = 2 * kHalfBytes;          // 32 KiB: a Q, K or V tile
-constexpr int kStages = 2;
-constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; P_X aliases S_X
+constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
+constexpr int kQTileBytes = 2 * kQHalfBytes;        // 32 KiB
+constexpr int kKvHalfBytes = kKeys * 128;           // one 64-element half of a 64-key K or V tile
+constexpr int kKvTileBytes = 2 * kKvHalfBytes;      // 16 KiB
+constexpr int kStages = 4;                          // K ring and V ring depth
+constexpr int kTmemCols = 512;     // per query tile X: two 64-column score buffers, then O_A | O_B (128 each);
+                                   // the packed probabilities of a key tile alias its score buffer
+constexpr int kPolyPairsOf8 = 0;           // of every 8 score pairs, this many take the polynomial exp2
 constexpr float kRescaleThreshold = 8.f;   // log2 units: O is rescaled only when a row max grows by more
 constexpr long long kWaitCycles = 4000000000LL;
 
@@ -73,6 +77,12 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .b32 r;\n\t.reg .pred p;\n\telect.sync r|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -132,6 +142,48 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Packed fp32x2 arithmetic (two lanes per instruction on sm_100): halves the issue slots of the
+// scale-and-subtract and of the row sum.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// 2^x for a packed pair on the FMA pipes instead of the special-function unit (which is the
+// scarcest resource of the softmax: 16 results per clock per SM).  x = n + f with n = round(x),
+// f in [-0.5, 0.5]; 2^f by a cubic (max relative error 1.0e-4, far below the rounding of P to a
+// 16-bit type); n is added to the exponent field.  x is clamped at -125 (result ~2e-38, i.e. 0).
+__device__ __forceinline__ void exp2_poly_pair(uint64_t x2, float &p0, float &p1) {
+    float x0, x1;
+    unpack_f32x2(x2, x0, x1);
+    x0 = fmaxf(x0, -125.f);
+    x1 = fmaxf(x1, -125.f);
+    const uint64_t xc = pack_f32x2(x0, x1);
+    const uint64_t t2 = add_f32x2(xc, pack_f32x2(12582912.f, 12582912.f));      // low mantissa bits = n
+    const uint64_t n2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
+    const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.f, -1.f), xc);
+    uint64_t q2 = fma_f32x2(pack_f32x2(0.05583828f, 0.05583828f), f2, pack_f32x2(0.24263948f, 0.24263948f));
+    q2 = fma_f32x2(q2, f2, pack_f32x2(0.69313675f, 0.69313675f));
+    q2 = fma_f32x2(q2, f2, pack_f32x2(0.99992454f, 0.99992454f));
+    float q0, q1, t0, t1;
+    unpack_f32x2(q2, q0, q1);
+    unpack_f32x2(t2, t0, t1);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -192,9 +244,9 @@ struct alignas(8) SmemCtrl {
     uint64_t q_full;
     uint64_t k_full[kStages], k_empty[kStages];
     uint64_t v_full[kStages], v_empty[kStages];
-    uint64_t s_full[2];     // score tile of query tile X is in TMEM
-    uint64_t p_full[2];     // probabilities of query tile X are in TMEM (128 arrivals)
-    uint64_t pv_done[2];    // the PV MMAs of query tile X for the current key tile have completed
+    uint64_t s_full[2][2];  // [query tile][score buffer]: the score tile is in TMEM
+    uint64_t p_full[2][2];  // [query tile][score buffer]: its probabilities are in TMEM (128 arrivals)
+    uint64_t pv_done[2];    // the PV MMAs of query tile X for one more key tile have completed
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -208,11 +260,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
     uint8_t *sbase = smem_raw + pad;
     uint8_t *q_tiles = sbase;                                   // 2 x 32 KiB (query tiles A and B)
-    uint8_t *k_ring = q_tiles + 2 * kTileBytes;                 // kStages x 32 KiB
-    uint8_t *v_ring = k_ring + kStages * kTileBytes;            // kStages x 32 KiB
-    SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStages * kTileBytes);
+    uint8_t *k_ring = q_tiles + 2 * kQTileBytes;                // kStages x 16 KiB
+    uint8_t *v_ring = k_ring + kStages * kKvTileBytes;          // kStages x 16 KiB
+    SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStages * kKvTileBytes);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
     // ---- which pair of query tiles is mine ----
     const int h = blockIdx.x % p.num_kv_heads;
@@ -243,8 +295,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             mbar_init(smem_u32(&ctrl->v_empty[i]), 1);
         }
         for (int x = 0; x < 2; ++x) {
-            mbar_init(smem_u32(&ctrl->s_full[x]), 1);
-            mbar_init(smem_u32(&ctrl->p_full[x]), 128);
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(smem_u32(&ctrl->s_full[x][b]), 1);
+                mbar_init(smem_u32(&ctrl->p_full[x][b]), 128);
+            }
             mbar_init(smem_u32(&ctrl->pv_done[x]), 1);
         }
         ctrl->abort_flag = 0;
@@ -261,13 +315,13 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     volatile int *abort_flag = &ctrl->abort_flag;
 
     // Register re-allocation between warpgroups (first statement of every role): the two softmax groups
-    // keep a whole 128-wide score row in registers, the third group (TMA, MMA, two idle warps) needs few.
+    // work on whole score rows in registers, the third group (TMA, MMA, two idle warps) needs few.
     if (warp == 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         // =========================== TMA producer (whole warp issues) ===========================
-        // A K or V tile is 16 boxes of 2 KiB (8 groups of 16 keys x 2 halves of 64 elements).  Lanes
-        // 0-15 issue the K boxes and lanes 16-31 the V boxes, each lane looking up its own block id one
-        // tile ahead, so neither the table reads nor the serial issue of 32 copies sit on the critical path.
+        // A K or V tile of 64 keys is 8 boxes of 2 KiB (4 groups of 16 keys x 2 halves of 64 elements).
+        // Lanes 0-7 issue the K boxes and lanes 8-15 the V boxes, each lane looking up its own block id
+        // one tile ahead, so neither the table reads nor a serial issue sit on the critical path.
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
@@ -279,17 +333,17 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             for (int x = 0; x < 2; ++x) {
                 if (tq_valid[x] <= 0) continue;
                 for (int hf = 0; hf < 2; ++hf)
-                    tma_load_3d(smem_u32(q_tiles + x * kTileBytes + hf * kHalfBytes), &tm_q, qbar, hf * 64,
+                    tma_load_3d(smem_u32(q_tiles + x * kQTileBytes + hf * kQHalfBytes), &tm_q, qbar, hf * 64,
                                 h * p.group, qoff + tok0[x]);
             }
         }
         const int32_t *table = p.block_tables + (long long)c * p.bt_row_stride;
-        const int is_v = lane >> 4, gi = (lane >> 1) & 7, hf = lane & 1;
-        const CUtensorMap *tm = is_v ? &tm_v : &tm_k;
-        auto lookup = [&](int j) {
-            const int key = j * kKeys + gi * 16;
+        const int role = lane >> 3, gi = (lane >> 1) & 3, hf = lane & 1;     // role 0 = K, 1 = V, others idle
+        const CUtensorMap *tm = role == 1 ? &tm_v : &tm_k;
+        auto lookup = [&](int t) {
+            const int key = t * kKeys + gi * 16;
             int id = 0;
-            if (j < n_kv && key < ctx_end) {
+            if (role < 2 && t < n_kv && key < ctx_end) {
                 id = __ldg(table + key / p.block_size);
                 if (id < 0 || id >= p.num_blocks) {
                     atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
@@ -300,114 +354,127 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         };
         int id_next = lookup(0);
         bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            const int stage = j % kStages;
-            const uint32_t par = ((j / kStages) - 1) & 1;
-            const int key0 = j * kKeys;
+        for (int t = 0; t < n_kv; ++t) {
+            const int stage = t % kStages;
+            const uint32_t par = ((t / kStages) - 1) & 1;
+            const int key0 = t * kKeys;
             const int id = id_next;
-            id_next = lookup(j + 1);
+            id_next = lookup(t + 1);
             // 16-key row groups holding at least one written key; the rest is never loaded
             int ngroups = 0;
             for (int g2 = 0; g2 < kKeys / 16; ++g2) ngroups += (key0 + g2 * 16 < ctx_end) ? 1 : 0;
             const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
             const int row = h * p.block_size + ((key0 + gi * 16) % p.block_size);
-            const uint32_t off = static_cast<uint32_t>(hf * kHalfBytes + gi * 2048);
-            // ---- K tile (lanes 0-15) ----
-            if (j >= kStages) ok = wait_or_abort(smem_u32(&ctrl->k_empty[stage]), par, abort_flag, p.status);
+            const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048);
+            // ---- K tile ----
+            if (t >= kStages) ok = wait_or_abort(smem_u32(&ctrl->k_empty[stage]), par, abort_flag, p.status);
             if (!__all_sync(0xffffffffu, ok)) break;
             if (lane == 0) {
-                NPD_TRACE(0, 1, j);
+                NPD_TRACE(0, 1, t);
                 mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
             }
             __syncwarp();
-            if (!is_v && gi < ngroups)
-                tma_load_3d(smem_u32(k_ring + (size_t)stage * kTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
+            if (role == 0 && gi < ngroups)
+                tma_load_3d(smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
                             hf * 64, row, id);
-            // ---- V tile (lanes 16-31) ----
-            if (j >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
+            // ---- V tile ----
+            if (t >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
             if (!__all_sync(0xffffffffu, ok)) break;
             if (lane == 0) {
-                NPD_TRACE(0, 2, j);
+                NPD_TRACE(0, 2, t);
                 mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
             }
             __syncwarp();
-            if (is_v && gi < ngroups)
-                tma_load_3d(smem_u32(v_ring + (size_t)stage * kTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
+            if (role == 1 && gi < ngroups)
+                tma_load_3d(smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
                             hf * 64, row, id);
         }
     } else if (warp == 9) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         // =========================== MMA issuer ===========================
-        if (lane == 0) {
+        // The whole warp runs this loop so that addresses and descriptors stay in uniform registers; one
+        // elected lane issues the tcgen05 instructions.
+        {
             constexpr uint32_t fmt = Elem<T>::kDtype == NPD_DTYPE_BF16 ? 1u : 0u;
             constexpr uint32_t idesc_s = instr_desc(fmt, 0u, kRows, kKeys);
             constexpr uint32_t idesc_pv = instr_desc(fmt, 1u, kRows, kD);
             const uint32_t q_addr = smem_u32(q_tiles);
             bool ok = wait_or_abort(smem_u32(&ctrl->q_full), 0, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);
 
-            // Descriptors are built once; a k-step only adds a constant to the start-address field
-            // (16 elements = 32 B inside the swizzle atom, the second half of the tile 16 KiB further on).
-            static_assert(kStages == 2, "descriptor selection below assumes two stages");
-            const uint64_t q_desc0 = desc_k_major(q_addr), q_desc1 = desc_k_major(q_addr + kTileBytes);
-            const uint64_t k_desc0 = desc_k_major(smem_u32(k_ring)), k_desc1 = desc_k_major(smem_u32(k_ring + kTileBytes));
-            const uint64_t v_desc0 = desc_mn_major(smem_u32(v_ring), kHalfBytes);
-            const uint64_t v_desc1 = desc_mn_major(smem_u32(v_ring + kTileBytes), kHalfBytes);
-            // S_X(j) = Q_X . K(j)^T : 8 k-steps of 16 elements
-            auto issue_s = [&](int x, int j) {
-                const uint64_t qd = x ? q_desc1 : q_desc0, kd = (j & 1) ? k_desc1 : k_desc0;
-                const uint32_t d = tmem + x * 128;
+            // Descriptors are built once; a k-step or a ring stage only adds a constant to the
+            // start-address field (16-byte units).
+            const uint64_t q_desc0 = desc_k_major(q_addr), q_desc1 = desc_k_major(q_addr + kQTileBytes);
+            const uint64_t k_desc0 = desc_k_major(smem_u32(k_ring));
+            const uint64_t v_desc0 = desc_mn_major(smem_u32(v_ring), kKvHalfBytes);
+            // S_X(t) = Q_X . K(t)^T into score buffer t&1 : 8 k-steps of 16 elements (32 B inside the
+            // swizzle atom; the second 64-element half starts one half-tile further on)
+            auto issue_s = [&](int x, int t) {
+                const uint64_t qd = x ? q_desc1 : q_desc0;
+                const uint64_t kd = k_desc0 + static_cast<uint64_t>(((t % kStages) * kKvTileBytes) >> 4);
+                const uint32_t d = tmem + x * 128 + (t & 1) * 64;
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
-                    tc_mma_ss(d, qd + off, kd + off, idesc_s, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < kD / 16; ++ks) {
+                        const uint64_t a_off = static_cast<uint64_t>(((ks >> 2) * kQHalfBytes + (ks & 3) * 32) >> 4);
+                        const uint64_t b_off = static_cast<uint64_t>(((ks >> 2) * kKvHalfBytes + (ks & 3) * 32) >> 4);
+                        tc_mma_ss(d, qd + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&ctrl->s_full[x][t & 1]));
+                    NPD_TRACE(1, 10 + x, t);
                 }
-                tc_commit(smem_u32(&ctrl->s_full[x]));
-                NPD_TRACE(1, 10 + x, j);
+                __syncwarp();
             };
-            // O_X (+)= P_X(j) . V(j) : P from TMEM (packed pairs, 8 columns per 16 keys), V MN-major from smem
-            // (16 keys = two 8-row groups = 2 KiB further on)
-            auto issue_pv = [&](int x, int j) {
-                const uint64_t vd = (j & 1) ? v_desc1 : v_desc0;
-                const uint32_t d = tmem + 256 + x * 128, a = tmem + x * 128;
+            // O_X (+)= P_X(t) . V(t) : P from TMEM (packed pairs, 8 columns per 16 keys), V MN-major from
+            // shared memory (16 keys = two 8-row groups = 2 KiB further on)
+            auto issue_pv = [&](int x, int t) {
+                const uint64_t vd = v_desc0 + static_cast<uint64_t>(((t % kStages) * kKvTileBytes) >> 4);
+                const uint32_t d = tmem + 256 + x * 128, a = tmem + x * 128 + (t & 1) * 64;
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < kKeys / 16; ++ks)
-                    tc_mma_ts(d, a + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
-                              (j > 0 || ks > 0) ? 1u : 0u);
-                tc_commit(smem_u32(&ctrl->pv_done[x]));
-                NPD_TRACE(1, 20 + x, j);
+                    for (int ks = 0; ks < kKeys / 16; ++ks)
+                        tc_mma_ts(d, a + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
+                                  (t > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit(smem_u32(&ctrl->pv_done[x]));
+                    NPD_TRACE(1, 20 + x, t);
+                }
+                __syncwarp();
+            };
+            auto commit = [&](uint64_t *bar) {
+                if (elect_one()) tc_commit(smem_u32(bar));
+                __syncwarp();
+            };
+            auto wait_all = [&](uint64_t *bar, uint32_t parity) {
+                const bool good = wait_or_abort(smem_u32(bar), parity, abort_flag, p.status);
+                return __all_sync(0xffffffffu, good);
             };
 
-            if (ok && n_kv > 0) {
-                ok = wait_or_abort(smem_u32(&ctrl->k_full[0]), 0, abort_flag, p.status);
-                if (ok) {
-                    tc_fence_after();
-                    if (ntiles[0] > 0) issue_s(0, 0);
-                    if (ntiles[1] > 0) issue_s(1, 0);
-                    tc_commit(smem_u32(&ctrl->k_empty[0]));
-                }
+            // Prologue: the first two score tiles of each query tile (one per score buffer).
+            for (int t = 0; ok && t < 2 && t < n_kv; ++t) {
+                if (!(ok = wait_all(&ctrl->k_full[t], 0))) break;
+                tc_fence_after();
+                for (int x = 0; x < 2; ++x)
+                    if (t < ntiles[x]) issue_s(x, t);
+                commit(&ctrl->k_empty[t]);
             }
-            for (int j = 0; ok && j < n_kv; ++j) {
-                const int stage = j % kStages;
-                const uint32_t par = (j / kStages) & 1;
-                const bool more = j + 1 < n_kv;
-                if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), par, abort_flag, p.status))) break;
-                if (more && !(ok = wait_or_abort(smem_u32(&ctrl->k_full[(j + 1) % kStages]), ((j + 1) / kStages) & 1,
-                                                 abort_flag, p.status)))
-                    break;
+            for (int t = 0; ok && t < n_kv; ++t) {
+                const int stage = t % kStages;
+                const bool ahead = t + 2 < n_kv;
+                if (!(ok = wait_all(&ctrl->v_full[stage], (t / kStages) & 1))) break;
+                if (ahead && !(ok = wait_all(&ctrl->k_full[(t + 2) % kStages], ((t + 2) / kStages) & 1))) break;
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
-                    if (j < ntiles[x]) {
-                        NPD_TRACE(1, 30 + x, j);
-                        if (!(ok = wait_or_abort(smem_u32(&ctrl->p_full[x]), j & 1, abort_flag, p.status))) break;
-                        NPD_TRACE(1, 40 + x, j);
+                    if (t < ntiles[x]) {
+                        if (!(ok = wait_all(&ctrl->p_full[x][t & 1], (t >> 1) & 1))) break;
                         tc_fence_after();
-                        issue_pv(x, j);
-                        if (j + 1 < ntiles[x]) issue_s(x, j + 1);   // P_X(j) is consumed before S_X(j+1) lands (in order)
+                        issue_pv(x, t);
+                        // the score buffer that held P_X(t) is reused by S_X(t+2); MMAs execute in issue order
+                        if (t + 2 < ntiles[x]) issue_s(x, t + 2);
                     }
                 }
                 if (!ok) break;
-                tc_commit(smem_u32(&ctrl->v_empty[stage]));
-                if (more) tc_commit(smem_u32(&ctrl->k_empty[(j + 1) % kStages]));
+                commit(&ctrl->v_empty[stage]);
+                if (ahead) commit(&ctrl->k_empty[(t + 2) % kStages]);
             }
         }
     } else if (warp >= 10) {
@@ -419,7 +486,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         const int wq = warp & 3;                                 // TMEM lane quarter this warp may touch
         const int row = wq * 32 + lane;                          // == TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-        const uint32_t t_s = tmem + x * 128 + lane_base;         // scores, later the packed probabilities
+        const uint32_t t_sx = tmem + x * 128 + lane_base;        // score buffers, later the packed probabilities
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
         const int pos = start + tok0[x] + tq_idx;                // last visible key of this row
@@ -427,52 +494,53 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
 
-        for (int j = 0; ok && j < my_tiles; ++j) {
-            const int stage = j % kStages;
-            const int key0 = j * kKeys;
+        for (int t = 0; ok && t < my_tiles; ++t) {
+            const int stage = t % kStages, buf = t & 1;
+            const int key0 = t * kKeys;
+            const uint32_t t_s = t_sx + buf * 64;
             // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
             // there cannot meet a NaN.  Both softmax groups do it (idempotent) before releasing their P.
             if (key0 + kKeys > ctx_end) {
-                if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (j / kStages) & 1, abort_flag, p.status))) break;
-                uint8_t *v_tile = v_ring + (size_t)stage * kTileBytes;
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (t / kStages) & 1, abort_flag, p.status))) break;
+                uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
                 const int first = max(ctx_end - key0, 0);
                 const int cnt = (kKeys - first) * 16;            // 16-byte pieces: 2 halves x 8 per row
                 for (int idx = threadIdx.x & 127; idx < cnt; idx += 128) {
                     const int r = first + idx / 16, piece = idx % 16;
-                    *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kHalfBytes + r * 128 + ((piece & 7) << 4)) =
+                    *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kKvHalfBytes + r * 128 + ((piece & 7) << 4)) =
                         make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async_smem();
             }
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 1, j);
-            if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x]), j & 1, abort_flag, p.status))) break;
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 1, t);
+            if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x][buf]), (t >> 1) & 1, abort_flag, p.status))) break;
             tc_fence_after();
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 2, j);
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 2, t);
 
-            // The whole score row (128 fp32) stays in registers from here to the packed store: one TMEM read.
-            float sc[4][32];
+            // The score row of this key tile (64 fp32) stays in registers until the packed store.
+            float sc[2][32];
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) tmem_ld32(t_s + cc * 32, sc[cc]);
+            for (int cc = 0; cc < 2; ++cc) tmem_ld32(t_s + cc * 32, sc[cc]);
             tmem_wait_ld();
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 3, j);
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 3, t);
             if (key0 + kKeys - 1 > start + tok0[x]) {   // only tiles that reach past the first row's diagonal
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc)
+                for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         if (key0 + cc * 32 + i > pos) sc[cc][i] = -INFINITY;
             }
-            // ---- row maximum (three-input max) ----
-            float mx0 = -INFINITY, mx1 = -INFINITY;
+            // ---- row maximum: four independent chains of three-input max ----
+            float mxa[4];
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc)
+            for (int q4 = 0; q4 < 4; ++q4) mxa[q4] = fmaxf(sc[q4 >> 1][(q4 & 1) * 16], sc[q4 >> 1][(q4 & 1) * 16 + 1]);
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    mx0 = fmax3(mx0, sc[cc][i], sc[cc][i + 1]);
-                    mx1 = fmax3(mx1, sc[cc][i + 2], sc[cc][i + 3]);
-                }
-            const float m_new = fmaxf(mx0, mx1) * p.scale_log2;
-            if (j == 0) {
+            for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+                for (int i = 2; i < 16; i += 2)
+                    mxa[q4] = fmax3(mxa[q4], sc[q4 >> 1][(q4 & 1) * 16 + i], sc[q4 >> 1][(q4 & 1) * 16 + i + 1]);
+            const float m_new = fmax3(fmaxf(mxa[0], mxa[1]), mxa[2], mxa[3]) * p.scale_log2;
+            if (t == 0) {
                 m_run = m_new;                                  // key 0 is visible to every row: finite
             } else {
                 // Lazy correction: O (in TMEM) and l are rescaled only when some row's maximum grew by more
@@ -481,7 +549,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 const bool grow = m_new > m_run + kRescaleThreshold;
                 if (__any_sync(0xffffffffu, grow)) {
                     const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
-                    if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (j - 1) & 1, abort_flag, p.status))) break;
+                    if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (t - 1) & 1, abort_flag, p.status))) break;
                     tc_fence_after();
 #pragma unroll 1
                     for (int cc = 0; cc < 4; ++cc) {
@@ -499,35 +567,48 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     }
                 }
             }
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 4, j);
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 4, t);
             // ---- probabilities in place (masked scores are -inf -> 0), packed in pairs over the score columns ----
-            float lsum0 = 0.f, lsum1 = 0.f;
-            const float neg_m = -m_run;
+            const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+            const uint64_t negm2 = pack_f32x2(-m_run, -m_run);
+            uint64_t acc2[2] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = 0; cc < 2; ++cc) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = fast_exp2(fmaf(sc[cc][i], p.scale_log2, neg_m));
-                    const float p1 = fast_exp2(fmaf(sc[cc][i + 1], p.scale_log2, neg_m));
-                    lsum0 += p0;
-                    lsum1 += p1;
+                    const uint64_t x2 = fma_f32x2(pack_f32x2(sc[cc][i], sc[cc][i + 1]), scale2, negm2);
+                    float p0, p1;
+                    if (((i >> 1) & 7) < kPolyPairsOf8) {       // compile-time pattern: some pairs avoid the SFU
+                        exp2_poly_pair(x2, p0, p1);
+                    } else {
+                        float x0, x1;
+                        unpack_f32x2(x2, x0, x1);
+                        p0 = fast_exp2(x0);
+                        p1 = fast_exp2(x1);
+                    }
+                    acc2[(i >> 1) & 1] = add_f32x2(acc2[(i >> 1) & 1], pack_f32x2(p0, p1));
                     packed[i >> 1] = Elem<T>::pack2(p0, p1);
                 }
                 tmem_st16(t_s + cc * 16, packed);
             }
-            const float lsum = lsum0 + lsum1;
-            l_run += lsum;
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 5, j);
+            float lsum0, lsum1, lsum2, lsum3;
+            unpack_f32x2(acc2[0], lsum0, lsum1);
+            unpack_f32x2(acc2[1], lsum2, lsum3);
+            l_run += (lsum0 + lsum2) + (lsum1 + lsum3);
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 5, t);
             tmem_wait_st();
             tc_fence_before();               // P is in TMEM, S has been read: the MMA warp may go on
-            mbar_arrive(smem_u32(&ctrl->p_full[x]));
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 6, j);
+            mbar_arrive(smem_u32(&ctrl->p_full[x][buf]));
+            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 6, t);
         }
 
         // ---- epilogue: O / l -> out ----
         if (ok && my_tiles > 0) {
-            ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (my_tiles - 1) & 1, abort_flag, p.status);
+            // The softmax may be up to two key tiles ahead of the PV MMAs, so a single parity wait could be
+            // satisfied by an older phase: observe the last two completions in order.
+            if (my_tiles > 1) ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (my_tiles - 2) & 1, abort_flag, p.status);
+            if (ok) ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (my_tiles - 1) & 1, abort_flag, p.status);
             if (ok) {
                 tc_fence_after();
                 const bool store = tq_idx < tq_valid[x] && row < p.tq * p.group;
@@ -625,7 +706,7 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                                       cache_block_stride, 16);
     if (rc != NPD_OK) return rc;
 
-    const size_t smem = 1024 + (size_t)kTileBytes * (2 + 2 * kStages) + sizeof(SmemCtrl) + 64;   // 2 Q + K ring + V ring
+    const size_t smem = 1024 + 2 * (size_t)kQTileBytes + 2 * (size_t)kStages * kKvTileBytes + sizeof(SmemCtrl) + 64;
     auto kern = dtype == NPD_DTYPE_F16 ? paged_prefill_kernel<__half> : paged_prefill_kernel<__nv_bfloat16>;
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
