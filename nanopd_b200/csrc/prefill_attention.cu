@@ -31,7 +31,7 @@ constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
 constexpr int kKeys = 64;          // keys per tile (UMMA N of the score MMA, K extent of the PV MMA)
 constexpr int kD = 128;            // head_dim
-constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA, 10-11 idle (register donors)
+constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA for A, 10 MMA for B, 11 idle
 constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
 constexpr int kQTileBytes = 2 * kQHalfBytes;        // 32 KiB
 constexpr int kKvHalfBytes = kKeys * 128;           // one 64-element half of a 64-key K or V tile
@@ -39,7 +39,7 @@ constexpr int kKvTileBytes = 2 * kKvHalfBytes;      // 16 KiB
 constexpr int kStages = 4;                          // K ring and V ring depth
 constexpr int kTmemCols = 512;     // per query tile X: two 64-column score buffers, then O_A | O_B (128 each);
                                    // the packed probabilities of a key tile alias its score buffer
-constexpr int kPolyPairsOf8 = 0;           // of every 8 score pairs, this many take the polynomial exp2
+constexpr int kPolyPairsOf8 = 2;           // of every 8 score pairs, this many take the polynomial exp2
 constexpr float kRescaleThreshold = 8.f;   // log2 units: O is rescaled only when a row max grows by more
 constexpr long long kWaitCycles = 4000000000LL;
 
@@ -55,6 +55,7 @@ struct PrefillParams {
     int max_blocks_per_seq;
     int num_blocks;
     long long bt_row_stride;
+    int debug_flags;        // performance experiments only: 1 = skip softmax math, 2 = skip MMA issue, 4 = skip K/V loads
     int chunk_q_offset[kMaxChunks];
     int chunk_tokens[kMaxChunks];
     int chunk_start[kMaxChunks];
@@ -142,47 +143,24 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// Packed fp32x2 arithmetic (two lanes per instruction on sm_100): halves the issue slots of the
-// scale-and-subtract and of the row sum.
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-    uint64_t v;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
-    return v;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-// 2^x for a packed pair on the FMA pipes instead of the special-function unit (which is the
-// scarcest resource of the softmax: 16 results per clock per SM).  x = n + f with n = round(x),
-// f in [-0.5, 0.5]; 2^f by a cubic (max relative error 1.0e-4, far below the rounding of P to a
-// 16-bit type); n is added to the exponent field.  x is clamped at -125 (result ~2e-38, i.e. 0).
-__device__ __forceinline__ void exp2_poly_pair(uint64_t x2, float &p0, float &p1) {
-    float x0, x1;
-    unpack_f32x2(x2, x0, x1);
-    x0 = fmaxf(x0, -125.f);
-    x1 = fmaxf(x1, -125.f);
-    const uint64_t xc = pack_f32x2(x0, x1);
-    const uint64_t t2 = add_f32x2(xc, pack_f32x2(12582912.f, 12582912.f));      // low mantissa bits = n
-    const uint64_t n2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
-    const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.f, -1.f), xc);
-    uint64_t q2 = fma_f32x2(pack_f32x2(0.05583828f, 0.05583828f), f2, pack_f32x2(0.24263948f, 0.24263948f));
-    q2 = fma_f32x2(q2, f2, pack_f32x2(0.69313675f, 0.69313675f));
-    q2 = fma_f32x2(q2, f2, pack_f32x2(0.99992454f, 0.99992454f));
-    float q0, q1, t0, t1;
-    unpack_f32x2(q2, q0, q1);
-    unpack_f32x2(t2, t0, t1);
-    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+// Packed fp32x2 arithmetic (__ffma2_rn / __fadd2_rn: two lanes per instruction on sm_100) halves the
+// issue slots of the scale-and-subtract and of the row sum.
+//
+// 2^x for a pair on the FMA pipes instead of the special-function unit (16 results per clock per SM,
+// the scarcest resource of the softmax).  x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic
+// (max relative error 1.0e-4, far below the rounding of P to a 16-bit type); n is added to the exponent
+// field.  x is clamped at -125 (result ~2e-38, i.e. 0 for every purpose here).
+__device__ __forceinline__ float2 exp2_poly_pair(float2 x) {
+    x.x = fmaxf(x.x, -125.f);
+    x.y = fmaxf(x.y, -125.f);
+    const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));          // low mantissa bits = n
+    const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+    float2 q = __ffma2_rn(make_float2(0.05583828f, 0.05583828f), f, make_float2(0.24263948f, 0.24263948f));
+    q = __ffma2_rn(q, f, make_float2(0.69313675f, 0.69313675f));
+    q = __ffma2_rn(q, f, make_float2(0.99992454f, 0.99992454f));
+    return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23)),
+                       __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23)));
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
@@ -202,6 +180,19 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t lbo_b
 // Instruction descriptor: fp32 accumulate, A/B of type `fmt` (0 = f16, 1 = bf16), M x N tile.
 __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_major, uint32_t M, uint32_t N) {
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+// Non-blocking phase test (try_wait may suspend the thread for a while; this never does).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
 }
 
 // Bounded, abortable mbarrier wait shared by all roles.
@@ -242,8 +233,8 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 
 struct alignas(8) SmemCtrl {
     uint64_t q_full;
-    uint64_t k_full[kStages], k_empty[kStages];
-    uint64_t v_full[kStages], v_empty[kStages];
+    uint64_t kv_full[kStages];   // K and V tile of a ring stage have landed
+    uint64_t kv_empty[kStages];  // both MMA warps are done with the stage (2 arrivals)
     uint64_t s_full[2][2];  // [query tile][score buffer]: the score tile is in TMEM
     uint64_t p_full[2][2];  // [query tile][score buffer]: its probabilities are in TMEM (128 arrivals)
     uint64_t pv_done[2];    // the PV MMAs of query tile X for one more key tile have completed
@@ -289,10 +280,8 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&ctrl->q_full), 1);
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(smem_u32(&ctrl->k_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->k_empty[i]), 1);
-            mbar_init(smem_u32(&ctrl->v_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->v_empty[i]), 1);
+            mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->kv_empty[i]), 2);
         }
         for (int x = 0; x < 2; ++x) {
             for (int b = 0; b < 2; ++b) {
@@ -366,118 +355,101 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
             const int row = h * p.block_size + ((key0 + gi * 16) % p.block_size);
             const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048);
-            // ---- K tile ----
-            if (t >= kStages) ok = wait_or_abort(smem_u32(&ctrl->k_empty[stage]), par, abort_flag, p.status);
+            if (t >= kStages) ok = wait_or_abort(smem_u32(&ctrl->kv_empty[stage]), par, abort_flag, p.status);
             if (!__all_sync(0xffffffffu, ok)) break;
+            const uint32_t bar = smem_u32(&ctrl->kv_full[stage]);
             if (lane == 0) {
                 NPD_TRACE(0, 1, t);
-                mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
+                if (p.debug_flags & 4) mbar_arrive(bar); else mbar_expect_tx(bar, 2 * bytes);
             }
             __syncwarp();
-            if (role == 0 && gi < ngroups)
-                tma_load_3d(smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
-                            hf * 64, row, id);
-            // ---- V tile ----
-            if (t >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
-            if (!__all_sync(0xffffffffu, ok)) break;
-            if (lane == 0) {
-                NPD_TRACE(0, 2, t);
-                mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
-            }
-            __syncwarp();
-            if (role == 1 && gi < ngroups)
-                tma_load_3d(smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
-                            hf * 64, row, id);
+            if (!(p.debug_flags & 4) && role < 2 && gi < ngroups)
+                tma_load_3d(smem_u32((role ? v_ring : k_ring) + (size_t)stage * kKvTileBytes) + off, tm, bar, hf * 64, row, id);
         }
-    } else if (warp == 9) {
+    } else if (warp == 9 || warp == 10) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-        // =========================== MMA issuer ===========================
-        // The whole warp runs this loop so that addresses and descriptors stay in uniform registers; one
-        // elected lane issues the tcgen05 instructions.
+        // =========================== MMA issuers: warp 9 for query tile A, warp 10 for B ===========================
+        // Each warp runs its loop in full (addresses and descriptors stay in uniform registers) and one elected
+        // lane issues the tcgen05 instructions.  Two issuers keep the two query tiles from blocking one another.
         {
+            const int x = warp - 9;
+            const int my_tiles = ntiles[x];
             constexpr uint32_t fmt = Elem<T>::kDtype == NPD_DTYPE_BF16 ? 1u : 0u;
             constexpr uint32_t idesc_s = instr_desc(fmt, 0u, kRows, kKeys);
             constexpr uint32_t idesc_pv = instr_desc(fmt, 1u, kRows, kD);
-            const uint32_t q_addr = smem_u32(q_tiles);
-            bool ok = wait_or_abort(smem_u32(&ctrl->q_full), 0, abort_flag, p.status);
-            ok = __all_sync(0xffffffffu, ok);
+            auto wait_all = [&](uint64_t *bar, uint32_t parity) {
+                const bool good = wait_or_abort(smem_u32(bar), parity, abort_flag, p.status);
+                return __all_sync(0xffffffffu, good);
+            };
+            auto commit = [&](uint64_t *bar) {
+                if (elect_one()) tc_commit(smem_u32(bar));
+                __syncwarp();
+            };
+            bool ok = wait_all(&ctrl->q_full, 0);
 
             // Descriptors are built once; a k-step or a ring stage only adds a constant to the
             // start-address field (16-byte units).
-            const uint64_t q_desc0 = desc_k_major(q_addr), q_desc1 = desc_k_major(q_addr + kQTileBytes);
+            const uint64_t q_desc = desc_k_major(smem_u32(q_tiles) + x * kQTileBytes);
             const uint64_t k_desc0 = desc_k_major(smem_u32(k_ring));
             const uint64_t v_desc0 = desc_mn_major(smem_u32(v_ring), kKvHalfBytes);
+            const uint32_t t_sx = tmem + x * 128, t_o = tmem + 256 + x * 128;
             // S_X(t) = Q_X . K(t)^T into score buffer t&1 : 8 k-steps of 16 elements (32 B inside the
             // swizzle atom; the second 64-element half starts one half-tile further on)
-            auto issue_s = [&](int x, int t) {
-                const uint64_t qd = x ? q_desc1 : q_desc0;
+            auto issue_s = [&](int t) {
                 const uint64_t kd = k_desc0 + static_cast<uint64_t>(((t % kStages) * kKvTileBytes) >> 4);
-                const uint32_t d = tmem + x * 128 + (t & 1) * 64;
+                const uint32_t d = t_sx + (t & 1) * 64;
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kD / 16; ++ks) {
+                        if (p.debug_flags & 2) break;
                         const uint64_t a_off = static_cast<uint64_t>(((ks >> 2) * kQHalfBytes + (ks & 3) * 32) >> 4);
                         const uint64_t b_off = static_cast<uint64_t>(((ks >> 2) * kKvHalfBytes + (ks & 3) * 32) >> 4);
-                        tc_mma_ss(d, qd + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
+                        tc_mma_ss(d, q_desc + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
                     }
                     tc_commit(smem_u32(&ctrl->s_full[x][t & 1]));
-                    NPD_TRACE(1, 10 + x, t);
+                    NPD_TRACE(1 , 10 + x, t);
                 }
                 __syncwarp();
             };
             // O_X (+)= P_X(t) . V(t) : P from TMEM (packed pairs, 8 columns per 16 keys), V MN-major from
             // shared memory (16 keys = two 8-row groups = 2 KiB further on)
-            auto issue_pv = [&](int x, int t) {
+            auto issue_pv = [&](int t) {
                 const uint64_t vd = v_desc0 + static_cast<uint64_t>(((t % kStages) * kKvTileBytes) >> 4);
-                const uint32_t d = tmem + 256 + x * 128, a = tmem + x * 128 + (t & 1) * 64;
+                const uint32_t a = t_sx + (t & 1) * 64;
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kKeys / 16; ++ks)
-                        tc_mma_ts(d, a + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
+                        if (!(p.debug_flags & 2)) tc_mma_ts(t_o, a + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
                                   (t > 0 || ks > 0) ? 1u : 0u);
                     tc_commit(smem_u32(&ctrl->pv_done[x]));
                     NPD_TRACE(1, 20 + x, t);
                 }
                 __syncwarp();
             };
-            auto commit = [&](uint64_t *bar) {
-                if (elect_one()) tc_commit(smem_u32(bar));
-                __syncwarp();
-            };
-            auto wait_all = [&](uint64_t *bar, uint32_t parity) {
-                const bool good = wait_or_abort(smem_u32(bar), parity, abort_flag, p.status);
-                return __all_sync(0xffffffffu, good);
-            };
 
-            // Prologue: the first two score tiles of each query tile (one per score buffer).
-            for (int t = 0; ok && t < 2 && t < n_kv; ++t) {
-                if (!(ok = wait_all(&ctrl->k_full[t], 0))) break;
+            // Prologue: the first two score tiles (one per score buffer).
+            for (int t = 0; ok && t < 2 && t < my_tiles; ++t) {
+                if (!(ok = wait_all(&ctrl->kv_full[t], 0))) break;
                 tc_fence_after();
-                for (int x = 0; x < 2; ++x)
-                    if (t < ntiles[x]) issue_s(x, t);
-                commit(&ctrl->k_empty[t]);
+                issue_s(t);
             }
             for (int t = 0; ok && t < n_kv; ++t) {
                 const int stage = t % kStages;
-                const bool ahead = t + 2 < n_kv;
-                if (!(ok = wait_all(&ctrl->v_full[stage], (t / kStages) & 1))) break;
-                if (ahead && !(ok = wait_all(&ctrl->k_full[(t + 2) % kStages], ((t + 2) / kStages) & 1))) break;
-#pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    if (t < ntiles[x]) {
-                        if (!(ok = wait_all(&ctrl->p_full[x][t & 1], (t >> 1) & 1))) break;
-                        tc_fence_after();
-                        issue_pv(x, t);
-                        // the score buffer that held P_X(t) is reused by S_X(t+2); MMAs execute in issue order
-                        if (t + 2 < ntiles[x]) issue_s(x, t + 2);
-                    }
+                if (t < my_tiles) {
+                    if (t + 2 < my_tiles && !(ok = wait_all(&ctrl->kv_full[(t + 2) % kStages], ((t + 2) / kStages) & 1))) break;
+                    if (!(ok = wait_all(&ctrl->p_full[x][t & 1], (t >> 1) & 1))) break;
+                    tc_fence_after();
+                    issue_pv(t);
+                    // the score buffer that held P_X(t) is reused by S_X(t+2); MMAs execute in issue order
+                    if (t + 2 < my_tiles) issue_s(t + 2);
+                } else {
+                    // a key tile only the other query tile needs: observe it so that ring phases stay in step
+                    if (!(ok = wait_all(&ctrl->kv_full[stage], (t / kStages) & 1))) break;
                 }
-                if (!ok) break;
-                commit(&ctrl->v_empty[stage]);
-                if (ahead) commit(&ctrl->k_empty[(t + 2) % kStages]);
+                commit(&ctrl->kv_empty[stage]);      // our reads of K(t) and V(t) are (or will be) complete
             }
         }
-    } else if (warp >= 10) {
+    } else if (warp >= 11) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
@@ -494,121 +466,149 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
 
-        for (int t = 0; ok && t < my_tiles; ++t) {
-            const int stage = t % kStages, buf = t & 1;
-            const int key0 = t * kKeys;
-            const uint32_t t_s = t_sx + buf * 64;
-            // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
-            // there cannot meet a NaN.  Both softmax groups do it (idempotent) before releasing their P.
-            if (key0 + kKeys > ctx_end) {
-                if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (t / kStages) & 1, abort_flag, p.status))) break;
-                uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
-                const int first = max(ctx_end - key0, 0);
-                const int cnt = (kKeys - first) * 16;            // 16-byte pieces: 2 halves x 8 per row
-                for (int idx = threadIdx.x & 127; idx < cnt; idx += 128) {
-                    const int r = first + idx / 16, piece = idx % 16;
-                    *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kKvHalfBytes + r * 128 + ((piece & 7) << 4)) =
-                        make_uint4(0, 0, 0, 0);
-                }
-                fence_proxy_async_smem();
-            }
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 1, t);
-            if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x][buf]), (t >> 1) & 1, abort_flag, p.status))) break;
+        // Software pipeline: the scores of key tile t+1 are fetched from TMEM while the probabilities of
+        // tile t are still on their way back (the score MMAs run two tiles ahead of the softmax).
+        float sc[2][2][32];                                      // [parity of t][32-column chunk][column]
+        if (my_tiles > 0) {
+            ok = wait_or_abort(smem_u32(&ctrl->s_full[x][0]), 0, abort_flag, p.status);
             tc_fence_after();
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 2, t);
-
-            // The score row of this key tile (64 fp32) stays in registers until the packed store.
-            float sc[2][32];
-#pragma unroll
-            for (int cc = 0; cc < 2; ++cc) tmem_ld32(t_s + cc * 32, sc[cc]);
-            tmem_wait_ld();
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 3, t);
-            if (key0 + kKeys - 1 > start + tok0[x]) {   // only tiles that reach past the first row's diagonal
-#pragma unroll
-                for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (key0 + cc * 32 + i > pos) sc[cc][i] = -INFINITY;
+            if (ok) {
+                tmem_ld32(t_sx, sc[0][0]);
+                tmem_ld32(t_sx + 32, sc[0][1]);
             }
-            // ---- row maximum: four independent chains of three-input max ----
-            float mxa[4];
+        }
+#pragma unroll 1
+        for (int t2 = 0; ok && t2 < my_tiles; t2 += 2) {
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) mxa[q4] = fmaxf(sc[q4 >> 1][(q4 & 1) * 16], sc[q4 >> 1][(q4 & 1) * 16 + 1]);
+            for (int par = 0; par < 2; ++par) {
+                const int t = t2 + par;
+                if (t >= my_tiles) break;
+                const int stage = t % kStages;
+                const int key0 = t * kKeys;
+                const uint32_t t_s = t_sx + par * 64;
+                // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
+                // there cannot meet a NaN.  Both softmax groups do it (idempotent) before releasing their P.
+                if (key0 + kKeys > ctx_end) {
+                    if (!(ok = wait_or_abort(smem_u32(&ctrl->kv_full[stage]), (t / kStages) & 1, abort_flag, p.status))) break;
+                    uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
+                    const int first = max(ctx_end - key0, 0);
+                    const int cnt = (kKeys - first) * 16;        // 16-byte pieces: 2 halves x 8 per row
+                    for (int idx = threadIdx.x & 127; idx < cnt; idx += 128) {
+                        const int r = first + idx / 16, piece = idx % 16;
+                        *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kKvHalfBytes + r * 128 + ((piece & 7) << 4)) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async_smem();
+                }
+                tmem_wait_ld();                                  // scores of tile t are in sc[par]
+                if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 3, t);
+                // Fetch the next tile's scores right away when they are already there (the usual case) ...
+                bool fetched = t + 1 >= my_tiles;
+                if (!fetched && __all_sync(0xffffffffu, mbar_test(smem_u32(&ctrl->s_full[x][par ^ 1]), ((t + 1) >> 1) & 1))) {
+                    tc_fence_after();
+                    tmem_ld32(t_sx + (par ^ 1) * 64, sc[par ^ 1][0]);
+                    tmem_ld32(t_sx + (par ^ 1) * 64 + 32, sc[par ^ 1][1]);
+                    fetched = true;
+                }
+                if (p.debug_flags & 1) {
+                    if (!fetched) { if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x][par ^ 1]), ((t + 1) >> 1) & 1, abort_flag, p.status))) break; tc_fence_after(); tmem_ld32(t_sx + (par ^ 1) * 64, sc[par ^ 1][0]); tmem_ld32(t_sx + (par ^ 1) * 64 + 32, sc[par ^ 1][1]); }
+                    if (t > 0 && !(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (t - 1) & 1, abort_flag, p.status))) break;
+                    tmem_wait_st(); tc_fence_before(); mbar_arrive(smem_u32(&ctrl->p_full[x][par]));
+                    l_run = 1.f;
+                    continue;
+                }
+                if (key0 + kKeys - 1 > start + tok0[x]) {        // only tiles that reach past the first row's diagonal
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
+                    for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (key0 + cc * 32 + i > pos) sc[par][cc][i] = -INFINITY;
+                }
+                // ---- row maximum: four independent chains of three-input max ----
+                float mxa[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    mxa[q4] = fmaxf(sc[par][q4 >> 1][(q4 & 1) * 16], sc[par][q4 >> 1][(q4 & 1) * 16 + 1]);
 #pragma unroll
                 for (int i = 2; i < 16; i += 2)
-                    mxa[q4] = fmax3(mxa[q4], sc[q4 >> 1][(q4 & 1) * 16 + i], sc[q4 >> 1][(q4 & 1) * 16 + i + 1]);
-            const float m_new = fmax3(fmaxf(mxa[0], mxa[1]), mxa[2], mxa[3]) * p.scale_log2;
-            if (t == 0) {
-                m_run = m_new;                                  // key 0 is visible to every row: finite
-            } else {
-                // Lazy correction: O (in TMEM) and l are rescaled only when some row's maximum grew by more
-                // than 2^8; otherwise the stale maximum keeps every probability below 256, exactly cancelled
-                // by the final division.
-                const bool grow = m_new > m_run + kRescaleThreshold;
-                if (__any_sync(0xffffffffu, grow)) {
-                    const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
-                    if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (t - 1) & 1, abort_flag, p.status))) break;
-                    tc_fence_after();
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        mxa[q4] = fmax3(mxa[q4], sc[par][q4 >> 1][(q4 & 1) * 16 + i], sc[par][q4 >> 1][(q4 & 1) * 16 + i + 1]);
+                const float m_new = fmax3(fmaxf(mxa[0], mxa[1]), mxa[2], mxa[3]) * p.scale_log2;
+                if (t == 0) {
+                    m_run = m_new;                              // key 0 is visible to every row: finite
+                } else {
+                    // Lazy correction: O (in TMEM) and l are rescaled only when some row's maximum grew by
+                    // more than 2^8; otherwise the stale maximum keeps every probability below 256, exactly
+                    // cancelled by the final division.
+                    const bool grow = m_new > m_run + kRescaleThreshold;
+                    if (__any_sync(0xffffffffu, grow)) {
+                        const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
+                        if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (t - 1) & 1, abort_flag, p.status))) break;
+                        tc_fence_after();
 #pragma unroll 1
-                    for (int cc = 0; cc < 4; ++cc) {
-                        float o[32];
-                        tmem_ld32(t_o + cc * 32, o);
-                        tmem_wait_ld();
+                        for (int cc = 0; cc < 4; ++cc) {
+                            float o[32];
+                            tmem_ld32(t_o + cc * 32, o);
+                            tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= alpha;
-                        tmem_st32(t_o + cc * 32, o);
-                    }
-                    tmem_wait_st();
-                    if (grow) {
-                        l_run *= alpha;
-                        m_run = m_new;
+                            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                            tmem_st32(t_o + cc * 32, o);
+                        }
+                        tmem_wait_st();
+                        if (grow) {
+                            l_run *= alpha;
+                            m_run = m_new;
+                        }
                     }
                 }
-            }
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 4, t);
-            // ---- probabilities in place (masked scores are -inf -> 0), packed in pairs over the score columns ----
-            const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
-            const uint64_t negm2 = pack_f32x2(-m_run, -m_run);
-            uint64_t acc2[2] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
+                if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 4, t);
+                // ---- probabilities (masked scores are -inf -> 0), packed in pairs over the score columns ----
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+                const float2 negm2 = make_float2(-m_run, -m_run);
+                float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                uint32_t packed[16];
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t packed[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const uint64_t x2 = fma_f32x2(pack_f32x2(sc[cc][i], sc[cc][i + 1]), scale2, negm2);
-                    float p0, p1;
-                    if (((i >> 1) & 7) < kPolyPairsOf8) {       // compile-time pattern: some pairs avoid the SFU
-                        exp2_poly_pair(x2, p0, p1);
-                    } else {
-                        float x0, x1;
-                        unpack_f32x2(x2, x0, x1);
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float2 xs = __ffma2_rn(make_float2(sc[par][cc][i], sc[par][cc][i + 1]), scale2, negm2);
+                        float2 pr;
+                        if (((i >> 1) & 7) < kPolyPairsOf8) {   // compile-time pattern: some pairs avoid the SFU
+                            pr = exp2_poly_pair(xs);
+                        } else {
+                            pr = make_float2(fast_exp2(xs.x), fast_exp2(xs.y));
+                        }
+                        acc2[(i >> 1) & 1] = __fadd2_rn(acc2[(i >> 1) & 1], pr);
+                        packed[i >> 1] = Elem<T>::pack2(pr.x, pr.y);
                     }
-                    acc2[(i >> 1) & 1] = add_f32x2(acc2[(i >> 1) & 1], pack_f32x2(p0, p1));
-                    packed[i >> 1] = Elem<T>::pack2(p0, p1);
+                    tmem_st16(t_s + cc * 16, packed);
                 }
-                tmem_st16(t_s + cc * 16, packed);
+                l_run += (acc2[0].x + acc2[1].x) + (acc2[0].y + acc2[1].y);
+                if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 5, t);
+                // ---- ... otherwise fetch them now, before waiting for our own stores to land ----
+                if (!fetched) {
+                    if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x][par ^ 1]), ((t + 1) >> 1) & 1, abort_flag, p.status)))
+                        break;
+                    tc_fence_after();
+                    tmem_ld32(t_sx + (par ^ 1) * 64, sc[par ^ 1][0]);
+                    tmem_ld32(t_sx + (par ^ 1) * 64 + 32, sc[par ^ 1][1]);
+                }
+                // Observe every completion of pv_done in order (the PV MMAs of tile t-1 were issued a whole tile
+                // ago, so this does not wait in practice): a parity wait is only unambiguous while the barrier is
+                // at most one phase ahead, and PV(t) cannot start before the arrival below.
+                if (t > 0 && !(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (t - 1) & 1, abort_flag, p.status))) break;
+                tmem_wait_st();
+                tc_fence_before();           // P is in TMEM, S has been read: the MMA warp may go on
+                mbar_arrive(smem_u32(&ctrl->p_full[x][par]));
+                if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 6, t);
             }
-            float lsum0, lsum1, lsum2, lsum3;
-            unpack_f32x2(acc2[0], lsum0, lsum1);
-            unpack_f32x2(acc2[1], lsum2, lsum3);
-            l_run += (lsum0 + lsum2) + (lsum1 + lsum3);
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 5, t);
-            tmem_wait_st();
-            tc_fence_before();               // P is in TMEM, S has been read: the MMA warp may go on
-            mbar_arrive(smem_u32(&ctrl->p_full[x][buf]));
-            if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 6, t);
         }
 
         // ---- epilogue: O / l -> out ----
         if (ok && my_tiles > 0) {
-            // The softmax may be up to two key tiles ahead of the PV MMAs, so a single parity wait could be
-            // satisfied by an older phase: observe the last two completions in order.
-            if (my_tiles > 1) ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (my_tiles - 2) & 1, abort_flag, p.status);
-            if (ok) ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (my_tiles - 1) & 1, abort_flag, p.status);
+            // every earlier completion of pv_done has been observed in the loop: this is the next one
+            ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (my_tiles - 1) & 1, abort_flag, p.status);
             if (ok) {
                 tc_fence_after();
                 const bool store = tq_idx < tq_valid[x] && row < p.tq * p.group;
@@ -657,7 +657,6 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                                            int64_t num_blocks, int64_t cache_block_stride, int64_t bt_row_stride,
                                            int dtype, void *workspace, size_t workspace_bytes, int flags,
                                            void *stream) {
-    (void)flags;
     NPD_REQUIRE(dtype == NPD_DTYPE_F16 || dtype == NPD_DTYPE_BF16, NPD_ERR_UNSUPPORTED,
                 "prefill attention supports float16 and bfloat16 only (dtype code %d)", dtype);
     NPD_REQUIRE(head_dim == kD, NPD_ERR_UNSUPPORTED, "prefill attention: head_dim %lld is not 128", (long long)head_dim);
@@ -727,6 +726,7 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
         p.num_blocks = static_cast<int>(num_blocks);
         p.bt_row_stride = bt_row_stride;
+        p.debug_flags = flags;
 #ifdef NPD_PREFILL_TRACE
         p.trace = workspace_bytes >= 256 + 4 * 4096 * sizeof(long long)
                       ? reinterpret_cast<long long *>(static_cast<uint8_t *>(workspace) + 256) : nullptr;

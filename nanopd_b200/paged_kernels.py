@@ -214,7 +214,7 @@ def paged_attention_forward(out, query, key_cache, value_cache, block_tables, se
 def paged_prefill_attention(out, query, key_cache, value_cache, block_tables,
                             chunk_q_offsets: Sequence[int], chunk_tokens: Sequence[int],
                             chunk_starts: Sequence[int], scale: float, block_size: int,
-                            max_num_blocks_per_seq: int) -> None:
+                            max_num_blocks_per_seq: int, _flags: int = 0) -> None:
     """Causal attention of prompt chunks over their paged K/V (the chunk's own rows included).
 
     Replaces the prefill branch of ``paged_forward`` (nanoPD/engine/model_runner.py:152-169).
@@ -255,7 +255,7 @@ def paged_prefill_attention(out, query, key_cache, value_cache, block_tables,
             out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
             block_tables.data_ptr(), arr(*chunk_q_offsets), arr(*chunk_tokens), arr(*chunk_starts),
             nchunks, float(scale), hq, hkv, d, bs, max_blk, nb, cstride, block_tables.stride(0),
-            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(), 0, handle))
+            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(), int(_flags), handle))
 
 
 # ---------------------------------------------------------------------------
