@@ -37,9 +37,9 @@ constexpr int kQTileBytes = 2 * kQHalfBytes;        // 32 KiB
 constexpr int kKvHalfBytes = kKeys * 128;           // one 64-element half of a 64-key K or V tile
 constexpr int kKvTileBytes = 2 * kKvHalfBytes;      // 16 KiB
 constexpr int kStages = 4;                          // K ring and V ring depth
-constexpr int kTmemCols = 512;     // per query tile X: two 64-column score buffers, then O_A | O_B (128 each);
-                                   // the packed probabilities of a key tile alias its score buffer
-constexpr int kPolyPairsOf8 = 2;           // of every 8 score pairs, this many take the polynomial exp2
+constexpr int kTmemCols = 512;     // per query tile X (128 columns): scores S (64) | P buffer 0 (32) | P buffer 1 (32);
+                                   // then O_A | O_B (128 each)
+constexpr int kPolyPairsOf8 = 0;           // of every 8 score pairs, this many take the polynomial exp2
 constexpr float kRescaleThreshold = 8.f;   // log2 units: O is rescaled only when a row max grows by more
 constexpr long long kWaitCycles = 4000000000LL;
 
@@ -182,19 +182,6 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_ma
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-// Non-blocking phase test (try_wait may suspend the thread for a while; this never does).
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
 // Bounded, abortable mbarrier wait shared by all roles.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                               int32_t *status) {
@@ -232,16 +219,57 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 #endif
 
 struct alignas(8) SmemCtrl {
-    uint64_t q_full;
+    uint64_t q_full;             // both query tiles of the current work item have landed
+    uint64_t q_empty;            // both MMA warps have issued their last score MMA of the item (2 arrivals)
     uint64_t kv_full[kStages];   // K and V tile of a ring stage have landed
     uint64_t kv_empty[kStages];  // both MMA warps are done with the stage (2 arrivals)
-    uint64_t s_full[2][2];  // [query tile][score buffer]: the score tile is in TMEM
-    uint64_t p_full[2][2];  // [query tile][score buffer]: its probabilities are in TMEM (128 arrivals)
-    uint64_t pv_done[2];    // the PV MMAs of query tile X for one more key tile have completed
+    uint64_t s_full[2];     // [query tile]: the score tile of the next key tile is in TMEM
+    uint64_t s_read[2];     // [query tile]: the softmax threads hold it in registers (128 arrivals)
+    uint64_t p_full[2][2];  // [query tile][P buffer]: the probabilities are in TMEM (128 arrivals)
+    uint64_t pv_done[2][2]; // [query tile][P buffer]: the PV MMAs that read the buffer have completed
+    uint64_t o_free[2];     // [query tile]: the epilogue has taken O out of TMEM (128 arrivals)
     uint32_t tmem_base;
     int abort_flag;
 };
 
+// One work item = a pair of 128-row query tiles of one chunk and one kv head.
+struct Item {
+    int c, h;
+    int start, qoff, ctx_end;
+    int tok0[2], tq_valid[2], ntiles[2];
+    int n_kv;
+};
+
+// Items are numbered (chunk-major, later = heavier pairs of a chunk first, then kv head); `c_hint` only grows.
+__device__ __forceinline__ Item decode_item(const PrefillParams &p, int item, int &c_hint) {
+    Item it;
+    it.h = item % p.num_kv_heads;
+    const int rank = item / p.num_kv_heads;
+    int c = c_hint;
+    while (c + 1 < p.num_chunks && p.cta_prefix[c + 1] <= rank) ++c;
+    c_hint = c;
+    it.c = c;
+    const int pairs = p.cta_prefix[c + 1] - p.cta_prefix[c];
+    const int pair = pairs - 1 - (rank - p.cta_prefix[c]);     // later tiles of a chunk see more keys: first
+    const int n_tok = p.chunk_tokens[c];
+    it.start = p.chunk_start[c];
+    it.qoff = p.chunk_q_offset[c];
+    it.ctx_end = it.start + n_tok;                              // keys written so far for this sequence
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        it.tok0[x] = (2 * pair + x) * p.tq;
+        it.tq_valid[x] = max(0, min(p.tq, n_tok - it.tok0[x]));
+        // keys [0, start + tok0 + tq_valid) are visible to the tile
+        it.ntiles[x] = it.tq_valid[x] > 0 ? (it.start + it.tok0[x] + it.tq_valid[x] + kKeys - 1) / kKeys : 0;
+    }
+    it.n_kv = max(it.ntiles[0], it.ntiles[1]);
+    return it;
+}
+
+// Persistent kernel: one CTA per SM walks the work items blockIdx.x, blockIdx.x + gridDim.x, ...  All
+// barrier phases are driven by running counters, so the producer already loads the next item's K/V tiles
+// (and, once the last score MMA has been issued, its query tiles) while the current item drains, and the
+// epilogue of an item overlaps the first MMAs of the next one.
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
@@ -256,39 +284,23 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStages * kKvTileBytes);
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-
-    // ---- which pair of query tiles is mine ----
-    const int h = blockIdx.x % p.num_kv_heads;
-    const int rank = blockIdx.x / p.num_kv_heads;
-    int c = 0;
-    while (c + 1 < p.num_chunks && p.cta_prefix[c + 1] <= rank) ++c;
-    const int ctas_in_chunk = p.cta_prefix[c + 1] - p.cta_prefix[c];
-    // later tiles of a chunk see more keys: hand them out first
-    const int pair = ctas_in_chunk - 1 - (rank - p.cta_prefix[c]);
-    const int n_tok = p.chunk_tokens[c], start = p.chunk_start[c], qoff = p.chunk_q_offset[c];
-    const int ctx_end = start + n_tok;                        // keys written so far for this sequence
-    int tok0[2], tq_valid[2], ntiles[2];
-#pragma unroll
-    for (int x = 0; x < 2; ++x) {
-        tok0[x] = (2 * pair + x) * p.tq;
-        tq_valid[x] = max(0, min(p.tq, n_tok - tok0[x]));
-        // keys [0, start + tok0 + tq_valid) are visible to the tile
-        ntiles[x] = tq_valid[x] > 0 ? (start + tok0[x] + tq_valid[x] + kKeys - 1) / kKeys : 0;
-    }
-    const int n_kv = max(ntiles[0], ntiles[1]);
+    const int total_items = p.cta_prefix[p.num_chunks] * p.num_kv_heads;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&ctrl->q_full), 1);
+        mbar_init(smem_u32(&ctrl->q_empty), 2);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
             mbar_init(smem_u32(&ctrl->kv_empty[i]), 2);
         }
         for (int x = 0; x < 2; ++x) {
+            mbar_init(smem_u32(&ctrl->s_full[x]), 1);
+            mbar_init(smem_u32(&ctrl->s_read[x]), 128);
+            mbar_init(smem_u32(&ctrl->o_free[x]), 128);
             for (int b = 0; b < 2; ++b) {
-                mbar_init(smem_u32(&ctrl->s_full[x][b]), 1);
                 mbar_init(smem_u32(&ctrl->p_full[x][b]), 128);
+                mbar_init(smem_u32(&ctrl->pv_done[x][b]), 1);
             }
-            mbar_init(smem_u32(&ctrl->pv_done[x]), 1);
         }
         ctrl->abort_flag = 0;
         mbar_fence_init();
@@ -304,7 +316,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     volatile int *abort_flag = &ctrl->abort_flag;
 
     // Register re-allocation between warpgroups (first statement of every role): the two softmax groups
-    // work on whole score rows in registers, the third group (TMA, MMA, two idle warps) needs few.
+    // work on whole score rows in registers, the third group (TMA, two MMA warps, one idle warp) needs few.
     if (warp == 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         // =========================== TMA producer (whole warp issues) ===========================
@@ -315,56 +327,66 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
-            // Query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch
-            const uint32_t qbar = smem_u32(&ctrl->q_full);
-            const int nq = (tq_valid[0] > 0 ? 1 : 0) + (tq_valid[1] > 0 ? 1 : 0);
-            mbar_expect_tx(qbar, static_cast<uint32_t>(nq * 2 * p.tq * p.group * 128));
-            for (int x = 0; x < 2; ++x) {
-                if (tq_valid[x] <= 0) continue;
-                for (int hf = 0; hf < 2; ++hf)
-                    tma_load_3d(smem_u32(q_tiles + x * kQTileBytes + hf * kQHalfBytes), &tm_q, qbar, hf * 64,
-                                h * p.group, qoff + tok0[x]);
-            }
         }
-        const int32_t *table = p.block_tables + (long long)c * p.bt_row_stride;
         const int role = lane >> 3, gi = (lane >> 1) & 3, hf = lane & 1;     // role 0 = K, 1 = V, others idle
         const CUtensorMap *tm = role == 1 ? &tm_v : &tm_k;
-        auto lookup = [&](int t) {
-            const int key = t * kKeys + gi * 16;
-            int id = 0;
-            if (role < 2 && t < n_kv && key < ctx_end) {
-                id = __ldg(table + key / p.block_size);
-                if (id < 0 || id >= p.num_blocks) {
-                    atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
-                    id = p.num_blocks;                // out of bounds for the tensor map: zero fill
+        int c_hint = 0, g = 0;                                  // g: key tiles loaded so far (ring position)
+        bool ok = true;
+        for (int k = 0, item = blockIdx.x; ok && item < total_items; ++k, item += gridDim.x) {
+            const Item it = decode_item(p, item, c_hint);
+            // ---- query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch
+            if (k > 0) ok = wait_or_abort(smem_u32(&ctrl->q_empty), (k - 1) & 1, abort_flag, p.status);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            if (lane == 0) {
+                const uint32_t qbar = smem_u32(&ctrl->q_full);
+                const int nq = (it.tq_valid[0] > 0 ? 1 : 0) + (it.tq_valid[1] > 0 ? 1 : 0);
+                mbar_expect_tx(qbar, static_cast<uint32_t>(nq * 2 * p.tq * p.group * 128));
+                for (int x = 0; x < 2; ++x) {
+                    if (it.tq_valid[x] <= 0) continue;
+                    for (int h2 = 0; h2 < 2; ++h2)
+                        tma_load_3d(smem_u32(q_tiles + x * kQTileBytes + h2 * kQHalfBytes), &tm_q, qbar, h2 * 64,
+                                    it.h * p.group, it.qoff + it.tok0[x]);
                 }
             }
-            return id;
-        };
-        int id_next = lookup(0);
-        bool ok = true;
-        for (int t = 0; t < n_kv; ++t) {
-            const int stage = t % kStages;
-            const uint32_t par = ((t / kStages) - 1) & 1;
-            const int key0 = t * kKeys;
-            const int id = id_next;
-            id_next = lookup(t + 1);
-            // 16-key row groups holding at least one written key; the rest is never loaded
-            int ngroups = 0;
-            for (int g2 = 0; g2 < kKeys / 16; ++g2) ngroups += (key0 + g2 * 16 < ctx_end) ? 1 : 0;
-            const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
-            const int row = h * p.block_size + ((key0 + gi * 16) % p.block_size);
-            const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048);
-            if (t >= kStages) ok = wait_or_abort(smem_u32(&ctrl->kv_empty[stage]), par, abort_flag, p.status);
-            if (!__all_sync(0xffffffffu, ok)) break;
-            const uint32_t bar = smem_u32(&ctrl->kv_full[stage]);
-            if (lane == 0) {
-                NPD_TRACE(0, 1, t);
-                if (p.debug_flags & 4) mbar_arrive(bar); else mbar_expect_tx(bar, 2 * bytes);
+            const int32_t *table = p.block_tables + (long long)it.c * p.bt_row_stride;
+            auto lookup = [&](int t) {
+                const int key = t * kKeys + gi * 16;
+                int id = 0;
+                if (role < 2 && t < it.n_kv && key < it.ctx_end) {
+                    id = __ldg(table + key / p.block_size);
+                    if (id < 0 || id >= p.num_blocks) {
+                        atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
+                        id = p.num_blocks;            // out of bounds for the tensor map: zero fill
+                    }
+                }
+                return id;
+            };
+            int id_next = lookup(0);
+            for (int t = 0; t < it.n_kv; ++t, ++g) {
+                const int stage = g % kStages;
+                const int key0 = t * kKeys;
+                const int id = id_next;
+                id_next = lookup(t + 1);
+                // 16-key row groups holding at least one written key; the rest is never loaded
+                int ngroups = 0;
+                for (int g2 = 0; g2 < kKeys / 16; ++g2) ngroups += (key0 + g2 * 16 < it.ctx_end) ? 1 : 0;
+                const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
+                const int row = it.h * p.block_size + ((key0 + gi * 16) % p.block_size);
+                const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048);
+                if (g >= kStages)
+                    ok = wait_or_abort(smem_u32(&ctrl->kv_empty[stage]), ((g / kStages) - 1) & 1, abort_flag, p.status);
+                if (!__all_sync(0xffffffffu, ok)) break;
+                const uint32_t bar = smem_u32(&ctrl->kv_full[stage]);
+                if (lane == 0) {
+                    NPD_TRACE(0, 1, t);
+                    if (p.debug_flags & 4) mbar_arrive(bar); else mbar_expect_tx(bar, 2 * bytes);
+                }
+                __syncwarp();
+                if (!(p.debug_flags & 4) && role < 2 && gi < ngroups)
+                    tma_load_3d(smem_u32((role ? v_ring : k_ring) + (size_t)stage * kKvTileBytes) + off, tm, bar,
+                                hf * 64, row, id);
             }
-            __syncwarp();
-            if (!(p.debug_flags & 4) && role < 2 && gi < ngroups)
-                tma_load_3d(smem_u32((role ? v_ring : k_ring) + (size_t)stage * kKvTileBytes) + off, tm, bar, hf * 64, row, id);
+            ok = __all_sync(0xffffffffu, ok);
         }
     } else if (warp == 9 || warp == 10) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
@@ -373,7 +395,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         // lane issues the tcgen05 instructions.  Two issuers keep the two query tiles from blocking one another.
         {
             const int x = warp - 9;
-            const int my_tiles = ntiles[x];
             constexpr uint32_t fmt = Elem<T>::kDtype == NPD_DTYPE_BF16 ? 1u : 0u;
             constexpr uint32_t idesc_s = instr_desc(fmt, 0u, kRows, kKeys);
             constexpr uint32_t idesc_pv = instr_desc(fmt, 1u, kRows, kD);
@@ -385,68 +406,87 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (elect_one()) tc_commit(smem_u32(bar));
                 __syncwarp();
             };
-            bool ok = wait_all(&ctrl->q_full, 0);
-
             // Descriptors are built once; a k-step or a ring stage only adds a constant to the
             // start-address field (16-byte units).
             const uint64_t q_desc = desc_k_major(smem_u32(q_tiles) + x * kQTileBytes);
             const uint64_t k_desc0 = desc_k_major(smem_u32(k_ring));
             const uint64_t v_desc0 = desc_mn_major(smem_u32(v_ring), kKvHalfBytes);
             const uint32_t t_sx = tmem + x * 128, t_o = tmem + 256 + x * 128;
-            // S_X(t) = Q_X . K(t)^T into score buffer t&1 : 8 k-steps of 16 elements (32 B inside the
-            // swizzle atom; the second 64-element half starts one half-tile further on)
-            auto issue_s = [&](int t) {
-                const uint64_t kd = k_desc0 + static_cast<uint64_t>(((t % kStages) * kKvTileBytes) >> 4);
-                const uint32_t d = t_sx + (t & 1) * 64;
+            // S_X = Q_X . K^T of ring stage `stage`: 8 k-steps of 16 elements (32 B inside the swizzle atom;
+            // the second 64-element half starts one half-tile further on)
+            auto issue_s = [&](int stage) {
+                const uint64_t kd = k_desc0 + static_cast<uint64_t>((stage * kKvTileBytes) >> 4);
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kD / 16; ++ks) {
                         if (p.debug_flags & 2) break;
                         const uint64_t a_off = static_cast<uint64_t>(((ks >> 2) * kQHalfBytes + (ks & 3) * 32) >> 4);
                         const uint64_t b_off = static_cast<uint64_t>(((ks >> 2) * kKvHalfBytes + (ks & 3) * 32) >> 4);
-                        tc_mma_ss(d, q_desc + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
+                        tc_mma_ss(t_sx, q_desc + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
                     }
-                    tc_commit(smem_u32(&ctrl->s_full[x][t & 1]));
-                    NPD_TRACE(1 , 10 + x, t);
+                    tc_commit(smem_u32(&ctrl->s_full[x]));
                 }
                 __syncwarp();
             };
-            // O_X (+)= P_X(t) . V(t) : P from TMEM (packed pairs, 8 columns per 16 keys), V MN-major from
-            // shared memory (16 keys = two 8-row groups = 2 KiB further on)
-            auto issue_pv = [&](int t) {
-                const uint64_t vd = v_desc0 + static_cast<uint64_t>(((t % kStages) * kKvTileBytes) >> 4);
-                const uint32_t a = t_sx + (t & 1) * 64;
+            // O_X (+)= P_X . V of ring stage `stage`: P from TMEM buffer `buf` (packed pairs, 8 columns per
+            // 16 keys), V MN-major from shared memory (16 keys = two 8-row groups = 2 KiB further on)
+            auto issue_pv = [&](int stage, int buf, bool first) {
+                const uint64_t vd = v_desc0 + static_cast<uint64_t>((stage * kKvTileBytes) >> 4);
+                const uint32_t a = t_sx + 64 + buf * 32;
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kKeys / 16; ++ks)
-                        if (!(p.debug_flags & 2)) tc_mma_ts(t_o, a + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
-                                  (t > 0 || ks > 0) ? 1u : 0u);
-                    tc_commit(smem_u32(&ctrl->pv_done[x]));
-                    NPD_TRACE(1, 20 + x, t);
+                        if (!(p.debug_flags & 2))
+                            tc_mma_ts(t_o, a + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
+                                      (!first || ks > 0) ? 1u : 0u);
+                    tc_commit(smem_u32(&ctrl->pv_done[x][buf]));
                 }
                 __syncwarp();
             };
 
-            // Prologue: the first two score tiles (one per score buffer).
-            for (int t = 0; ok && t < 2 && t < my_tiles; ++t) {
-                if (!(ok = wait_all(&ctrl->kv_full[t], 0))) break;
-                tc_fence_after();
-                issue_s(t);
-            }
-            for (int t = 0; ok && t < n_kv; ++t) {
-                const int stage = t % kStages;
-                if (t < my_tiles) {
-                    if (t + 2 < my_tiles && !(ok = wait_all(&ctrl->kv_full[(t + 2) % kStages], ((t + 2) / kStages) & 1))) break;
-                    if (!(ok = wait_all(&ctrl->p_full[x][t & 1], (t >> 1) & 1))) break;
+            int c_hint = 0;
+            int g = 0;         // key tiles seen so far (ring position of the item's first key tile)
+            int cnt = 0;       // own key tiles processed so far (phases of s_full, s_read, p_full, pv_done)
+            int items_done = 0;   // items in which this query tile had work (phases of o_free)
+            bool ok = true;
+            for (int k = 0, item = blockIdx.x; ok && item < total_items; ++k, item += gridDim.x) {
+                const Item it = decode_item(p, item, c_hint);
+                const int my_tiles = it.ntiles[x];
+                if (!(ok = wait_all(&ctrl->q_full, k & 1))) break;
+                if (my_tiles > 0) {
+                    // the score columns are free once the softmax threads took the previous item's last tile
+                    if (cnt > 0 && !(ok = wait_all(&ctrl->s_read[x], (cnt - 1) & 1))) break;
+                    if (!(ok = wait_all(&ctrl->kv_full[g % kStages], (g / kStages) & 1))) break;
                     tc_fence_after();
-                    issue_pv(t);
-                    // the score buffer that held P_X(t) is reused by S_X(t+2); MMAs execute in issue order
-                    if (t + 2 < my_tiles) issue_s(t + 2);
-                } else {
-                    // a key tile only the other query tile needs: observe it so that ring phases stay in step
-                    if (!(ok = wait_all(&ctrl->kv_full[stage], (t / kStages) & 1))) break;
+                    issue_s(g % kStages);
                 }
-                commit(&ctrl->kv_empty[stage]);      // our reads of K(t) and V(t) are (or will be) complete
+                if (my_tiles <= 1) commit(&ctrl->q_empty);   // no further score MMA of this item reads Q_X
+                for (int t = 0; ok && t < it.n_kv; ++t) {
+                    const int gt = g + t, stage = gt % kStages;
+                    if (t < my_tiles) {
+                        const int ct = cnt + t;
+                        if (t + 1 < my_tiles) {
+                            // the next score tile may be computed as soon as the softmax threads have taken this one
+                            if (!(ok = wait_all(&ctrl->s_read[x], ct & 1))) break;
+                            if (!(ok = wait_all(&ctrl->kv_full[(gt + 1) % kStages], ((gt + 1) / kStages) & 1))) break;
+                            tc_fence_after();
+                            issue_s((gt + 1) % kStages);
+                            if (t + 2 == my_tiles) commit(&ctrl->q_empty);   // that was the last one
+                        }
+                        // O_X is overwritten by the first PV of an item: the previous epilogue must have read it
+                        if (t == 0 && items_done > 0 && !(ok = wait_all(&ctrl->o_free[x], (items_done - 1) & 1))) break;
+                        if (!(ok = wait_all(&ctrl->p_full[x][ct & 1], (ct >> 1) & 1))) break;
+                        tc_fence_after();
+                        issue_pv(stage, ct & 1, t == 0);
+                    } else {
+                        // a key tile only the other query tile needs: observe it so that ring phases stay in step
+                        if (!(ok = wait_all(&ctrl->kv_full[stage], (gt / kStages) & 1))) break;
+                    }
+                    commit(&ctrl->kv_empty[stage]);      // our reads of K and V of this stage are (or will be) complete
+                }
+                g += it.n_kv;
+                cnt += my_tiles;
+                items_done += my_tiles > 0 ? 1 : 0;
             }
         }
     } else if (warp >= 11) {
@@ -458,93 +498,82 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         const int wq = warp & 3;                                 // TMEM lane quarter this warp may touch
         const int row = wq * 32 + lane;                          // == TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-        const uint32_t t_sx = tmem + x * 128 + lane_base;        // score buffers, later the packed probabilities
+        const uint32_t t_sx = tmem + x * 128 + lane_base;        // scores (64 columns), then two P buffers (32 + 32)
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
-        const int pos = start + tok0[x] + tq_idx;                // last visible key of this row
-        const int my_tiles = ntiles[x];
-        float m_run = -INFINITY, l_run = 0.f;
+        int c_hint = 0, g = 0, cnt = 0;
         bool ok = true;
 
-        // Software pipeline: the scores of key tile t+1 are fetched from TMEM while the probabilities of
-        // tile t are still on their way back (the score MMAs run two tiles ahead of the softmax).
-        float sc[2][2][32];                                      // [parity of t][32-column chunk][column]
-        if (my_tiles > 0) {
-            ok = wait_or_abort(smem_u32(&ctrl->s_full[x][0]), 0, abort_flag, p.status);
-            tc_fence_after();
-            if (ok) {
-                tmem_ld32(t_sx, sc[0][0]);
-                tmem_ld32(t_sx + 32, sc[0][1]);
-            }
-        }
+        for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+            const Item it = decode_item(p, item, c_hint);
+            const int my_tiles = it.ntiles[x];
+            const int pos = it.start + it.tok0[x] + tq_idx;      // last visible key of this row
+            float m_run = -INFINITY, l_run = 0.f;
 #pragma unroll 1
-        for (int t2 = 0; ok && t2 < my_tiles; t2 += 2) {
-#pragma unroll
-            for (int par = 0; par < 2; ++par) {
-                const int t = t2 + par;
-                if (t >= my_tiles) break;
-                const int stage = t % kStages;
+            for (int t = 0; ok && t < my_tiles; ++t) {
+                const int ct = cnt + t, buf = ct & 1;
+                const int gt = g + t, stage = gt % kStages;
                 const int key0 = t * kKeys;
-                const uint32_t t_s = t_sx + par * 64;
+                const uint32_t t_p = t_sx + 64 + buf * 32;       // packed probabilities of this tile
                 // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
                 // there cannot meet a NaN.  Both softmax groups do it (idempotent) before releasing their P.
-                if (key0 + kKeys > ctx_end) {
-                    if (!(ok = wait_or_abort(smem_u32(&ctrl->kv_full[stage]), (t / kStages) & 1, abort_flag, p.status))) break;
+                if (key0 + kKeys > it.ctx_end) {
+                    if (!(ok = wait_or_abort(smem_u32(&ctrl->kv_full[stage]), (gt / kStages) & 1, abort_flag, p.status))) break;
                     uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
-                    const int first = max(ctx_end - key0, 0);
-                    const int cnt = (kKeys - first) * 16;        // 16-byte pieces: 2 halves x 8 per row
-                    for (int idx = threadIdx.x & 127; idx < cnt; idx += 128) {
+                    const int first = max(it.ctx_end - key0, 0);
+                    const int n16 = (kKeys - first) * 16;        // 16-byte pieces: 2 halves x 8 per row
+                    for (int idx = threadIdx.x & 127; idx < n16; idx += 128) {
                         const int r = first + idx / 16, piece = idx % 16;
                         *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kKvHalfBytes + r * 128 + ((piece & 7) << 4)) =
                             make_uint4(0, 0, 0, 0);
                     }
                     fence_proxy_async_smem();
                 }
-                tmem_wait_ld();                                  // scores of tile t are in sc[par]
-                if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 3, t);
-                // Fetch the next tile's scores right away when they are already there (the usual case) ...
-                bool fetched = t + 1 >= my_tiles;
-                if (!fetched && __all_sync(0xffffffffu, mbar_test(smem_u32(&ctrl->s_full[x][par ^ 1]), ((t + 1) >> 1) & 1))) {
-                    tc_fence_after();
-                    tmem_ld32(t_sx + (par ^ 1) * 64, sc[par ^ 1][0]);
-                    tmem_ld32(t_sx + (par ^ 1) * 64 + 32, sc[par ^ 1][1]);
-                    fetched = true;
-                }
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x]), ct & 1, abort_flag, p.status))) break;
+                tc_fence_after();
+                // The score row of this key tile (64 fp32) moves to registers; the score columns are then free
+                // for the next tile's MMA, which runs while this tile's probabilities are computed.
+                float sc[2][32];
+                tmem_ld32(t_sx, sc[0]);
+                tmem_ld32(t_sx + 32, sc[1]);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(smem_u32(&ctrl->s_read[x]));
                 if (p.debug_flags & 1) {
-                    if (!fetched) { if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x][par ^ 1]), ((t + 1) >> 1) & 1, abort_flag, p.status))) break; tc_fence_after(); tmem_ld32(t_sx + (par ^ 1) * 64, sc[par ^ 1][0]); tmem_ld32(t_sx + (par ^ 1) * 64 + 32, sc[par ^ 1][1]); }
-                    if (t > 0 && !(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (t - 1) & 1, abort_flag, p.status))) break;
-                    tmem_wait_st(); tc_fence_before(); mbar_arrive(smem_u32(&ctrl->p_full[x][par]));
+                    if (ct >= 2 && !(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][buf]), ((ct - 2) >> 1) & 1, abort_flag, p.status))) break;
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&ctrl->p_full[x][buf]));
                     l_run = 1.f;
                     continue;
                 }
-                if (key0 + kKeys - 1 > start + tok0[x]) {        // only tiles that reach past the first row's diagonal
+                if (key0 + kKeys - 1 > it.start + it.tok0[x]) {  // only tiles that reach past the first row's diagonal
 #pragma unroll
                     for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (key0 + cc * 32 + i > pos) sc[par][cc][i] = -INFINITY;
+                            if (key0 + cc * 32 + i > pos) sc[cc][i] = -INFINITY;
                 }
                 // ---- row maximum: four independent chains of three-input max ----
                 float mxa[4];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4)
-                    mxa[q4] = fmaxf(sc[par][q4 >> 1][(q4 & 1) * 16], sc[par][q4 >> 1][(q4 & 1) * 16 + 1]);
+                for (int q4 = 0; q4 < 4; ++q4) mxa[q4] = fmaxf(sc[q4 >> 1][(q4 & 1) * 16], sc[q4 >> 1][(q4 & 1) * 16 + 1]);
 #pragma unroll
                 for (int i = 2; i < 16; i += 2)
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4)
-                        mxa[q4] = fmax3(mxa[q4], sc[par][q4 >> 1][(q4 & 1) * 16 + i], sc[par][q4 >> 1][(q4 & 1) * 16 + i + 1]);
+                        mxa[q4] = fmax3(mxa[q4], sc[q4 >> 1][(q4 & 1) * 16 + i], sc[q4 >> 1][(q4 & 1) * 16 + i + 1]);
                 const float m_new = fmax3(fmaxf(mxa[0], mxa[1]), mxa[2], mxa[3]) * p.scale_log2;
                 if (t == 0) {
                     m_run = m_new;                              // key 0 is visible to every row: finite
                 } else {
-                    // Lazy correction: O (in TMEM) and l are rescaled only when some row's maximum grew by
-                    // more than 2^8; otherwise the stale maximum keeps every probability below 256, exactly
-                    // cancelled by the final division.
+                    // Lazy correction: O (in TMEM) and l are rescaled only when some row's maximum grew by more
+                    // than 2^8; otherwise the stale maximum keeps every probability below 256, exactly cancelled
+                    // by the final division.
                     const bool grow = m_new > m_run + kRescaleThreshold;
                     if (__any_sync(0xffffffffu, grow)) {
                         const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
-                        if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (t - 1) & 1, abort_flag, p.status))) break;
+                        // every PV up to tile t-1 must have landed in O: PV(t-1) is the newest, PV(t-2) precedes it
+                        if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][buf ^ 1]), ((ct - 1) >> 1) & 1, abort_flag, p.status))) break;
                         tc_fence_after();
 #pragma unroll 1
                         for (int cc = 0; cc < 4; ++cc) {
@@ -562,8 +591,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         }
                     }
                 }
-                if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 4, t);
-                // ---- probabilities (masked scores are -inf -> 0), packed in pairs over the score columns ----
+                // The P buffer of this tile was last read by the PV MMAs two tiles ago.  (Each pv_done barrier sees
+                // every second tile, so a parity wait on it is never more than one phase behind.)
+                if (ct >= 2 && !(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][buf]), ((ct - 2) >> 1) & 1, abort_flag, p.status))) break;
+                // ---- probabilities (masked scores are -inf -> 0), packed in pairs ----
                 const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
                 const float2 negm2 = make_float2(-m_run, -m_run);
                 float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
@@ -572,7 +603,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     uint32_t packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float2 xs = __ffma2_rn(make_float2(sc[par][cc][i], sc[par][cc][i + 1]), scale2, negm2);
+                        const float2 xs = __ffma2_rn(make_float2(sc[cc][i], sc[cc][i + 1]), scale2, negm2);
                         float2 pr;
                         if (((i >> 1) & 7) < kPolyPairsOf8) {   // compile-time pattern: some pairs avoid the SFU
                             pr = exp2_poly_pair(xs);
@@ -582,57 +613,54 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         acc2[(i >> 1) & 1] = __fadd2_rn(acc2[(i >> 1) & 1], pr);
                         packed[i >> 1] = Elem<T>::pack2(pr.x, pr.y);
                     }
-                    tmem_st16(t_s + cc * 16, packed);
+                    tmem_st16(t_p + cc * 16, packed);
                 }
                 l_run += (acc2[0].x + acc2[1].x) + (acc2[0].y + acc2[1].y);
-                if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 5, t);
-                // ---- ... otherwise fetch them now, before waiting for our own stores to land ----
-                if (!fetched) {
-                    if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x][par ^ 1]), ((t + 1) >> 1) & 1, abort_flag, p.status)))
-                        break;
-                    tc_fence_after();
-                    tmem_ld32(t_sx + (par ^ 1) * 64, sc[par ^ 1][0]);
-                    tmem_ld32(t_sx + (par ^ 1) * 64 + 32, sc[par ^ 1][1]);
-                }
-                // Observe every completion of pv_done in order (the PV MMAs of tile t-1 were issued a whole tile
-                // ago, so this does not wait in practice): a parity wait is only unambiguous while the barrier is
-                // at most one phase ahead, and PV(t) cannot start before the arrival below.
-                if (t > 0 && !(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (t - 1) & 1, abort_flag, p.status))) break;
                 tmem_wait_st();
-                tc_fence_before();           // P is in TMEM, S has been read: the MMA warp may go on
-                mbar_arrive(smem_u32(&ctrl->p_full[x][par]));
-                if (threadIdx.x == x * 128) NPD_TRACE(2 + x, 6, t);
+                tc_fence_before();           // P is in TMEM: the MMA warp may issue the PV MMAs of this tile
+                mbar_arrive(smem_u32(&ctrl->p_full[x][buf]));
             }
-        }
 
-        // ---- epilogue: O / l -> out ----
-        if (ok && my_tiles > 0) {
-            // every earlier completion of pv_done has been observed in the loop: this is the next one
-            ok = wait_or_abort(smem_u32(&ctrl->pv_done[x]), (my_tiles - 1) & 1, abort_flag, p.status);
-            if (ok) {
-                tc_fence_after();
-                const bool store = tq_idx < tq_valid[x] && row < p.tq * p.group;
-                const float inv = 1.f / l_run;
-                T *dst = static_cast<T *>(p.out) +
-                         ((long long)(qoff + tok0[x] + tq_idx) * p.num_q_heads + (long long)h * p.group + hg) * kD;
+            // ---- epilogue: O / l -> out ----
+            if (ok && my_tiles > 0) {
+                // the last PV on each P buffer (earlier completions of both barriers were observed in the loop)
+                const int ce = cnt + my_tiles;
+                if (ce >= 2)
+                    ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][(ce - 2) & 1]), ((ce - 2) >> 1) & 1, abort_flag, p.status);
+                if (ok)
+                    ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][(ce - 1) & 1]), ((ce - 1) >> 1) & 1, abort_flag, p.status);
+                if (ok) {
+                    tc_fence_after();
+                    const bool store = tq_idx < it.tq_valid[x] && row < p.tq * p.group;
+                    const float inv = 1.f / l_run;
+                    T *dst = static_cast<T *>(p.out) +
+                             ((long long)(it.qoff + it.tok0[x] + tq_idx) * p.num_q_heads + (long long)it.h * p.group + hg) * kD;
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    float o[32];
-                    tmem_ld32(t_o + cc * 32, o);
-                    tmem_wait_ld();
-                    if (store) {
+                    for (int cc = 0; cc < 4; ++cc) {
+                        float o[32];
+                        tmem_ld32(t_o + cc * 32, o);
+                        tmem_wait_ld();
+                        if (cc == 3) {
+                            // O is in registers: the next item's first PV may overwrite the accumulator
+                            tc_fence_before();
+                            mbar_arrive(smem_u32(&ctrl->o_free[x]));
+                        }
+                        if (store) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 w;
-                            w.x = Elem<T>::pack2(o[i] * inv, o[i + 1] * inv);
-                            w.y = Elem<T>::pack2(o[i + 2] * inv, o[i + 3] * inv);
-                            w.z = Elem<T>::pack2(o[i + 4] * inv, o[i + 5] * inv);
-                            w.w = Elem<T>::pack2(o[i + 6] * inv, o[i + 7] * inv);
-                            *reinterpret_cast<uint4 *>(dst + cc * 32 + i) = w;
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 w;
+                                w.x = Elem<T>::pack2(o[i] * inv, o[i + 1] * inv);
+                                w.y = Elem<T>::pack2(o[i + 2] * inv, o[i + 3] * inv);
+                                w.z = Elem<T>::pack2(o[i + 4] * inv, o[i + 5] * inv);
+                                w.w = Elem<T>::pack2(o[i + 6] * inv, o[i + 7] * inv);
+                                *reinterpret_cast<uint4 *>(dst + cc * 32 + i) = w;
+                            }
                         }
                     }
                 }
             }
+            g += it.n_kv;
+            cnt += my_tiles;
         }
     }
 
@@ -710,6 +738,9 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int dev = 0;
+    NPD_CUDA_TRY(cudaGetDevice(&dev));
+    const long long sms = npd::sm_count(dev);
     for (int64_t c0 = 0; c0 < num_chunks; c0 += kMaxChunks) {
         const int nc = static_cast<int>(num_chunks - c0 < kMaxChunks ? num_chunks - c0 : kMaxChunks);
         PrefillParams p;
@@ -738,9 +769,10 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
             p.chunk_start[i] = chunk_start_host[c0 + i];
             p.cta_prefix[i + 1] = p.cta_prefix[i] + (p.chunk_tokens[i] + 2 * tq - 1) / (2 * tq);
         }
-        const long long grid = (long long)p.cta_prefix[nc] * num_kv_heads;
-        if (grid == 0) continue;
-        NPD_REQUIRE(grid < INT32_MAX, NPD_ERR_INVALID_ARG, "prefill attention: too many tiles");
+        const long long items = (long long)p.cta_prefix[nc] * num_kv_heads;
+        if (items == 0) continue;
+        NPD_REQUIRE(items < INT32_MAX, NPD_ERR_INVALID_ARG, "prefill attention: too many tiles");
+        const long long grid = items < sms ? items : sms;     // persistent: one CTA per SM walks the items
         kern<<<static_cast<unsigned>(grid), kThreads, smem, st>>>(p, tq_map, tk, tv);
         NPD_CUDA_TRY(cudaGetLastError());
     }
