@@ -29,16 +29,16 @@ using namespace npd;
 
 constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays)
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
-constexpr int kKeys = 64;          // keys per tile (UMMA N of the score MMA, K extent of the PV MMA)
+constexpr int kKeys = 128;         // keys per tile (UMMA N of the score MMA, K extent of the PV MMA)
 constexpr int kD = 128;            // head_dim
 constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA for A, 10 MMA for B, 11 idle
 constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
 constexpr int kQTileBytes = 2 * kQHalfBytes;        // 32 KiB
-constexpr int kKvHalfBytes = kKeys * 128;           // one 64-element half of a 64-key K or V tile
-constexpr int kKvTileBytes = 2 * kKvHalfBytes;      // 16 KiB
-constexpr int kStages = 4;                          // K ring and V ring depth
-constexpr int kTmemCols = 512;     // per query tile X (128 columns): scores S (64) | P buffer 0 (32) | P buffer 1 (32);
-                                   // then O_A | O_B (128 each)
+constexpr int kKvHalfBytes = kKeys * 128;           // one 64-element half of a 128-key K or V tile
+constexpr int kKvTileBytes = 2 * kKvHalfBytes;      // 32 KiB
+constexpr int kStages = 2;                          // K ring and V ring depth
+constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; the packed probabilities of a key
+                                   // tile overwrite the first 64 columns of its scores
 constexpr int kPolyPairsOf8 = 0;           // of every 8 score pairs, this many take the polynomial exp2
 constexpr float kRescaleThreshold = 8.f;   // log2 units: O is rescaled only when a row max grows by more
 constexpr long long kWaitCycles = 4000000000LL;
@@ -221,12 +221,11 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 struct alignas(8) SmemCtrl {
     uint64_t q_full;             // both query tiles of the current work item have landed
     uint64_t q_empty;            // both MMA warps have issued their last score MMA of the item (2 arrivals)
-    uint64_t kv_full[kStages];   // K and V tile of a ring stage have landed
-    uint64_t kv_empty[kStages];  // both MMA warps are done with the stage (2 arrivals)
-    uint64_t s_full[2];     // [query tile]: the score tile of the next key tile is in TMEM
-    uint64_t s_read[2];     // [query tile]: the softmax threads hold it in registers (128 arrivals)
-    uint64_t p_full[2][2];  // [query tile][P buffer]: the probabilities are in TMEM (128 arrivals)
-    uint64_t pv_done[2][2]; // [query tile][P buffer]: the PV MMAs that read the buffer have completed
+    uint64_t k_full[kStages], v_full[kStages];     // the K / V tile of a ring stage has landed
+    uint64_t k_empty[kStages], v_empty[kStages];   // both MMA warps are done with it (2 arrivals)
+    uint64_t s_full[2];     // [query tile]: the score tile of the next key tile is in TMEM (and every earlier PV done)
+    uint64_t p_full[2];     // [query tile]: the probabilities are in TMEM (128 arrivals)
+    uint64_t o_full[2];     // [query tile]: the last PV MMA of the work item has completed
     uint64_t o_free[2];     // [query tile]: the epilogue has taken O out of TMEM (128 arrivals)
     uint32_t tmem_base;
     int abort_flag;
@@ -290,17 +289,16 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         mbar_init(smem_u32(&ctrl->q_full), 1);
         mbar_init(smem_u32(&ctrl->q_empty), 2);
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->kv_empty[i]), 2);
+            mbar_init(smem_u32(&ctrl->k_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->v_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->k_empty[i]), 2);
+            mbar_init(smem_u32(&ctrl->v_empty[i]), 2);
         }
         for (int x = 0; x < 2; ++x) {
             mbar_init(smem_u32(&ctrl->s_full[x]), 1);
-            mbar_init(smem_u32(&ctrl->s_read[x]), 128);
+            mbar_init(smem_u32(&ctrl->p_full[x]), 128);
+            mbar_init(smem_u32(&ctrl->o_full[x]), 1);
             mbar_init(smem_u32(&ctrl->o_free[x]), 128);
-            for (int b = 0; b < 2; ++b) {
-                mbar_init(smem_u32(&ctrl->p_full[x][b]), 128);
-                mbar_init(smem_u32(&ctrl->pv_done[x][b]), 1);
-            }
         }
         ctrl->abort_flag = 0;
         mbar_fence_init();
@@ -320,15 +318,15 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     if (warp == 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         // =========================== TMA producer (whole warp issues) ===========================
-        // A K or V tile of 64 keys is 8 boxes of 2 KiB (4 groups of 16 keys x 2 halves of 64 elements).
-        // Lanes 0-7 issue the K boxes and lanes 8-15 the V boxes, each lane looking up its own block id
+        // A K or V tile of 128 keys is 16 boxes of 2 KiB (8 groups of 16 keys x 2 halves of 64 elements).
+        // Lanes 0-15 issue the K boxes and lanes 16-31 the V boxes, each lane looking up its own block id
         // one tile ahead, so neither the table reads nor a serial issue sit on the critical path.
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
         }
-        const int role = lane >> 3, gi = (lane >> 1) & 3, hf = lane & 1;     // role 0 = K, 1 = V, others idle
+        const int role = lane >> 4, gi = (lane >> 1) & 7, hf = lane & 1;     // role 0 = K, 1 = V
         const CUtensorMap *tm = role == 1 ? &tm_v : &tm_k;
         int c_hint = 0, g = 0;                                  // g: key tiles loaded so far (ring position)
         bool ok = true;
@@ -373,17 +371,29 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
                 const int row = it.h * p.block_size + ((key0 + gi * 16) % p.block_size);
                 const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048);
-                if (g >= kStages)
-                    ok = wait_or_abort(smem_u32(&ctrl->kv_empty[stage]), ((g / kStages) - 1) & 1, abort_flag, p.status);
+                const uint32_t par = ((g / kStages) - 1) & 1;
+                // ---- K tile (lanes 0-15): its stage is free as soon as the score MMAs two tiles back are done
+                if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->k_empty[stage]), par, abort_flag, p.status);
                 if (!__all_sync(0xffffffffu, ok)) break;
-                const uint32_t bar = smem_u32(&ctrl->kv_full[stage]);
                 if (lane == 0) {
                     NPD_TRACE(0, 1, t);
-                    if (p.debug_flags & 4) mbar_arrive(bar); else mbar_expect_tx(bar, 2 * bytes);
+                    if (p.debug_flags & 4) mbar_arrive(smem_u32(&ctrl->k_full[stage]));
+                    else mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (!(p.debug_flags & 4) && role < 2 && gi < ngroups)
-                    tma_load_3d(smem_u32((role ? v_ring : k_ring) + (size_t)stage * kKvTileBytes) + off, tm, bar,
+                if (!(p.debug_flags & 4) && role == 0 && gi < ngroups)
+                    tma_load_3d(smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
+                                hf * 64, row, id);
+                // ---- V tile (lanes 16-31): free once the PV MMAs two tiles back are done
+                if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
+                if (!__all_sync(0xffffffffu, ok)) break;
+                if (lane == 0) {
+                    if (p.debug_flags & 4) mbar_arrive(smem_u32(&ctrl->v_full[stage]));
+                    else mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
+                }
+                __syncwarp();
+                if (!(p.debug_flags & 4) && role == 1 && gi < ngroups)
+                    tma_load_3d(smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
                                 hf * 64, row, id);
             }
             ok = __all_sync(0xffffffffu, ok);
@@ -428,61 +438,65 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 __syncwarp();
             };
-            // O_X (+)= P_X . V of ring stage `stage`: P from TMEM buffer `buf` (packed pairs, 8 columns per
-            // 16 keys), V MN-major from shared memory (16 keys = two 8-row groups = 2 KiB further on)
-            auto issue_pv = [&](int stage, int buf, bool first) {
+            // O_X (+)= P_X . V of ring stage `stage`: P from TMEM (packed pairs over the first 64 score columns,
+            // 8 columns per 16 keys), V MN-major from shared memory (16 keys = two 8-row groups = 2 KiB further on)
+            auto issue_pv = [&](int stage, bool first, bool last) {
                 const uint64_t vd = v_desc0 + static_cast<uint64_t>((stage * kKvTileBytes) >> 4);
-                const uint32_t a = t_sx + 64 + buf * 32;
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kKeys / 16; ++ks)
                         if (!(p.debug_flags & 2))
-                            tc_mma_ts(t_o, a + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
+                            tc_mma_ts(t_o, t_sx + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
                                       (!first || ks > 0) ? 1u : 0u);
-                    tc_commit(smem_u32(&ctrl->pv_done[x][buf]));
+                    if (last) tc_commit(smem_u32(&ctrl->o_full[x]));
                 }
                 __syncwarp();
             };
 
             int c_hint = 0;
             int g = 0;         // key tiles seen so far (ring position of the item's first key tile)
-            int cnt = 0;       // own key tiles processed so far (phases of s_full, s_read, p_full, pv_done)
-            int items_done = 0;   // items in which this query tile had work (phases of o_free)
+            int cnt = 0;       // own key tiles processed so far (phases of s_full and p_full)
+            int items_done = 0;   // items in which this query tile had work (phases of o_full and o_free)
             bool ok = true;
             for (int k = 0, item = blockIdx.x; ok && item < total_items; ++k, item += gridDim.x) {
                 const Item it = decode_item(p, item, c_hint);
                 const int my_tiles = it.ntiles[x];
                 if (!(ok = wait_all(&ctrl->q_full, k & 1))) break;
                 if (my_tiles > 0) {
-                    // the score columns are free once the softmax threads took the previous item's last tile
-                    if (cnt > 0 && !(ok = wait_all(&ctrl->s_read[x], (cnt - 1) & 1))) break;
-                    if (!(ok = wait_all(&ctrl->kv_full[g % kStages], (g / kStages) & 1))) break;
+                    // (the score columns are free: the previous item's last PV, which read P from them, was
+                    // issued before this MMA and MMAs execute in issue order)
+                    if (!(ok = wait_all(&ctrl->k_full[g % kStages], (g / kStages) & 1))) break;
                     tc_fence_after();
                     issue_s(g % kStages);
+                    commit(&ctrl->k_empty[g % kStages]);
                 }
                 if (my_tiles <= 1) commit(&ctrl->q_empty);   // no further score MMA of this item reads Q_X
                 for (int t = 0; ok && t < it.n_kv; ++t) {
                     const int gt = g + t, stage = gt % kStages;
                     if (t < my_tiles) {
                         const int ct = cnt + t;
-                        if (t + 1 < my_tiles) {
-                            // the next score tile may be computed as soon as the softmax threads have taken this one
-                            if (!(ok = wait_all(&ctrl->s_read[x], ct & 1))) break;
-                            if (!(ok = wait_all(&ctrl->kv_full[(gt + 1) % kStages], ((gt + 1) / kStages) & 1))) break;
-                            tc_fence_after();
-                            issue_s((gt + 1) % kStages);
-                            if (t + 2 == my_tiles) commit(&ctrl->q_empty);   // that was the last one
-                        }
                         // O_X is overwritten by the first PV of an item: the previous epilogue must have read it
                         if (t == 0 && items_done > 0 && !(ok = wait_all(&ctrl->o_free[x], (items_done - 1) & 1))) break;
-                        if (!(ok = wait_all(&ctrl->p_full[x][ct & 1], (ct >> 1) & 1))) break;
+                        if (!(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
+                        if (!(ok = wait_all(&ctrl->p_full[x], ct & 1))) break;
                         tc_fence_after();
-                        issue_pv(stage, ct & 1, t == 0);
+                        issue_pv(stage, t == 0, t + 1 == my_tiles);
+                        commit(&ctrl->v_empty[stage]);
+                        if (t + 1 < my_tiles) {
+                            // S(t+1) overwrites the columns P(t) sits in; it executes after the PV MMAs above
+                            if (!(ok = wait_all(&ctrl->k_full[(gt + 1) % kStages], ((gt + 1) / kStages) & 1))) break;
+                            tc_fence_after();
+                            issue_s((gt + 1) % kStages);
+                            commit(&ctrl->k_empty[(gt + 1) % kStages]);
+                            if (t + 2 == my_tiles) commit(&ctrl->q_empty);   // that was the last one
+                        }
                     } else {
                         // a key tile only the other query tile needs: observe it so that ring phases stay in step
-                        if (!(ok = wait_all(&ctrl->kv_full[stage], (gt / kStages) & 1))) break;
+                        if (!(ok = wait_all(&ctrl->k_full[stage], (gt / kStages) & 1))) break;
+                        commit(&ctrl->k_empty[stage]);
+                        if (!(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
+                        commit(&ctrl->v_empty[stage]);
                     }
-                    commit(&ctrl->kv_empty[stage]);      // our reads of K and V of this stage are (or will be) complete
                 }
                 g += it.n_kv;
                 cnt += my_tiles;
@@ -498,10 +512,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         const int wq = warp & 3;                                 // TMEM lane quarter this warp may touch
         const int row = wq * 32 + lane;                          // == TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-        const uint32_t t_sx = tmem + x * 128 + lane_base;        // scores (64 columns), then two P buffers (32 + 32)
+        const uint32_t t_sx = tmem + x * 128 + lane_base;        // scores (128 columns); P overwrites the first 64
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
-        int c_hint = 0, g = 0, cnt = 0;
+        int c_hint = 0, g = 0, cnt = 0, items_seen = 0;       // items_seen: items in which this tile had work
         bool ok = true;
 
         for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
@@ -511,14 +525,13 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             float m_run = -INFINITY, l_run = 0.f;
 #pragma unroll 1
             for (int t = 0; ok && t < my_tiles; ++t) {
-                const int ct = cnt + t, buf = ct & 1;
+                const int ct = cnt + t;
                 const int gt = g + t, stage = gt % kStages;
                 const int key0 = t * kKeys;
-                const uint32_t t_p = t_sx + 64 + buf * 32;       // packed probabilities of this tile
                 // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
                 // there cannot meet a NaN.  Both softmax groups do it (idempotent) before releasing their P.
                 if (key0 + kKeys > it.ctx_end) {
-                    if (!(ok = wait_or_abort(smem_u32(&ctrl->kv_full[stage]), (gt / kStages) & 1, abort_flag, p.status))) break;
+                    if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (gt / kStages) & 1, abort_flag, p.status))) break;
                     uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
                     const int first = max(it.ctx_end - key0, 0);
                     const int n16 = (kKeys - first) * 16;        // 16-byte pieces: 2 halves x 8 per row
@@ -529,40 +542,39 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     }
                     fence_proxy_async_smem();
                 }
+                // s_full(t) also tells that every earlier PV MMA of this query tile has completed (commits
+                // cover all MMAs issued before them), so O may be rescaled below without a further wait.
                 if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x]), ct & 1, abort_flag, p.status))) break;
                 tc_fence_after();
-                // The score row of this key tile (64 fp32) moves to registers; the score columns are then free
-                // for the next tile's MMA, which runs while this tile's probabilities are computed.
-                float sc[2][32];
-                tmem_ld32(t_sx, sc[0]);
-                tmem_ld32(t_sx + 32, sc[1]);
+                // The whole score row of this key tile (128 fp32) moves to registers: one TMEM read.
+                float sc[4][32];
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) tmem_ld32(t_sx + cc * 32, sc[cc]);
                 tmem_wait_ld();
-                tc_fence_before();
-                mbar_arrive(smem_u32(&ctrl->s_read[x]));
                 if (p.debug_flags & 1) {
-                    if (ct >= 2 && !(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][buf]), ((ct - 2) >> 1) & 1, abort_flag, p.status))) break;
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&ctrl->p_full[x][buf]));
+                    mbar_arrive(smem_u32(&ctrl->p_full[x]));
                     l_run = 1.f;
                     continue;
                 }
                 if (key0 + kKeys - 1 > it.start + it.tok0[x]) {  // only tiles that reach past the first row's diagonal
 #pragma unroll
-                    for (int cc = 0; cc < 2; ++cc)
+                    for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
                             if (key0 + cc * 32 + i > pos) sc[cc][i] = -INFINITY;
                 }
-                // ---- row maximum: four independent chains of three-input max ----
-                float mxa[4];
+                // ---- row maximum: eight independent chains of three-input max ----
+                float mxa[8];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) mxa[q4] = fmaxf(sc[q4 >> 1][(q4 & 1) * 16], sc[q4 >> 1][(q4 & 1) * 16 + 1]);
+                for (int q8 = 0; q8 < 8; ++q8) mxa[q8] = fmaxf(sc[q8 >> 1][(q8 & 1) * 16], sc[q8 >> 1][(q8 & 1) * 16 + 1]);
 #pragma unroll
                 for (int i = 2; i < 16; i += 2)
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4)
-                        mxa[q4] = fmax3(mxa[q4], sc[q4 >> 1][(q4 & 1) * 16 + i], sc[q4 >> 1][(q4 & 1) * 16 + i + 1]);
-                const float m_new = fmax3(fmaxf(mxa[0], mxa[1]), mxa[2], mxa[3]) * p.scale_log2;
+                    for (int q8 = 0; q8 < 8; ++q8)
+                        mxa[q8] = fmax3(mxa[q8], sc[q8 >> 1][(q8 & 1) * 16 + i], sc[q8 >> 1][(q8 & 1) * 16 + i + 1]);
+                const float m_new = fmaxf(fmax3(fmaxf(mxa[0], mxa[1]), mxa[2], mxa[3]),
+                                          fmax3(fmaxf(mxa[4], mxa[5]), mxa[6], mxa[7])) * p.scale_log2;
                 if (t == 0) {
                     m_run = m_new;                              // key 0 is visible to every row: finite
                 } else {
@@ -572,9 +584,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     const bool grow = m_new > m_run + kRescaleThreshold;
                     if (__any_sync(0xffffffffu, grow)) {
                         const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
-                        // every PV up to tile t-1 must have landed in O: PV(t-1) is the newest, PV(t-2) precedes it
-                        if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][buf ^ 1]), ((ct - 1) >> 1) & 1, abort_flag, p.status))) break;
-                        tc_fence_after();
 #pragma unroll 1
                         for (int cc = 0; cc < 4; ++cc) {
                             float o[32];
@@ -591,15 +600,13 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         }
                     }
                 }
-                // The P buffer of this tile was last read by the PV MMAs two tiles ago.  (Each pv_done barrier sees
-                // every second tile, so a parity wait on it is never more than one phase behind.)
-                if (ct >= 2 && !(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][buf]), ((ct - 2) >> 1) & 1, abort_flag, p.status))) break;
-                // ---- probabilities (masked scores are -inf -> 0), packed in pairs ----
+                // ---- probabilities in place (masked scores are -inf -> 0), packed in pairs over the score
+                //      columns already read ----
                 const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
                 const float2 negm2 = make_float2(-m_run, -m_run);
                 float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
+                for (int cc = 0; cc < 4; ++cc) {
                     uint32_t packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
@@ -613,22 +620,19 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         acc2[(i >> 1) & 1] = __fadd2_rn(acc2[(i >> 1) & 1], pr);
                         packed[i >> 1] = Elem<T>::pack2(pr.x, pr.y);
                     }
-                    tmem_st16(t_p + cc * 16, packed);
+                    tmem_st16(t_sx + cc * 16, packed);
                 }
                 l_run += (acc2[0].x + acc2[1].x) + (acc2[0].y + acc2[1].y);
                 tmem_wait_st();
-                tc_fence_before();           // P is in TMEM: the MMA warp may issue the PV MMAs of this tile
-                mbar_arrive(smem_u32(&ctrl->p_full[x][buf]));
+                tc_fence_before();           // P is in TMEM, S has been read: the MMA warp may go on
+                mbar_arrive(smem_u32(&ctrl->p_full[x]));
             }
 
             // ---- epilogue: O / l -> out ----
             if (ok && my_tiles > 0) {
-                // the last PV on each P buffer (earlier completions of both barriers were observed in the loop)
-                const int ce = cnt + my_tiles;
-                if (ce >= 2)
-                    ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][(ce - 2) & 1]), ((ce - 2) >> 1) & 1, abort_flag, p.status);
-                if (ok)
-                    ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][(ce - 1) & 1]), ((ce - 1) >> 1) & 1, abort_flag, p.status);
+                // o_full completes once per work item, after its last PV MMA
+                ok = wait_or_abort(smem_u32(&ctrl->o_full[x]), items_seen & 1, abort_flag, p.status);
+                ++items_seen;
                 if (ok) {
                     tc_fence_after();
                     const bool store = tq_idx < it.tq_valid[x] && row < p.tq * p.group;
