@@ -157,10 +157,12 @@ int npd_paged_prefill_attention(void *out, const void *q, const void *k_cache,
  * `*_block_stride` in elements; block_elems*elem_bytes must be a multiple of 16.
  * src_blocks/dst_blocks are DEVICE int32 arrays resident on the device the kernel runs
  * on (the current device).  Either pool may live on a peer GPU whose memory is mapped
- * into the current device (peer access enabled, or an IPC mapping); the copy is a
- * plain load/store kernel, so no copy engine or NCCL call is involved.
- * `max_ctas` caps the grid (0 = one CTA per SM) so a side-stream migration leaves SMs
- * to the compute stream.                                                               */
+ * into the current device (peer access enabled, or an IPC mapping); the copy is done by
+ * the kernel itself (bulk asynchronous copies through shared memory, no multicast), so no
+ * copy engine or NCCL call is involved.
+ * `max_ctas` > 0 caps the grid (one warp per CTA; 0 = 32 CTAs, which saturate NVLink) so
+ * a side-stream migration leaves the SMs to the compute stream; `max_ctas` < 0 selects the
+ * plain load/store variant with -max_ctas CTAs of 256 threads.                          */
 int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
                    const int32_t *src_blocks, const int32_t *dst_blocks, int64_t num_pairs,
                    int64_t num_layers, int64_t block_elems, int elem_bytes,

@@ -3,46 +3,66 @@
 // The reference moves a request's pages with two strided copy_ calls per block
 // (nanoPD/workers/kv_transfer.py:73-79), i.e. up to thousands of launches per request, each a
 // [layers] x 32 KiB strided copy.  Here one launch walks every (block pair, layer, K|V) unit —
-// block_elems*elem bytes, contiguous on both sides — with 16-byte loads and stores, eight
-// loads in flight per thread before the first store.  Either side may be peer memory mapped
-// over NVLink, so the same kernel pushes (source local) or pulls (destination local).  It
-// runs on a side stream with a capped CTA count so the compute stream keeps most SMs.
+// block_elems*elem bytes, contiguous on both sides.  Either side may be peer memory mapped over
+// NVLink, so the same kernel pushes (source local) or pulls (destination local).
+//
+// Two data paths:
+//   * bulk (default): one warp per CTA; an elected lane streams units through a ring of
+//     shared-memory stages with cp.async.bulk (global -> shared on an mbarrier, shared -> global in
+//     bulk groups).  192 KiB of copies in flight per CTA without occupying registers or issue slots,
+//     so a handful of CTAs fill the link and the compute stream keeps the SMs.  No multicast.
+//   * ld/st: 256 threads per CTA, 16-byte loads and stores, eight loads in flight per thread —
+//     used when a unit is not a multiple of 16 bytes wide enough for the bulk path.
 // Link- or HBM-bound: blocks * layers * 2 * block_bytes, one direction.
 #include "npd_common.cuh"
 
 namespace {
 
+using namespace npd;
+
 struct MigrateParams {
-    const uint4 *src_k, *src_v;
-    uint4 *dst_k, *dst_v;
+    const uint8_t *src_k, *src_v;
+    uint8_t *dst_k, *dst_v;
     const int32_t *src_blocks, *dst_blocks;
     int32_t *status;
     long long num_pairs;
     int num_layers;
-    int chunks_per_block;              // block bytes / 16
-    long long src_layer_stride, src_block_stride, dst_layer_stride, dst_block_stride;   // 16-byte units
+    long long block_bytes;
+    long long src_layer_stride, src_block_stride, dst_layer_stride, dst_block_stride;   // bytes
     int src_num_blocks, dst_num_blocks;
+    int pieces_per_unit;      // bulk path: a unit is moved in pieces of at most kPieceBytes
 };
 
 constexpr int kThreads = 256;
 constexpr int kUnroll = 8;
+constexpr int kPieceBytes = 32 * 1024;
+constexpr int kBulkStages = 6;            // 6 x 32 KiB = 192 KiB of shared memory per CTA
 
-__global__ void __launch_bounds__(kThreads) kv_migrate_kernel(const MigrateParams p) {
+__device__ __forceinline__ bool locate_unit(const MigrateParams &p, long long u, const uint8_t *&src, uint8_t *&dst) {
+    // Unit order: pair-major, then layer, then K|V — consecutive units work on one block.
+    const int kv = static_cast<int>(u & 1);
+    const long long pl = u >> 1;
+    const long long pair = pl / p.num_layers;
+    const int layer = static_cast<int>(pl - pair * p.num_layers);
+    const int sb = __ldg(p.src_blocks + pair), db = __ldg(p.dst_blocks + pair);
+    if (sb < 0 || sb >= p.src_num_blocks || db < 0 || db >= p.dst_num_blocks) return false;
+    src = (kv ? p.src_v : p.src_k) + layer * p.src_layer_stride + sb * p.src_block_stride;
+    dst = (kv ? p.dst_v : p.dst_k) + layer * p.dst_layer_stride + db * p.dst_block_stride;
+    return true;
+}
+
+__global__ void __launch_bounds__(kThreads) kv_migrate_ldst_kernel(const MigrateParams p) {
     const long long units = p.num_pairs * p.num_layers * 2;
     for (long long u = blockIdx.x; u < units; u += gridDim.x) {
-        // Unit order: pair-major, then layer, then K|V — consecutive CTAs work on one block.
-        const int kv = static_cast<int>(u & 1);
-        const long long pl = u >> 1;
-        const long long pair = pl / p.num_layers;
-        const int layer = static_cast<int>(pl - pair * p.num_layers);
-        const int sb = __ldg(p.src_blocks + pair), db = __ldg(p.dst_blocks + pair);
-        if (sb < 0 || sb >= p.src_num_blocks || db < 0 || db >= p.dst_num_blocks) {
+        const uint8_t *src8;
+        uint8_t *dst8;
+        if (!locate_unit(p, u, src8, dst8)) {
             if (p.status && threadIdx.x == 0) atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
             continue;
         }
-        const uint4 *src = (kv ? p.src_v : p.src_k) + layer * p.src_layer_stride + sb * p.src_block_stride;
-        uint4 *dst = (kv ? p.dst_v : p.dst_k) + layer * p.dst_layer_stride + db * p.dst_block_stride;
-        const int n = p.chunks_per_block;
+        const uint4 *src = reinterpret_cast<const uint4 *>(src8);
+        uint4 *dst = reinterpret_cast<uint4 *>(dst8);
+        const int n = static_cast<int>(p.block_bytes / 16);
         for (int base = 0; base < n; base += kThreads * kUnroll) {
             uint4 buf[kUnroll];
 #pragma unroll
@@ -57,6 +77,95 @@ __global__ void __launch_bounds__(kThreads) kv_migrate_kernel(const MigrateParam
             }
         }
     }
+}
+
+// ---- bulk-copy helpers (untiled cp.async.bulk: 16-byte aligned addresses and sizes) ----
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void *dst, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {     // at most N store groups still READING shared memory
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// One warp per CTA; lane 0 drives a ring of kBulkStages pieces: load piece i+S-1 while piece i is stored.
+__global__ void __launch_bounds__(32) kv_migrate_bulk_kernel(const MigrateParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t bars[kBulkStages];
+    if (threadIdx.x != 0) return;
+    for (int i = 0; i < kBulkStages; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+
+    const long long units = p.num_pairs * p.num_layers * 2;
+    const long long pieces = units * p.pieces_per_unit;
+    // this CTA's pieces: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const long long my_count = pieces > blockIdx.x ? (pieces - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    auto piece_ptrs = [&](long long i, const uint8_t *&src, uint8_t *&dst, uint32_t &bytes) {
+        const long long piece = blockIdx.x + i * gridDim.x;
+        const long long u = piece / p.pieces_per_unit;
+        const int part = static_cast<int>(piece - u * p.pieces_per_unit);
+        const uint8_t *s;
+        uint8_t *d;
+        if (!locate_unit(p, u, s, d)) {
+            if (p.status) atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
+            return false;
+        }
+        const long long off = (long long)part * kPieceBytes;
+        const long long left = p.block_bytes - off;
+        bytes = static_cast<uint32_t>(left < kPieceBytes ? left : kPieceBytes);
+        src = s + off;
+        dst = d + off;
+        return true;
+    };
+
+    bool dead = false;
+    long long issued = 0;
+    auto issue_load = [&](long long i) {
+        const int st = static_cast<int>(i % kBulkStages);
+        const uint8_t *src;
+        uint8_t *dst;
+        uint32_t bytes = 0;
+        const uint32_t bar = smem_u32(&bars[st]);
+        if (piece_ptrs(i, src, dst, bytes)) {
+            mbar_expect_tx(bar, bytes);
+            bulk_g2s(smem_u32(smem + (size_t)st * kPieceBytes), src, bytes, bar);
+        } else {
+            mbar_arrive(bar);          // skipped piece: keep the ring's phases in step
+        }
+    };
+    for (; issued < my_count && issued < kBulkStages - 1; ++issued) issue_load(issued);
+
+    for (long long i = 0; i < my_count && !dead; ++i) {
+        const int st = static_cast<int>(i % kBulkStages);
+        if (!mbar_wait_bounded(smem_u32(&bars[st]), static_cast<uint32_t>((i / kBulkStages) & 1))) {
+            if (p.status) atomicOr(p.status, NPD_STATUS_WAIT_TIMEOUT);
+            dead = true;
+            break;
+        }
+        const uint8_t *src;
+        uint8_t *dst;
+        uint32_t bytes = 0;
+        if (piece_ptrs(i, src, dst, bytes)) bulk_s2g(dst, smem_u32(smem + (size_t)st * kPieceBytes), bytes);
+        bulk_commit();
+        // The next load reuses the stage whose store was committed one iteration ago: wait until at most
+        // one store group (the one just committed) is still reading shared memory.
+        if (issued < my_count) {
+            bulk_wait_read<1>();
+            issue_load(issued);
+            ++issued;
+        }
+    }
+    bulk_wait_all();     // all stores have landed before the kernel (and its stream position) completes
 }
 
 }  // namespace
@@ -87,29 +196,45 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
                 NPD_ERR_INVALID_ARG, "npd_kv_migrate: dimension out of range");
 
     MigrateParams p;
-    p.src_k = static_cast<const uint4 *>(src_k);
-    p.src_v = static_cast<const uint4 *>(src_v);
-    p.dst_k = static_cast<uint4 *>(dst_k);
-    p.dst_v = static_cast<uint4 *>(dst_v);
+    p.src_k = static_cast<const uint8_t *>(src_k);
+    p.src_v = static_cast<const uint8_t *>(src_v);
+    p.dst_k = static_cast<uint8_t *>(dst_k);
+    p.dst_v = static_cast<uint8_t *>(dst_v);
     p.src_blocks = src_blocks;
     p.dst_blocks = dst_blocks;
     p.status = status;
     p.num_pairs = num_pairs;
     p.num_layers = static_cast<int>(num_layers);
-    p.chunks_per_block = static_cast<int>(block_elems * elem_bytes / 16);
-    p.src_layer_stride = src_layer_stride * elem_bytes / 16;
-    p.src_block_stride = src_block_stride * elem_bytes / 16;
-    p.dst_layer_stride = dst_layer_stride * elem_bytes / 16;
-    p.dst_block_stride = dst_block_stride * elem_bytes / 16;
+    p.block_bytes = block_elems * elem_bytes;
+    p.src_layer_stride = src_layer_stride * elem_bytes;
+    p.src_block_stride = src_block_stride * elem_bytes;
+    p.dst_layer_stride = dst_layer_stride * elem_bytes;
+    p.dst_block_stride = dst_block_stride * elem_bytes;
     p.src_num_blocks = static_cast<int>(src_num_blocks);
     p.dst_num_blocks = static_cast<int>(dst_num_blocks);
+    p.pieces_per_unit = static_cast<int>((p.block_bytes + kPieceBytes - 1) / kPieceBytes);
 
     int dev = 0;
     NPD_CUDA_TRY(cudaGetDevice(&dev));
-    long long grid = max_ctas > 0 ? max_ctas : npd::sm_count(dev);
     const long long units = num_pairs * num_layers * 2;
-    if (grid > units) grid = units;
-    kv_migrate_kernel<<<static_cast<unsigned>(grid), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    // max_ctas < 0 selects the load/store path with -max_ctas CTAs (kept for comparison and as a fallback).
+    if (max_ctas >= 0) {
+        const long long pieces = units * p.pieces_per_unit;
+        // 32 CTAs x 192 KiB in flight saturate NVLink and most of a same-GPU copy; more only takes shared
+        // memory away from the compute stream
+        long long grid = max_ctas > 0 ? max_ctas : 32;
+        if (grid > npd::sm_count(dev)) grid = npd::sm_count(dev);
+        if (grid > pieces) grid = pieces;
+        const size_t smem = (size_t)kBulkStages * kPieceBytes;
+        NPD_CUDA_TRY(cudaFuncSetAttribute(kv_migrate_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kv_migrate_bulk_kernel<<<static_cast<unsigned>(grid), 32, smem, st>>>(p);
+    } else {
+        long long grid = -static_cast<long long>(max_ctas);
+        if (grid > units) grid = units;
+        kv_migrate_ldst_kernel<<<static_cast<unsigned>(grid), kThreads, 0, st>>>(p);
+    }
     NPD_CUDA_TRY(cudaGetLastError());
     return NPD_OK;
 }

@@ -275,8 +275,9 @@ def paged_kv_migrate(src_k, src_v, dst_k, dst_v, src_blocks, dst_blocks=None, ma
     One kernel on the current stream of the CURRENT device, which must be able to address
     both pools (same device, or peer access enabled — see ``kv_transfer.transfer_kv``).
     ``src_blocks``/``dst_blocks``: int32 tensors on the current device (or Python lists,
-    which are copied there).  ``max_ctas`` caps the grid so a side-stream migration leaves
-    SMs to compute.
+    which are copied there).  ``max_ctas`` > 0 caps the grid of the bulk-copy kernel (one warp
+    per CTA; 0 = 32 CTAs) so a side-stream migration leaves the SMs to compute; a negative value
+    selects the plain load/store kernel with that many CTAs.
     """
     dev = torch.device("cuda", torch.cuda.current_device())
     L, snb, belems, sls, sbs = _pool_geometry(src_k, "src_k")

@@ -16,7 +16,7 @@ def _pools(L, nb, Hkv, B, D, dtype, device, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("max_ctas", [0, 4])
+@pytest.mark.parametrize("max_ctas", [0, 1, 4, -8])
 def test_same_ids_like_the_reference(kernels, dtype, max_ctas):
     """transfer_kv with equal ids on both sides (kv_transfer.py:73-79), both pools on one GPU."""
     L, nb, Hkv, B, D = 4, 24, 8, 16, 128
@@ -65,6 +65,48 @@ def test_request_sized_migration_roundtrip(kernels):
     rest = torch.ones(nb, dtype=torch.bool, device="cuda:0")
     rest[sel] = False
     assert torch.count_nonzero(back_k[:, rest]) == 0
+
+
+@pytest.mark.parametrize("block_shape,dtype", [((1, 16, 64), torch.float16),     # 2 KiB units: one small piece each
+                                               ((8, 32, 128), torch.bfloat16),   # 64 KiB units: two pieces each
+                                               ((5, 16, 72), torch.float16)])    # 11 520-byte units
+def test_unit_sizes(kernels, block_shape, dtype):
+    Hkv, B, D = block_shape
+    L, nb = 3, 12
+    sk, sv, dsk, dsv = _pools(L, nb, Hkv, B, D, dtype, "cuda:0", 9)
+    dk, dv = torch.zeros_like(sk), torch.zeros_like(sv)
+    ddk, ddv = dk.to("cuda:0"), dv.to("cuda:0")
+    kv_transfer.transfer_kv(dsk, dsv, ddk, ddv, [0, 11, 5, 6, 2], dst_block_table=[4, 3, 2, 1, 0], max_ctas=3)
+    paged_oracle.kv_migrate(sk, sv, dk, dv, [0, 11, 5, 6, 2], [4, 3, 2, 1, 0])
+    torch.cuda.synchronize()
+    assert torch.equal(ddk.cpu(), dk) and torch.equal(ddv.cpu(), dv)
+
+
+def test_migration_overlaps_decode_attention(kernels):
+    """Migration on a side stream while decode attention runs on the main stream: both results are exact
+    (the migrated blocks are disjoint from the ones the decode batch reads, as the allocator guarantees)."""
+    from nanopd_b200 import workloads
+    b = workloads.make_decode_batch([700, 1500, 64, 3000], 32, 8, 128, 16, torch.bfloat16, device="cuda:0", seed=5,
+                                    pool_blocks=400)
+    want = torch.zeros_like(b.query)
+    kernels.paged_attention_forward(want, b.query, b.k_cache, b.v_cache, b.block_tables, b.ctx_lens, b.scale, 16,
+                                    b.block_tables.size(1))
+    L = 4
+    src_k = torch.randn(L, 400, 8, 16, 128, device="cuda:0").bfloat16()
+    src_v = torch.randn(L, 400, 8, 16, 128, device="cuda:0").bfloat16()
+    dst_k, dst_v = torch.zeros_like(src_k), torch.zeros_like(src_v)
+    ids = torch.randperm(400)[:300].tolist()
+    side = torch.cuda.Stream(device="cuda:0")
+    side.wait_stream(torch.cuda.current_stream())
+    out = torch.zeros_like(b.query)
+    for _ in range(3):
+        kv_transfer.transfer_kv(src_k, src_v, dst_k, dst_v, ids, stream=side, max_ctas=8)
+        kernels.paged_attention_forward(out, b.query, b.k_cache, b.v_cache, b.block_tables, b.ctx_lens, b.scale, 16,
+                                        b.block_tables.size(1))
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    sel = torch.tensor(ids, device="cuda:0")
+    assert torch.equal(dst_k[:, sel], src_k[:, sel]) and torch.equal(dst_v[:, sel], src_v[:, sel])
 
 
 def test_bad_block_id_is_skipped(kernels):
