@@ -21,6 +21,9 @@
 // abort flag lets all roles leave together, after which TMEM is released.
 //
 // Algorithmic flops per chunk: 4*Hq*D*(n*start + n(n+1)/2)  (causal; masked work not counted).
+#include <algorithm>
+#include <vector>
+
 #include "npd_common.cuh"
 
 namespace {
@@ -28,6 +31,8 @@ namespace {
 using namespace npd;
 
 constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays)
+constexpr int kMaxPairs = 2048;    // query-tile pairs per launch (kernel-parameter array, heaviest first)
+constexpr int kSchedSlots = 4;     // work items the producer may publish ahead of the slowest consumer
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
 constexpr int kKeys = 128;         // keys per tile (UMMA N of the score MMA, K extent of the PV MMA)
 constexpr int kD = 128;            // head_dim
@@ -55,11 +60,14 @@ struct PrefillParams {
     int max_blocks_per_seq;
     int num_blocks;
     long long bt_row_stride;
-    int debug_flags;        // performance experiments only: 1 = skip softmax math, 2 = skip MMA issue, 4 = skip K/V loads
+    int debug_flags;        // only read when built with -DNPD_PREFILL_EXPERIMENTS (timing experiments that give
+                            // wrong results): 1 = skip softmax math, 2 = skip MMA issue, 4 = skip K/V loads
     int chunk_q_offset[kMaxChunks];
     int chunk_tokens[kMaxChunks];
     int chunk_start[kMaxChunks];
-    int cta_prefix[kMaxChunks + 1];   // exclusive prefix of ceil(chunk_tokens / (2*tq)): CTAs per kv head
+    int num_pairs;                    // entries of pair_order
+    int *work_counter;                // device int32, zero before the launch: next work item to hand out
+    uint32_t pair_order[kMaxPairs];   // (chunk << 16 | pair of query tiles), sorted by key tiles, heaviest first
 #ifdef NPD_PREFILL_TRACE
     long long *trace;
 #endif
@@ -198,6 +206,12 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     return true;
 }
 
+#ifdef NPD_PREFILL_EXPERIMENTS
+#define NPD_EXPERIMENT_FLAGS(p) ((p).debug_flags)
+#else
+#define NPD_EXPERIMENT_FLAGS(p) 0
+#endif
+
 // Optional phase tracing for performance work (compiled out unless NPD_PREFILL_TRACE is defined):
 // the CTA with blockIdx.x == 0 appends (tag, key tile, clock) triples to the workspace after its header.
 #ifdef NPD_PREFILL_TRACE
@@ -219,6 +233,8 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 #endif
 
 struct alignas(8) SmemCtrl {
+    uint64_t sched_full[kSchedSlots];   // the producer warp has published the next work item
+    int sched_item[kSchedSlots];
     uint64_t q_full;             // both query tiles of the current work item have landed
     uint64_t q_empty;            // both MMA warps have issued their last score MMA of the item (2 arrivals)
     uint64_t k_full[kStages], v_full[kStages];     // the K / V tile of a ring stage has landed
@@ -239,17 +255,13 @@ struct Item {
     int n_kv;
 };
 
-// Items are numbered (chunk-major, later = heavier pairs of a chunk first, then kv head); `c_hint` only grows.
-__device__ __forceinline__ Item decode_item(const PrefillParams &p, int item, int &c_hint) {
+// Work item `item` = kv head (item % Hkv) of entry (item / Hkv) of the host-sorted pair list.
+__device__ __forceinline__ Item decode_item(const PrefillParams &p, int item) {
     Item it;
     it.h = item % p.num_kv_heads;
-    const int rank = item / p.num_kv_heads;
-    int c = c_hint;
-    while (c + 1 < p.num_chunks && p.cta_prefix[c + 1] <= rank) ++c;
-    c_hint = c;
+    const uint32_t entry = p.pair_order[item / p.num_kv_heads];
+    const int c = static_cast<int>(entry >> 16), pair = static_cast<int>(entry & 0xffffu);
     it.c = c;
-    const int pairs = p.cta_prefix[c + 1] - p.cta_prefix[c];
-    const int pair = pairs - 1 - (rank - p.cta_prefix[c]);     // later tiles of a chunk see more keys: first
     const int n_tok = p.chunk_tokens[c];
     it.start = p.chunk_start[c];
     it.qoff = p.chunk_q_offset[c];
@@ -265,10 +277,11 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, int item, in
     return it;
 }
 
-// Persistent kernel: one CTA per SM walks the work items blockIdx.x, blockIdx.x + gridDim.x, ...  All
-// barrier phases are driven by running counters, so the producer already loads the next item's K/V tiles
-// (and, once the last score MMA has been issued, its query tiles) while the current item drains, and the
-// epilogue of an item overlaps the first MMAs of the next one.
+// Persistent kernel: one CTA per SM.  Work items are handed out heaviest first through an atomic counter (the
+// producer warp fetches the next one and publishes it to the other roles through a small shared-memory ring), so
+// ragged chunks balance across the SMs.  All barrier phases are driven by running counters: the producer
+// already loads the next item's K/V tiles (and, once the last score MMA has been issued, its query tiles) while
+// the current item drains, and the epilogue of an item overlaps the first MMAs of the next one.
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
@@ -283,11 +296,18 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStages * kKvTileBytes);
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-    const int total_items = p.cta_prefix[p.num_chunks] * p.num_kv_heads;
+    const int total_items = p.num_pairs * p.num_kv_heads;
+    // Consumers read the item the producer published for their k-th iteration (-1 = no more work).
+    auto next_item = [&](int k, bool &ok_ref) {
+        const int slot = k % kSchedSlots;
+        ok_ref = wait_or_abort(smem_u32(&ctrl->sched_full[slot]), (k / kSchedSlots) & 1, &ctrl->abort_flag, p.status);
+        return ok_ref ? *reinterpret_cast<volatile int *>(&ctrl->sched_item[slot]) : -1;
+    };
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&ctrl->q_full), 1);
         mbar_init(smem_u32(&ctrl->q_empty), 2);
+        for (int i = 0; i < kSchedSlots; ++i) mbar_init(smem_u32(&ctrl->sched_full[i]), 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(smem_u32(&ctrl->k_full[i]), 1);
             mbar_init(smem_u32(&ctrl->v_full[i]), 1);
@@ -328,10 +348,22 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         }
         const int role = lane >> 4, gi = (lane >> 1) & 7, hf = lane & 1;     // role 0 = K, 1 = V
         const CUtensorMap *tm = role == 1 ? &tm_v : &tm_k;
-        int c_hint = 0, g = 0;                                  // g: key tiles loaded so far (ring position)
+        int g = 0;                                              // g: key tiles loaded so far (ring position)
         bool ok = true;
-        for (int k = 0, item = blockIdx.x; ok && item < total_items; ++k, item += gridDim.x) {
-            const Item it = decode_item(p, item, c_hint);
+        for (int k = 0; ok; ++k) {
+            // Fetch and publish the next work item.  A slot is reused kSchedSlots items later; by then every
+            // role has long read it (the producer cannot run more than two items ahead of the MMA warps,
+            // which cannot run ahead of the softmax groups).
+            int item = 0;
+            if (lane == 0) {
+                item = atomicAdd(p.work_counter, 1);
+                if (item >= total_items) item = -1;
+                *reinterpret_cast<volatile int *>(&ctrl->sched_item[k % kSchedSlots]) = item;
+                mbar_arrive(smem_u32(&ctrl->sched_full[k % kSchedSlots]));
+            }
+            item = __shfl_sync(0xffffffffu, item, 0);
+            if (item < 0) break;
+            const Item it = decode_item(p, item);
             // ---- query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch
             if (k > 0) ok = wait_or_abort(smem_u32(&ctrl->q_empty), (k - 1) & 1, abort_flag, p.status);
             if (!__all_sync(0xffffffffu, ok)) break;
@@ -377,22 +409,22 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (!__all_sync(0xffffffffu, ok)) break;
                 if (lane == 0) {
                     NPD_TRACE(0, 1, t);
-                    if (p.debug_flags & 4) mbar_arrive(smem_u32(&ctrl->k_full[stage]));
+                    if (NPD_EXPERIMENT_FLAGS(p) & 4) mbar_arrive(smem_u32(&ctrl->k_full[stage]));
                     else mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (!(p.debug_flags & 4) && role == 0 && gi < ngroups)
+                if (!(NPD_EXPERIMENT_FLAGS(p) & 4) && role == 0 && gi < ngroups)
                     tma_load_3d(smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
                                 hf * 64, row, id);
                 // ---- V tile (lanes 16-31): free once the PV MMAs two tiles back are done
                 if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
                 if (!__all_sync(0xffffffffu, ok)) break;
                 if (lane == 0) {
-                    if (p.debug_flags & 4) mbar_arrive(smem_u32(&ctrl->v_full[stage]));
+                    if (NPD_EXPERIMENT_FLAGS(p) & 4) mbar_arrive(smem_u32(&ctrl->v_full[stage]));
                     else mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (!(p.debug_flags & 4) && role == 1 && gi < ngroups)
+                if (!(NPD_EXPERIMENT_FLAGS(p) & 4) && role == 1 && gi < ngroups)
                     tma_load_3d(smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
                                 hf * 64, row, id);
             }
@@ -429,7 +461,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kD / 16; ++ks) {
-                        if (p.debug_flags & 2) break;
+                        if (NPD_EXPERIMENT_FLAGS(p) & 2) break;
                         const uint64_t a_off = static_cast<uint64_t>(((ks >> 2) * kQHalfBytes + (ks & 3) * 32) >> 4);
                         const uint64_t b_off = static_cast<uint64_t>(((ks >> 2) * kKvHalfBytes + (ks & 3) * 32) >> 4);
                         tc_mma_ss(t_sx, q_desc + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
@@ -445,7 +477,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kKeys / 16; ++ks)
-                        if (!(p.debug_flags & 2))
+                        if (!(NPD_EXPERIMENT_FLAGS(p) & 2))
                             tc_mma_ts(t_o, t_sx + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
                                       (!first || ks > 0) ? 1u : 0u);
                     if (last) tc_commit(smem_u32(&ctrl->o_full[x]));
@@ -453,13 +485,14 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 __syncwarp();
             };
 
-            int c_hint = 0;
             int g = 0;         // key tiles seen so far (ring position of the item's first key tile)
             int cnt = 0;       // own key tiles processed so far (phases of s_full and p_full)
             int items_done = 0;   // items in which this query tile had work (phases of o_full and o_free)
             bool ok = true;
-            for (int k = 0, item = blockIdx.x; ok && item < total_items; ++k, item += gridDim.x) {
-                const Item it = decode_item(p, item, c_hint);
+            for (int k = 0; ok; ++k) {
+                const int item = next_item(k, ok);
+                if (!__all_sync(0xffffffffu, ok) || item < 0) break;
+                const Item it = decode_item(p, item);
                 const int my_tiles = it.ntiles[x];
                 if (!(ok = wait_all(&ctrl->q_full, k & 1))) break;
                 if (my_tiles > 0) {
@@ -515,11 +548,13 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         const uint32_t t_sx = tmem + x * 128 + lane_base;        // scores (128 columns); P overwrites the first 64
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
-        int c_hint = 0, g = 0, cnt = 0, items_seen = 0;       // items_seen: items in which this tile had work
+        int g = 0, cnt = 0, items_seen = 0;                   // items_seen: items in which this tile had work
         bool ok = true;
 
-        for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-            const Item it = decode_item(p, item, c_hint);
+        for (int k = 0; ok; ++k) {
+            const int item = next_item(k, ok);
+            if (!ok || item < 0) break;
+            const Item it = decode_item(p, item);
             const int my_tiles = it.ntiles[x];
             const int pos = it.start + it.tok0[x] + tq_idx;      // last visible key of this row
             float m_run = -INFINITY, l_run = 0.f;
@@ -551,7 +586,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) tmem_ld32(t_sx + cc * 32, sc[cc]);
                 tmem_wait_ld();
-                if (p.debug_flags & 1) {
+                if (NPD_EXPERIMENT_FLAGS(p) & 1) {
                     tc_fence_before();
                     mbar_arrive(smem_u32(&ctrl->p_full[x]));
                     l_run = 1.f;
@@ -766,19 +801,35 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.trace = workspace_bytes >= 256 + 4 * 4096 * sizeof(long long)
                       ? reinterpret_cast<long long *>(static_cast<uint8_t *>(workspace) + 256) : nullptr;
 #endif
-        p.cta_prefix[0] = 0;
+        // Pairs of query tiles of the launch, heaviest (most key tiles) first; the kernel hands them out in
+        // this order through an atomic counter.
+        struct Entry { int weight; uint32_t code; };
+        std::vector<Entry> entries;
         for (int i = 0; i < nc; ++i) {
             p.chunk_q_offset[i] = chunk_q_offset_host[c0 + i];
             p.chunk_tokens[i] = chunk_tokens_host[c0 + i];
             p.chunk_start[i] = chunk_start_host[c0 + i];
-            p.cta_prefix[i + 1] = p.cta_prefix[i] + (p.chunk_tokens[i] + 2 * tq - 1) / (2 * tq);
+            const int pairs = (p.chunk_tokens[i] + 2 * tq - 1) / (2 * tq);
+            NPD_REQUIRE(pairs <= 0xffff, NPD_ERR_INVALID_ARG, "prefill attention: chunk %d is too long", i);
+            for (int pr = 0; pr < pairs; ++pr) {
+                const int last_tok = std::min(p.chunk_tokens[i], (2 * pr + 2) * tq);
+                entries.push_back({(p.chunk_start[i] + last_tok + kKeys - 1) / kKeys,
+                                   (static_cast<uint32_t>(i) << 16) | static_cast<uint32_t>(pr)});
+            }
         }
-        const long long items = (long long)p.cta_prefix[nc] * num_kv_heads;
-        if (items == 0) continue;
-        NPD_REQUIRE(items < INT32_MAX, NPD_ERR_INVALID_ARG, "prefill attention: too many tiles");
-        const long long grid = items < sms ? items : sms;     // persistent: one CTA per SM walks the items
-        kern<<<static_cast<unsigned>(grid), kThreads, smem, st>>>(p, tq_map, tk, tv);
-        NPD_CUDA_TRY(cudaGetLastError());
+        std::stable_sort(entries.begin(), entries.end(), [](const Entry &a, const Entry &b) { return a.weight > b.weight; });
+        cudaStream_t launch_stream = st;
+        for (size_t e0 = 0; e0 < entries.size(); e0 += kMaxPairs) {
+            const int ne = static_cast<int>(std::min<size_t>(kMaxPairs, entries.size() - e0));
+            for (int e = 0; e < ne; ++e) p.pair_order[e] = entries[e0 + e].code;
+            p.num_pairs = ne;
+            p.work_counter = reinterpret_cast<int *>(static_cast<uint8_t *>(workspace) + 64);
+            NPD_CUDA_TRY(cudaMemsetAsync(p.work_counter, 0, sizeof(int), launch_stream));
+            const long long items = (long long)ne * num_kv_heads;
+            const long long grid = items < sms ? items : sms;     // persistent: one CTA per SM
+            kern<<<static_cast<unsigned>(grid), kThreads, smem, launch_stream>>>(p, tq_map, tk, tv);
+            NPD_CUDA_TRY(cudaGetLastError());
+        }
     }
     return NPD_OK;
 }

@@ -1,0 +1,149 @@
+"""The attention step of ``ModelRunner.paged_forward`` on top of the paged kernels.
+
+The reference's closure (nanoPD/engine/model_runner.py:117-212) turns the scheduler's context dict
+(nanoPD/engine/engine.py:68-90) into device tensors INSIDE every layer: one ``torch.tensor(..., device=)``
+per decode sequence and per prompt, 36 times per step with identical content
+(model_runner.py:132-140, 176-187).  Here the context is packed ONCE per step — every table, length and
+position in one pinned staging buffer and one host-to-device copy — and each layer only launches kernels:
+
+    sc = build_step_context(runner._current_context, device)        # once per step
+    attn_out = paged_attention_step(sc, q, k, v, k_cache[layer], v_cache[layer], scale)   # per layer
+
+``paged_attention_step`` replaces the block between the rotary embedding and ``o_proj``
+(model_runner.py:117-210): store the new K/V rows, causal attention of the prompt chunks over their
+paged K/V (all earlier chunks included), decode attention of the running sequences.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from . import paged_kernels
+
+
+@dataclass
+class StepContext:
+    """Device-resident form of one scheduler step (same content as the reference's ``_current_context``)."""
+    num_prefill_tokens: int
+    num_decode_tokens: int
+    block_size: int
+    # prompt chunks, packed one after another in the first num_prefill_tokens rows
+    prefill_tables: Optional[torch.Tensor] = None      # int32 [chunks, max_blk_p], zero padded
+    prefill_positions: Optional[torch.Tensor] = None   # int32 [num_prefill_tokens]
+    prefill_offsets: List[int] = field(default_factory=list)
+    prefill_tokens: List[int] = field(default_factory=list)
+    prefill_starts: List[int] = field(default_factory=list)
+    # decode sequences, one token each, in the last num_decode_tokens rows
+    decode_tables: Optional[torch.Tensor] = None       # int32 [Dn, max_blk_d], zero padded
+    decode_positions: Optional[torch.Tensor] = None    # int32 [Dn]
+    decode_seq_lens: Optional[torch.Tensor] = None     # int32 [Dn] = position + 1
+    h2d_bytes: int = 0
+
+
+def _padded_table(rows: List[List[int]]) -> np.ndarray:
+    width = max(1, max(len(r) for r in rows))
+    out = np.zeros((len(rows), width), dtype=np.int32)
+    for i, r in enumerate(rows):
+        out[i, :len(r)] = r
+    return out
+
+
+def build_step_context(ctx: Dict, device, block_size: int = 16) -> StepContext:
+    """Packs the scheduler's context dict for the device with a single host-to-device copy.
+
+    ``ctx`` has the reference's schema (nanoPD/engine/engine.py:68-90, model_runner.py:32-46):
+    ``num_prefill_tokens``, ``num_decode_tokens``, ``prefills`` (list of ``block_table``,
+    ``start_position``, ``num_tokens``) and ``decodes`` (list of ``block_table``, ``position``).
+    Decode tables are zero padded to the longest one and ``seq_lens = position + 1``, exactly what
+    the reference builds per layer (model_runner.py:176-187).
+    """
+    device = torch.device(device)
+    prefills, decodes = ctx.get("prefills", []), ctx.get("decodes", [])
+    num_p, num_d = int(ctx["num_prefill_tokens"]), int(ctx["num_decode_tokens"])
+    if sum(int(p["num_tokens"]) for p in prefills) != num_p:
+        raise RuntimeError("num_prefill_tokens does not match the prefill entries")
+    if len(decodes) != num_d:
+        raise RuntimeError("num_decode_tokens does not match the decode entries")
+
+    parts: Dict[str, np.ndarray] = {}
+    sc = StepContext(num_prefill_tokens=num_p, num_decode_tokens=num_d, block_size=block_size)
+    if prefills:
+        parts["prefill_tables"] = _padded_table([list(p["block_table"]) for p in prefills])
+        pos, off = [], 0
+        for p in prefills:
+            n, start = int(p["num_tokens"]), int(p["start_position"])
+            if start + n > len(p["block_table"]) * block_size:
+                raise RuntimeError("a prefill chunk reaches beyond its block table")
+            pos.append(np.arange(start, start + n, dtype=np.int32))
+            sc.prefill_offsets.append(off)
+            sc.prefill_tokens.append(n)
+            sc.prefill_starts.append(start)
+            off += n
+        parts["prefill_positions"] = np.concatenate(pos) if pos else np.zeros(0, np.int32)
+    if decodes:
+        parts["decode_tables"] = _padded_table([list(d["block_table"]) for d in decodes])
+        positions = np.asarray([int(d["position"]) for d in decodes], dtype=np.int32)
+        for d, p in zip(decodes, positions):
+            if p // block_size >= len(d["block_table"]):
+                raise RuntimeError("a decode position lies beyond its block table")
+        parts["decode_positions"] = positions
+        parts["decode_seq_lens"] = positions + 1
+
+    # one staging buffer, 256-byte aligned sections, one copy
+    offsets, total = {}, 0
+    for name, arr in parts.items():
+        offsets[name] = total
+        total += (arr.nbytes + 255) // 256 * 256
+    sc.h2d_bytes = total
+    if total == 0:
+        return sc
+    stage = torch.empty(total, dtype=torch.uint8)
+    if device.type == "cuda":
+        stage = stage.pin_memory()
+    host = stage.numpy()
+    for name, arr in parts.items():
+        host[offsets[name]:offsets[name] + arr.nbytes] = arr.reshape(-1).view(np.uint8)
+    dev_buf = stage.to(device, non_blocking=True)
+    for name, arr in parts.items():
+        view = dev_buf[offsets[name]:offsets[name] + arr.nbytes].view(torch.int32).view(arr.shape)
+        setattr(sc, name, view)
+    sc._staging = (stage, dev_buf)      # keeps the pinned buffer alive until the copy has run
+    return sc
+
+
+def paged_attention_step(sc: StepContext, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                         k_cache: torch.Tensor, v_cache: torch.Tensor, scale: float) -> torch.Tensor:
+    """Store + attention of one layer for one step.
+
+    ``q`` is ``[1, Hq, total, D]``, ``k``/``v`` ``[1, Hkv, total, D]`` after the rotary embedding (the tensors
+    the reference holds at model_runner.py:115); the first ``num_prefill_tokens`` columns are the packed
+    prompt chunks, the rest one token per decode sequence.  ``k_cache``/``v_cache`` are the layer's
+    ``[blocks, Hkv, B, D]`` pools.  Returns ``[1, total, Hq*D]`` like the reference's ``attn_out``
+    (model_runner.py:210) — with one difference the reference's tests do not cover: a chunk with
+    ``start_position > 0`` attends to the earlier chunks' keys in the pages as well.
+    """
+    P, Dn = sc.num_prefill_tokens, sc.num_decode_tokens
+    total = P + Dn
+    _, hq, tq, d = q.shape
+    if tq != total or k.size(2) != total or v.size(2) != total:
+        raise RuntimeError("q/k/v token count does not match the step context")
+    bs = k_cache.size(2)
+    out = torch.empty(total, hq, d, dtype=q.dtype, device=q.device)
+    if P > 0:
+        for i, (off, n) in enumerate(zip(sc.prefill_offsets, sc.prefill_tokens)):
+            # the prompt's table row, read in place for every token of the chunk (stride-0 expand)
+            paged_kernels.paged_kv_store(k_cache, v_cache, k[0, :, off:off + n], v[0, :, off:off + n],
+                                         sc.prefill_tables[i:i + 1].expand(n, -1), sc.prefill_positions[off:off + n])
+        q_p = q[0, :, :P].transpose(0, 1).contiguous()
+        paged_kernels.paged_prefill_attention(out[:P], q_p, k_cache, v_cache, sc.prefill_tables,
+                                              sc.prefill_offsets, sc.prefill_tokens, sc.prefill_starts,
+                                              scale, bs, sc.prefill_tables.size(1))
+    if Dn > 0:
+        paged_kernels.paged_kv_store(k_cache, v_cache, k[0, :, P:], v[0, :, P:], sc.decode_tables, sc.decode_positions)
+        q_d = q[0, :, P:].transpose(0, 1).contiguous()
+        paged_kernels.paged_attention_forward(out[P:], q_d, k_cache, v_cache, sc.decode_tables, sc.decode_seq_lens,
+                                              scale, bs, sc.decode_tables.size(1))
+    return out.view(1, total, hq * d)
