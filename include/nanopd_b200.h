@@ -41,7 +41,7 @@ extern "C" {
 #define NPD_STATUS_WAIT_TIMEOUT   4   /* a bounded wait on an in-kernel barrier ran out                       */
 
 /* Flags of npd_paged_decode_attention */
-#define NPD_DECODE_SKIP_MERGE     1   /* diagnostic: run only the streaming kernel (split sequences stay unmerged) */
+#define NPD_DECODE_SKIP_MERGE     1   /* diagnostic: sequences split across workers stay unmerged (wrong rows for those) */
 
 int         npd_version(void);
 const char *npd_last_error(void);

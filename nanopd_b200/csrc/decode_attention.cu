@@ -17,9 +17,10 @@
 //     operand with movmatrix, O^T = V^T . P^T accumulated in fp32 registers.
 //   * A (sequence, kv head) whose tiles fall into one worker is normalised and written
 //     straight to `out`.  One cut by a range boundary leaves fp32 partials (m, l, O) in the
-//     workspace — at most two per worker — and a small second kernel merges them
-//     (the role of paged_attention_reduce_kernel, csrc/paged_attention_optimized/
-//     paged_attention_optimized.cu:173-219, without its per-call allocations and sync).
+//     workspace — at most two per worker; the worker that delivers the LAST partial of a
+//     (sequence, kv head) — found with an atomic ticket, no spinning — merges them in the
+//     same kernel (the role of paged_attention_reduce_kernel, csrc/paged_attention_optimized/
+//     paged_attention_optimized.cu:173-219, without a second launch, per-call allocations or a sync).
 //   * Every mbarrier wait is bounded; on time-out the warp raises NPD_STATUS_WAIT_TIMEOUT
 //     and leaves.  Out-of-range block ids are redirected to an out-of-bounds TMA coordinate
 //     (zero fill) and flagged — nothing can fault.
@@ -38,6 +39,8 @@ constexpr int kTile = 16;               // tokens per stage
 constexpr int kMaxSeqsPerLaunch = 4096; // prefix array lives in shared memory
 constexpr int kMinTilesPerWorker = 4;   // keeps tiny batches from dissolving into partials
 constexpr int kStatusBytes = 256;       // workspace header: status word + padding
+constexpr int kTicketCapacity = 1 << 18;   // ticket words (1 MiB): a FIXED region right after the header, so that no
+                                        // launch shape ever puts partial records where another shape keeps tickets
 
 struct DecodeParams {
     void *out;
@@ -45,8 +48,9 @@ struct DecodeParams {
     const int32_t *block_tables;
     const int32_t *seq_lens;
     int32_t *status;
-    int32_t *prefix;      // [num_seqs + 1] tile prefix, written by CTA 0 for the merge kernel
+    int32_t *tickets;     // [num_seqs * num_vheads] partials delivered so far; zero between launches
     float *partials;      // [num_workers][2][rec_floats]
+    int skip_merge;       // diagnostic: leave cut (sequence, kv head) pairs unmerged
     float scale_log2;
     int num_seqs;
     int num_q_heads;
@@ -257,6 +261,40 @@ __device__ __forceinline__ void write_partial(const AttnState<T, D, NT> &st, flo
     }
 }
 
+// Folds the partial records of workers wf..wl (one (sequence, kv head) cut by range boundaries) into `st`.
+// Records were written by other SMs during this launch: read them through L2 (ld.global.cg), never L1.
+template <typename T, int D, int NT>
+__device__ __forceinline__ void merge_partials(AttnState<T, D, NT> &st, const DecodeParams &p, int wf, int wl, int lane) {
+    constexpr int KS = D / 16;
+    st.reset();
+    for (int w = wf; w <= wl; ++w) {
+        const float *rec = p.partials + ((size_t)w * 2 + (w == wf ? 1 : 0)) * rec_floats<D, NT>();
+        const float4 *o4 = reinterpret_cast<const float4 *>(rec);
+        const float4 *ml4 = reinterpret_cast<const float4 *>(rec + NT * KS * 128);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const float4 ml = __ldcg(ml4 + nt * 4 + (lane & 3));
+            const float mn0 = fmaxf(st.m[nt][0], ml.x), mn1 = fmaxf(st.m[nt][1], ml.y);
+            const float so0 = st.m[nt][0] == -INFINITY ? 0.f : fast_exp2(st.m[nt][0] - mn0);
+            const float so1 = st.m[nt][1] == -INFINITY ? 0.f : fast_exp2(st.m[nt][1] - mn1);
+            const float sn0 = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - mn0);
+            const float sn1 = ml.y == -INFINITY ? 0.f : fast_exp2(ml.y - mn1);
+            st.l[nt][0] = st.l[nt][0] * so0 + ml.z * sn0;
+            st.l[nt][1] = st.l[nt][1] * so1 + ml.w * sn1;
+            st.m[nt][0] = mn0;
+            st.m[nt][1] = mn1;
+#pragma unroll
+            for (int j = 0; j < KS; ++j) {
+                const float4 o = __ldcg(o4 + (nt * KS + j) * 32 + lane);
+                st.o[nt][j][0] = st.o[nt][j][0] * so0 + o.x * sn0;
+                st.o[nt][j][1] = st.o[nt][j][1] * so1 + o.y * sn1;
+                st.o[nt][j][2] = st.o[nt][j][2] * so0 + o.z * sn0;
+                st.o[nt][j][3] = st.o[nt][j][3] * so1 + o.w * sn1;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Streaming kernel
 // ---------------------------------------------------------------------------
@@ -292,8 +330,13 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
         tma_prefetch_desc(&tm_v);
     }
     build_tile_prefix(p, pre);   // ends with __syncthreads(): barriers are initialised for everyone
-    if (blockIdx.x == 0)
-        for (int i = threadIdx.x; i <= p.num_seqs; i += blockDim.x) p.prefix[i] = pre[i];
+    // Empty sequences get zero rows, as the reference's kernel leaves them
+    // (nanoPD/paged_attention/csrc/attention/paged_attention_kernel.cu:117-150 with seq_len 0).
+    for (int s0 = blockIdx.x; s0 < p.num_seqs; s0 += gridDim.x) {
+        if (pre[s0 + 1] != pre[s0]) continue;
+        uint32_t *row = reinterpret_cast<uint32_t *>(static_cast<T *>(p.out) + (long long)s0 * p.num_q_heads * D);
+        for (int i = threadIdx.x; i < p.num_q_heads * D / 2; i += blockDim.x) row[i] = 0u;
+    }
 
     const long long total = (long long)p.num_vheads * pre[p.num_seqs];
     const long long W = tiles_per_worker(total, p.num_workers);
@@ -497,6 +540,24 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
         } else {
             float *rec = p.partials + ((size_t)worker * 2 + (head_cut ? 0 : 1)) * rec_floats<D, NT>();
             write_partial<T, D, NT>(st, rec, lane);
+            if (!p.skip_merge) {
+                // Which workers share this (sequence, kv head)?  The one whose ticket is the last merges.
+                const int n_s = pre[seg_s + 1] - pre[seg_s];
+                const long long fb = (long long)p.num_vheads * pre[seg_s] + (long long)seg_h * n_s;
+                const int wf = static_cast<int>(fb / W), wl = static_cast<int>((fb + n_s - 1) / W);
+                __threadfence();                       // every lane: my part of the record is visible device-wide
+                __syncwarp();
+                int ticket = 0;
+                int *slot = p.tickets + seg_s * p.num_vheads + seg_h;
+                if (lane == 0) ticket = atomicAdd(slot, 1);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket == wl - wf) {
+                    __threadfence();                   // the other workers' records are visible to me
+                    merge_partials<T, D, NT>(st, p, wf, wl, lane);
+                    write_output<T, D, NT>(st, p, seg_s, seg_h, lane);
+                    if (lane == 0) *slot = 0;          // ready for the next launch
+                }
+            }
         }
     }
 
@@ -512,63 +573,6 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
             }
         }
     }
-}
-
-// ---------------------------------------------------------------------------
-// Merge kernel: one warp per (sequence, virtual kv head)
-// ---------------------------------------------------------------------------
-template <typename T, int D, int NT>
-__global__ void __launch_bounds__(256)
-paged_decode_merge_kernel(const DecodeParams p) {
-    constexpr int KS = D / 16;
-    const int lane = threadIdx.x & 31;
-    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= p.num_seqs * p.num_vheads) return;
-    const int s = item / p.num_vheads, h = item - s * p.num_vheads;
-    const int *Tp = p.prefix;
-    const int n = Tp[s + 1] - Tp[s];
-    if (n == 0) {
-        // Empty sequence: zero rows, as the reference's kernel leaves them
-        // (nanoPD/paged_attention/csrc/attention/paged_attention_kernel.cu:117-150 with seq_len 0).
-        T *row = static_cast<T *>(p.out) + ((long long)s * p.num_q_heads + (long long)h * p.group) * D;
-        for (int i = lane; i < p.group * D / 2; i += 32) reinterpret_cast<uint32_t *>(row)[i] = 0u;
-        return;
-    }
-    const long long total = (long long)p.num_vheads * Tp[p.num_seqs];
-    const long long W = tiles_per_worker(total, p.num_workers);
-    const long long fb = (long long)p.num_vheads * Tp[s] + (long long)h * n, fe = fb + n;
-    const int wf = static_cast<int>(fb / W), wl = static_cast<int>((fe - 1) / W);
-    if (wf == wl) return;   // written directly by its worker
-
-    AttnState<T, D, NT> st;
-    st.reset();
-    for (int w = wf; w <= wl; ++w) {
-        const float *rec = p.partials + ((size_t)w * 2 + (w == wf ? 1 : 0)) * rec_floats<D, NT>();
-        const float4 *o4 = reinterpret_cast<const float4 *>(rec);
-        const float4 *ml4 = reinterpret_cast<const float4 *>(rec + NT * KS * 128);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const float4 ml = ml4[nt * 4 + (lane & 3)];
-            const float mn0 = fmaxf(st.m[nt][0], ml.x), mn1 = fmaxf(st.m[nt][1], ml.y);
-            const float so0 = st.m[nt][0] == -INFINITY ? 0.f : fast_exp2(st.m[nt][0] - mn0);
-            const float so1 = st.m[nt][1] == -INFINITY ? 0.f : fast_exp2(st.m[nt][1] - mn1);
-            const float sn0 = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - mn0);
-            const float sn1 = ml.y == -INFINITY ? 0.f : fast_exp2(ml.y - mn1);
-            st.l[nt][0] = st.l[nt][0] * so0 + ml.z * sn0;
-            st.l[nt][1] = st.l[nt][1] * so1 + ml.w * sn1;
-            st.m[nt][0] = mn0;
-            st.m[nt][1] = mn1;
-#pragma unroll
-            for (int j = 0; j < KS; ++j) {
-                const float4 o = o4[(nt * KS + j) * 32 + lane];
-                st.o[nt][j][0] = st.o[nt][j][0] * so0 + o.x * sn0;
-                st.o[nt][j][1] = st.o[nt][j][1] * so1 + o.y * sn1;
-                st.o[nt][j][2] = st.o[nt][j][2] * so0 + o.z * sn0;
-                st.o[nt][j][3] = st.o[nt][j][3] * so1 + o.w * sn1;
-            }
-        }
-    }
-    write_output<T, D, NT>(st, p, s, h, lane);
 }
 
 // ---------------------------------------------------------------------------
@@ -608,34 +612,29 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <typename T, int D, int NT>
 int launch_decode(const DecodeParams &p, const CUtensorMap &tk, const CUtensorMap &tv, const LaunchShape &ls,
-                  bool merge, cudaStream_t stream) {
+                  cudaStream_t stream) {
     constexpr int STAGE_BYTES = 2 * kTile * D * 2;
     const size_t smem = 1024 + (size_t)ls.nwarps * ls.nstages * (STAGE_BYTES + 8) + ((size_t)p.num_seqs + 1) * 4 + 16;
     auto kern = paged_decode_stream_kernel<T, D, NT>;
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<ls.grid, ls.nwarps * 32, smem, stream>>>(p, tk, tv);
     NPD_CUDA_TRY(cudaGetLastError());
-    if (merge) {
-        const int items = p.num_seqs * p.num_vheads;
-        paged_decode_merge_kernel<T, D, NT><<<(items + 7) / 8, 256, 0, stream>>>(p);
-        NPD_CUDA_TRY(cudaGetLastError());
-    }
     return NPD_OK;
 }
 
 template <typename T>
 int dispatch_decode(int head_dim, int nt, const DecodeParams &p, const CUtensorMap &tk, const CUtensorMap &tv,
-                    const LaunchShape &ls, bool merge, cudaStream_t stream) {
-    if (head_dim == 64 && nt == 1) return launch_decode<T, 64, 1>(p, tk, tv, ls, merge, stream);
-    if (head_dim == 64 && nt == 2) return launch_decode<T, 64, 2>(p, tk, tv, ls, merge, stream);
-    if (head_dim == 128 && nt == 1) return launch_decode<T, 128, 1>(p, tk, tv, ls, merge, stream);
-    if (head_dim == 128 && nt == 2) return launch_decode<T, 128, 2>(p, tk, tv, ls, merge, stream);
-    if (head_dim == 256 && nt == 1) return launch_decode<T, 256, 1>(p, tk, tv, ls, merge, stream);
+                    const LaunchShape &ls, cudaStream_t stream) {
+    if (head_dim == 64 && nt == 1) return launch_decode<T, 64, 1>(p, tk, tv, ls, stream);
+    if (head_dim == 64 && nt == 2) return launch_decode<T, 64, 2>(p, tk, tv, ls, stream);
+    if (head_dim == 128 && nt == 1) return launch_decode<T, 128, 1>(p, tk, tv, ls, stream);
+    if (head_dim == 128 && nt == 2) return launch_decode<T, 128, 2>(p, tk, tv, ls, stream);
+    if (head_dim == 256 && nt == 1) return launch_decode<T, 256, 1>(p, tk, tv, ls, stream);
     return npd::fail(NPD_ERR_UNSUPPORTED, "decode attention: no kernel for head_dim %d with %d head tiles", head_dim, nt);
 }
 
 struct WorkspacePlan {
-    size_t prefix_off, partial_off, total;
+    size_t ticket_off, partial_off, total;
     int kv_rep, nt, group;
 };
 
@@ -649,8 +648,9 @@ WorkspacePlan plan_workspace(int64_t num_seqs, int64_t num_q_heads, int64_t num_
     w.nt = w.group <= 8 ? 1 : 2;
     const size_t seqs = static_cast<size_t>(num_seqs < kMaxSeqsPerLaunch ? num_seqs : kMaxSeqsPerLaunch);
     const size_t rec = (size_t)w.nt * ((size_t)(head_dim / 16) * 128 + 16) * sizeof(float);
-    w.prefix_off = kStatusBytes;
-    w.partial_off = align_up(w.prefix_off + (seqs + 1) * sizeof(int32_t), 256);
+    (void)seqs;
+    w.ticket_off = kStatusBytes;
+    w.partial_off = align_up(w.ticket_off + (size_t)kTicketCapacity * sizeof(int32_t), 256);
     w.total = w.partial_off + (size_t)ls.grid * ls.nwarps * 2 * rec;
     return w;
 }
@@ -716,7 +716,7 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     DecodeParams p;
     p.status = reinterpret_cast<int32_t *>(ws);
-    p.prefix = reinterpret_cast<int32_t *>(ws + wp.prefix_off);
+    p.tickets = reinterpret_cast<int32_t *>(ws + wp.ticket_off);
     p.partials = reinterpret_cast<float *>(ws + wp.partial_off);
     p.scale_log2 = scale * 1.4426950408889634f;
     p.num_q_heads = static_cast<int>(num_q_heads);
@@ -732,20 +732,23 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
     p.num_stages = ls.nstages;
 
     const size_t elem = 2;
-    const bool merge = (flags & NPD_DECODE_SKIP_MERGE) == 0;
+    p.skip_merge = (flags & NPD_DECODE_SKIP_MERGE) != 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Batches beyond the shared-memory prefix capacity run as consecutive sub-batches; the
     // stream orders their use of the workspace.
-    for (int64_t s0 = 0; s0 < num_seqs; s0 += kMaxSeqsPerLaunch) {
-        const int64_t ns = num_seqs - s0 < kMaxSeqsPerLaunch ? num_seqs - s0 : kMaxSeqsPerLaunch;
+    int64_t batch_cap = kTicketCapacity / p.num_vheads;
+    if (batch_cap > kMaxSeqsPerLaunch) batch_cap = kMaxSeqsPerLaunch;
+    NPD_REQUIRE(batch_cap >= 1, NPD_ERR_UNSUPPORTED, "decode attention: too many kv heads (%d virtual heads)", p.num_vheads);
+    for (int64_t s0 = 0; s0 < num_seqs; s0 += batch_cap) {
+        const int64_t ns = num_seqs - s0 < batch_cap ? num_seqs - s0 : batch_cap;
         p.num_seqs = static_cast<int>(ns);
         p.out = static_cast<uint8_t *>(out) + (size_t)s0 * num_q_heads * head_dim * elem;
         p.q = static_cast<const uint8_t *>(q) + (size_t)s0 * num_q_heads * head_dim * elem;
         p.block_tables = block_tables + s0 * bt_row_stride;
         p.seq_lens = seq_lens + s0;
         rc = dtype == NPD_DTYPE_F16
-                 ? dispatch_decode<__half>(static_cast<int>(head_dim), wp.nt, p, tk, tv, ls, merge, st)
-                 : dispatch_decode<__nv_bfloat16>(static_cast<int>(head_dim), wp.nt, p, tk, tv, ls, merge, st);
+                 ? dispatch_decode<__half>(static_cast<int>(head_dim), wp.nt, p, tk, tv, ls, st)
+                 : dispatch_decode<__nv_bfloat16>(static_cast<int>(head_dim), wp.nt, p, tk, tv, ls, st);
         if (rc != NPD_OK) return rc;
     }
     return NPD_OK;
