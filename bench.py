@@ -441,9 +441,9 @@ def run_gpu_arm(args):
             "gpu_launches": 2 * steps,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
-                         # DRAM bytes per launch from the ncu capture of a batch-64 case (read 1.0037 x algorithmic,
+                         # DRAM bytes per launch from the ncu capture of a batch-64 case (read 1.0087 x algorithmic,
                          # plus ~7 MB of partial/output writes), scaled by the tokens processed
-                         "traffic": int(attn_bytes * 1.0037 + 7e6), "traffic_source": "profiles/decode_stream_batch64_ncu_full.md",
+                         "traffic": int(attn_bytes * 1.0087 + 7e6), "traffic_source": "profiles/decode_stream_batch64_ncu_full.md",
                          "peak_source": peak_src,
                          "kernel": "paged_decode_stream_kernel<bf16,128,1>",
                          "algorithmic_bytes_per_launch": attn_bytes, "launch_ms": round(ms_stream_max, 5)},

@@ -44,7 +44,17 @@ constexpr int kKvTileBytes = 2 * kKvHalfBytes;      // 32 KiB
 constexpr int kStages = 2;                          // K ring and V ring depth
 constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; the packed probabilities of a key
                                    // tile overwrite the first 64 columns of its scores
-constexpr int kPolyPairsOf8 = 0;           // of every 8 score pairs, this many take the polynomial exp2
+#ifndef NPD_STAGGER
+#define NPD_STAGGER 1
+#endif
+// Tile B starts an item half a step behind tile A: the two softmax groups then alternate on the special-function
+// units and the two MMA streams alternate on the tensor pipe instead of running in lock-step.
+constexpr bool kStagger = NPD_STAGGER != 0;
+constexpr long long kStaggerWaitCycles = 4000;
+#ifndef NPD_POLY_PAIRS_OF_8
+#define NPD_POLY_PAIRS_OF_8 0
+#endif
+constexpr int kPolyPairsOf8 = NPD_POLY_PAIRS_OF_8;           // of every 8 score pairs, this many take the polynomial exp2
 constexpr float kRescaleThreshold = 8.f;   // log2 units: O is rescaled only when a row max grows by more
 constexpr long long kWaitCycles = 4000000000LL;
 
@@ -215,36 +225,41 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 // Optional phase tracing for performance work (compiled out unless NPD_PREFILL_TRACE is defined):
 // the CTA with blockIdx.x == 0 appends (tag, key tile, clock) triples to the workspace after its header.
 #ifdef NPD_PREFILL_TRACE
+#define NPD_TRACE_DECL int trace_n_ = 0;
 #define NPD_TRACE(role, tag, j)                                                                   \
     do {                                                                                          \
-        if (blockIdx.x == NPD_PREFILL_TRACE && p.trace) {                                         \
-            long long *t_ = p.trace + (role) * 4096;                                              \
-            const int n_ = static_cast<int>(t_[0]);                                               \
-            if (n_ < 1300) {                                                                      \
-                t_[1 + 3 * n_] = (tag);                                                           \
-                t_[2 + 3 * n_] = (j);                                                             \
-                t_[3 + 3 * n_] = clock64();                                                       \
-                t_[0] = n_ + 1;                                                                   \
-            }                                                                                     \
+        if (blockIdx.x == NPD_PREFILL_TRACE && p.trace && trace_n_ < 2040) {                      \
+            longlong2 e_;                                                                         \
+            e_.x = (static_cast<long long>(tag) << 32) | static_cast<unsigned>(j);               \
+            e_.y = clock64();                                                                     \
+            reinterpret_cast<longlong2 *>(p.trace + (role) * 4096)[trace_n_++] = e_;              \
         }                                                                                         \
     } while (0)
 #else
+#define NPD_TRACE_DECL
 #define NPD_TRACE(role, tag, j) do { } while (0)
+#endif
+#ifdef NPD_PREFILL_TRACE_FINE
+#define NPD_TRACE_FINE(role, tag, j) NPD_TRACE(role, tag, j)
+#else
+#define NPD_TRACE_FINE(role, tag, j) do { } while (0)
 #endif
 
 struct alignas(8) SmemCtrl {
     uint64_t sched_full[kSchedSlots];   // the producer warp has published the next work item
     int sched_item[kSchedSlots];
-    uint64_t q_full;             // both query tiles of the current work item have landed
-    uint64_t q_empty;            // both MMA warps have issued their last score MMA of the item (2 arrivals)
+    uint64_t q_full[2];          // [query tile]: its rows of the current work item have landed
+    uint64_t q_empty[2];         // [query tile]: its MMA warp has issued the last score MMA of the item
     uint64_t k_full[kStages], v_full[kStages];     // the K / V tile of a ring stage has landed
     uint64_t k_empty[kStages], v_empty[kStages];   // both MMA warps are done with it (2 arrivals)
     uint64_t s_full[2];     // [query tile]: the score tile of the next key tile is in TMEM (and every earlier PV done)
-    uint64_t p_full[2];     // [query tile]: the probabilities are in TMEM (128 arrivals)
+    uint64_t p_half[2];     // [query tile]: the probabilities of the first 64 keys are in TMEM (128 arrivals)
+    uint64_t p_full[2];     // [query tile]: all probabilities are in TMEM (128 arrivals)
     uint64_t o_full[2];     // [query tile]: the last PV MMA of the work item has completed
     uint64_t o_free[2];     // [query tile]: the epilogue has taken O out of TMEM (128 arrivals)
     uint32_t tmem_base;
     int abort_flag;
+    int sm_progress[2];     // [query tile]: key-tile steps whose first half of P has been released (running count)
 };
 
 // One work item = a pair of 128-row query tiles of one chunk and one kv head.
@@ -305,8 +320,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     };
 
     if (threadIdx.x == 0) {
-        mbar_init(smem_u32(&ctrl->q_full), 1);
-        mbar_init(smem_u32(&ctrl->q_empty), 2);
         for (int i = 0; i < kSchedSlots; ++i) mbar_init(smem_u32(&ctrl->sched_full[i]), 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(smem_u32(&ctrl->k_full[i]), 1);
@@ -315,12 +328,16 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             mbar_init(smem_u32(&ctrl->v_empty[i]), 2);
         }
         for (int x = 0; x < 2; ++x) {
+            mbar_init(smem_u32(&ctrl->q_full[x]), 1);
+            mbar_init(smem_u32(&ctrl->q_empty[x]), 1);
             mbar_init(smem_u32(&ctrl->s_full[x]), 1);
+            mbar_init(smem_u32(&ctrl->p_half[x]), 128);
             mbar_init(smem_u32(&ctrl->p_full[x]), 128);
             mbar_init(smem_u32(&ctrl->o_full[x]), 1);
             mbar_init(smem_u32(&ctrl->o_free[x]), 128);
         }
         ctrl->abort_flag = 0;
+        ctrl->sm_progress[0] = ctrl->sm_progress[1] = 0;
         mbar_fence_init();
     }
     if (warp == 9) {
@@ -349,6 +366,8 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         const int role = lane >> 4, gi = (lane >> 1) & 7, hf = lane & 1;     // role 0 = K, 1 = V
         const CUtensorMap *tm = role == 1 ? &tm_v : &tm_k;
         int g = 0;                                              // g: key tiles loaded so far (ring position)
+        int q_loads[2] = {0, 0};                                // per query tile: items loaded so far (phases of q_empty)
+        NPD_TRACE_DECL
         bool ok = true;
         for (int k = 0; ok; ++k) {
             // Fetch and publish the next work item.  A slot is reused kSchedSlots items later; by then every
@@ -364,20 +383,25 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             item = __shfl_sync(0xffffffffu, item, 0);
             if (item < 0) break;
             const Item it = decode_item(p, item);
-            // ---- query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch
-            if (k > 0) ok = wait_or_abort(smem_u32(&ctrl->q_empty), (k - 1) & 1, abort_flag, p.status);
-            if (!__all_sync(0xffffffffu, ok)) break;
-            if (lane == 0) {
-                const uint32_t qbar = smem_u32(&ctrl->q_full);
-                const int nq = (it.tq_valid[0] > 0 ? 1 : 0) + (it.tq_valid[1] > 0 ? 1 : 0);
-                mbar_expect_tx(qbar, static_cast<uint32_t>(nq * 2 * p.tq * p.group * 128));
-                for (int x = 0; x < 2; ++x) {
-                    if (it.tq_valid[x] <= 0) continue;
+            // ---- query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch.
+            //      Each tile has its own barriers, so a tile that finishes an item early moves on alone.  Tile B's
+            //      rows are requested after the first K tile: tile A, half a step ahead, needs that one first.
+            auto load_q = [&](int x) {
+                if (it.tq_valid[x] <= 0) return true;
+                bool good = true;
+                if (q_loads[x] > 0) good = wait_or_abort(smem_u32(&ctrl->q_empty[x]), (q_loads[x] - 1) & 1, abort_flag, p.status);
+                if (!__all_sync(0xffffffffu, good)) return false;
+                ++q_loads[x];
+                if (lane == 0) {
+                    const uint32_t qbar = smem_u32(&ctrl->q_full[x]);
+                    mbar_expect_tx(qbar, static_cast<uint32_t>(2 * p.tq * p.group * 128));
                     for (int h2 = 0; h2 < 2; ++h2)
                         tma_load_3d(smem_u32(q_tiles + x * kQTileBytes + h2 * kQHalfBytes), &tm_q, qbar, h2 * 64,
                                     it.h * p.group, it.qoff + it.tok0[x]);
                 }
-            }
+                return true;
+            };
+            if (!(ok = load_q(0))) break;
             const int32_t *table = p.block_tables + (long long)it.c * p.bt_row_stride;
             auto lookup = [&](int t) {
                 const int key = t * kKeys + gi * 16;
@@ -416,6 +440,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (!(NPD_EXPERIMENT_FLAGS(p) & 4) && role == 0 && gi < ngroups)
                     tma_load_3d(smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
                                 hf * 64, row, id);
+                if (t == 0 && !(ok = load_q(1))) break;
                 // ---- V tile (lanes 16-31): free once the PV MMAs two tiles back are done
                 if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
                 if (!__all_sync(0xffffffffu, ok)) break;
@@ -472,30 +497,39 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             };
             // O_X (+)= P_X . V of ring stage `stage`: P from TMEM (packed pairs over the first 64 score columns,
             // 8 columns per 16 keys), V MN-major from shared memory (16 keys = two 8-row groups = 2 KiB further on)
-            auto issue_pv = [&](int stage, bool first, bool last) {
+            // (issued in two halves of 64 keys: the first starts while the softmax group still works on the second)
+            auto issue_pv = [&](int stage, int half, bool first, bool last) {
                 const uint64_t vd = v_desc0 + static_cast<uint64_t>((stage * kKvTileBytes) >> 4);
                 if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < kKeys / 16; ++ks)
+                    for (int ks = half * (kKeys / 32); ks < (half + 1) * (kKeys / 32); ++ks)
                         if (!(NPD_EXPERIMENT_FLAGS(p) & 2))
                             tc_mma_ts(t_o, t_sx + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
                                       (!first || ks > 0) ? 1u : 0u);
-                    if (last) tc_commit(smem_u32(&ctrl->o_full[x]));
+                    if (last && half == 1) tc_commit(smem_u32(&ctrl->o_full[x]));
                 }
                 __syncwarp();
             };
 
             int g = 0;         // key tiles seen so far (ring position of the item's first key tile)
             int cnt = 0;       // own key tiles processed so far (phases of s_full and p_full)
+            int cnt_other = 0; // the other query tile's count at the start of the current item
             int items_done = 0;   // items in which this query tile had work (phases of o_full and o_free)
+            NPD_TRACE_DECL
             bool ok = true;
             for (int k = 0; ok; ++k) {
                 const int item = next_item(k, ok);
                 if (!__all_sync(0xffffffffu, ok) || item < 0) break;
                 const Item it = decode_item(p, item);
                 const int my_tiles = it.ntiles[x];
-                if (!(ok = wait_all(&ctrl->q_full, k & 1))) break;
                 if (my_tiles > 0) {
+                    if (!(ok = wait_all(&ctrl->q_full[x], items_done & 1))) break;
+                    if (kStagger && x == 1 && it.ntiles[0] > 0) {
+                        // advisory and bounded: go on once tile A has released half of its first step of this item
+                        const long long t_start = clock64();
+                        while (*reinterpret_cast<volatile int *>(&ctrl->sm_progress[0]) <= cnt_other &&
+                               clock64() - t_start < kStaggerWaitCycles) { }
+                    }
                     // (the score columns are free: the previous item's last PV, which read P from them, was
                     // issued before this MMA and MMAs execute in issue order)
                     if (!(ok = wait_all(&ctrl->k_full[g % kStages], (g / kStages) & 1))) break;
@@ -503,7 +537,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     issue_s(g % kStages);
                     commit(&ctrl->k_empty[g % kStages]);
                 }
-                if (my_tiles <= 1) commit(&ctrl->q_empty);   // no further score MMA of this item reads Q_X
+                if (my_tiles == 1) commit(&ctrl->q_empty[x]);   // no further score MMA of this item reads Q_X
                 for (int t = 0; ok && t < it.n_kv; ++t) {
                     const int gt = g + t, stage = gt % kStages;
                     if (t < my_tiles) {
@@ -511,17 +545,24 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         // O_X is overwritten by the first PV of an item: the previous epilogue must have read it
                         if (t == 0 && items_done > 0 && !(ok = wait_all(&ctrl->o_free[x], (items_done - 1) & 1))) break;
                         if (!(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
-                        if (!(ok = wait_all(&ctrl->p_full[x], ct & 1))) break;
+                        NPD_TRACE(x == 0 ? 1 : 4, 10, t);
+                        if (!(ok = wait_all(&ctrl->p_half[x], ct & 1))) break;
                         tc_fence_after();
-                        issue_pv(stage, t == 0, t + 1 == my_tiles);
+                        issue_pv(stage, 0, t == 0, t + 1 == my_tiles);
+                        if (t + 1 < my_tiles &&
+                            !(ok = wait_all(&ctrl->k_full[(gt + 1) % kStages], ((gt + 1) / kStages) & 1))) break;
+                        if (!(ok = wait_all(&ctrl->p_full[x], ct & 1))) break;
+                        NPD_TRACE(x == 0 ? 1 : 4, 11, t);
+                        tc_fence_after();
+                        issue_pv(stage, 1, t == 0, t + 1 == my_tiles);
                         commit(&ctrl->v_empty[stage]);
                         if (t + 1 < my_tiles) {
                             // S(t+1) overwrites the columns P(t) sits in; it executes after the PV MMAs above
-                            if (!(ok = wait_all(&ctrl->k_full[(gt + 1) % kStages], ((gt + 1) / kStages) & 1))) break;
-                            tc_fence_after();
+                            NPD_TRACE(x == 0 ? 1 : 4, 12, t);
                             issue_s((gt + 1) % kStages);
+                            NPD_TRACE(x == 0 ? 1 : 4, 13, t);
                             commit(&ctrl->k_empty[(gt + 1) % kStages]);
-                            if (t + 2 == my_tiles) commit(&ctrl->q_empty);   // that was the last one
+                            if (t + 2 == my_tiles) commit(&ctrl->q_empty[x]);   // that was the last one
                         }
                     } else {
                         // a key tile only the other query tile needs: observe it so that ring phases stay in step
@@ -533,6 +574,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 g += it.n_kv;
                 cnt += my_tiles;
+                cnt_other += it.ntiles[x ^ 1];
                 items_done += my_tiles > 0 ? 1 : 0;
             }
         }
@@ -549,6 +591,9 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
         int g = 0, cnt = 0, items_seen = 0;                   // items_seen: items in which this tile had work
+        const int sm_role = wq == 0 ? 2 + x : 5 + x * 3 + (wq - 1);   // trace slot (used only by tracing builds)
+        (void)sm_role;
+        NPD_TRACE_DECL
         bool ok = true;
 
         for (int k = 0; ok; ++k) {
@@ -579,15 +624,19 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 // s_full(t) also tells that every earlier PV MMA of this query tile has completed (commits
                 // cover all MMAs issued before them), so O may be rescaled below without a further wait.
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 20, t);
                 if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x]), ct & 1, abort_flag, p.status))) break;
+                if (lane == 0) NPD_TRACE(sm_role, 21, t);
                 tc_fence_after();
                 // The whole score row of this key tile (128 fp32) moves to registers: one TMEM read.
                 float sc[4][32];
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) tmem_ld32(t_sx + cc * 32, sc[cc]);
                 tmem_wait_ld();
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 22, t);
                 if (NPD_EXPERIMENT_FLAGS(p) & 1) {
                     tc_fence_before();
+                    mbar_arrive(smem_u32(&ctrl->p_half[x]));
                     mbar_arrive(smem_u32(&ctrl->p_full[x]));
                     l_run = 1.f;
                     continue;
@@ -599,6 +648,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         for (int i = 0; i < 32; ++i)
                             if (key0 + cc * 32 + i > pos) sc[cc][i] = -INFINITY;
                 }
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 40, t);
                 // ---- row maximum: eight independent chains of three-input max ----
                 float mxa[8];
 #pragma unroll
@@ -610,6 +660,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         mxa[q8] = fmax3(mxa[q8], sc[q8 >> 1][(q8 & 1) * 16 + i], sc[q8 >> 1][(q8 & 1) * 16 + i + 1]);
                 const float m_new = fmaxf(fmax3(fmaxf(mxa[0], mxa[1]), mxa[2], mxa[3]),
                                           fmax3(fmaxf(mxa[4], mxa[5]), mxa[6], mxa[7])) * p.scale_log2;
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 41, t);
                 if (t == 0) {
                     m_run = m_new;                              // key 0 is visible to every row: finite
                 } else {
@@ -635,6 +686,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         }
                     }
                 }
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 23, t);
                 // ---- probabilities in place (masked scores are -inf -> 0), packed in pairs over the score
                 //      columns already read ----
                 const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
@@ -656,17 +708,28 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         packed[i >> 1] = Elem<T>::pack2(pr.x, pr.y);
                     }
                     tmem_st16(t_sx + cc * 16, packed);
+                    if (cc == 1) {               // first 64 keys done: their PV MMAs may start
+                        tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&ctrl->p_half[x]));
+                        if (kStagger && row == 0) *reinterpret_cast<volatile int *>(&ctrl->sm_progress[x]) = ct + 1;
+                    }
+                    if (lane == 0) NPD_TRACE_FINE(sm_role, 50 + cc, t);
                 }
                 l_run += (acc2[0].x + acc2[1].x) + (acc2[0].y + acc2[1].y);
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 24, t);
                 tmem_wait_st();
                 tc_fence_before();           // P is in TMEM, S has been read: the MMA warp may go on
                 mbar_arrive(smem_u32(&ctrl->p_full[x]));
+                if (lane == 0) NPD_TRACE(sm_role, 25, t);
             }
 
             // ---- epilogue: O / l -> out ----
             if (ok && my_tiles > 0) {
                 // o_full completes once per work item, after its last PV MMA
+                if (lane == 0) NPD_TRACE(sm_role, 30, k);
                 ok = wait_or_abort(smem_u32(&ctrl->o_full[x]), items_seen & 1, abort_flag, p.status);
+                if (lane == 0) NPD_TRACE(sm_role, 31, k);
                 ++items_seen;
                 if (ok) {
                     tc_fence_after();
@@ -698,6 +761,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     }
                 }
             }
+            if (lane == 0) NPD_TRACE(sm_role, 32, k);
             g += it.n_kv;
             cnt += my_tiles;
         }
@@ -798,7 +862,7 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.bt_row_stride = bt_row_stride;
         p.debug_flags = flags;
 #ifdef NPD_PREFILL_TRACE
-        p.trace = workspace_bytes >= 256 + 4 * 4096 * sizeof(long long)
+        p.trace = workspace_bytes >= 256 + 11 * 4096 * sizeof(long long)
                       ? reinterpret_cast<long long *>(static_cast<uint8_t *>(workspace) + 256) : nullptr;
 #endif
         // Pairs of query tiles of the launch, heaviest (most key tiles) first; the kernel hands them out in
