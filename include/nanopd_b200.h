@@ -170,6 +170,31 @@ int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k, void *dst_
                    int64_t dst_layer_stride, int64_t dst_block_stride, int64_t dst_num_blocks,
                    int max_ctas, int32_t *status, void *stream);
 
+/* ---- (5) fused QK-norm + rotary embedding + KV store ------------------------------
+ * Replaces the chain of element-wise passes the caller runs between the projections and
+ * the store (nanoPD/engine/model_runner.py:97-115: q_norm, k_norm, transposes, rotary
+ * embedding of Q and K) together with paged_kv_store (model_runner.py:142-149, 188-194).
+ * For token t: q_out[t, h, :] = rope(norm(q[t, h, :])), the K page slot of the token gets
+ * rope(norm(k[t, h, :])) and the V page slot v[t, h, :]; slots as in npd_kv_store.
+ *   norm(x) = w * T(float(x) * rsqrt(mean(float(x)^2) + eps))      (skipped when w is NULL)
+ *   rope(y) = T(y * cos[t]) + T(rotate_half(y) * sin[t]),  rotate_half(y) = (-y[D/2:], y[:D/2])
+ * with T(.) the rounding to the 16-bit dtype the Hugging Face modules apply at each step
+ * (Qwen3RMSNorm and apply_rotary_pos_emb of transformers, which the reference calls).
+ * q, k, v are token-major: element (t, h, d) at t*token_stride + h*head_dim + d, so views
+ * into one fused projection output are accepted; q_out may alias q.  cos/sin: [T, head_dim]
+ * rows `cos_sin_row_stride` elements apart (0 broadcasts one row).  head_dim in {64,128,256},
+ * dtype f16/bf16; strides multiples of 8 elements, pointers 16-byte aligned.              */
+int npd_qk_norm_rope_store(void *q_out, const void *q, const void *k, const void *v,
+                           const void *q_norm_weight, const void *k_norm_weight,
+                           const void *cos, const void *sin, float eps,
+                           void *k_cache, void *v_cache, const int32_t *block_tables,
+                           const int32_t *positions, int64_t num_tokens, int64_t num_q_heads,
+                           int64_t num_kv_heads, int64_t head_dim, int64_t block_size,
+                           int64_t num_blocks, int64_t max_blocks_per_seq, int64_t cache_block_stride,
+                           int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
+                           int64_t q_out_token_stride, int64_t cos_sin_row_stride,
+                           int64_t bt_row_stride, int dtype, int32_t *status, void *stream);
+
 /* Enables peer access from the current device to `peer_device` (idempotent).
  * Stands in for the driver-side mapping torch's copy_ sets up in the reference
  * (nanoPD/workers/kv_transfer.py:6-14 only probes can_device_access_peer).              */

@@ -37,6 +37,8 @@ SIGNATURES = {
     "npd_kv_migrate": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_int, c_void_p, c_void_p]),
+    "npd_qk_norm_rope_store": (c_int, [c_void_p] * 8 + [c_float] + [c_void_p] * 4 + [c_int64] * 14 +
+                               [c_int, c_void_p, c_void_p]),
     "npd_enable_peer_access": (c_int, [c_int]),
 }
 

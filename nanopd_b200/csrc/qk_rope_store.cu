@@ -1,0 +1,237 @@
+// Fused per-head RMSNorm (optional) + rotary embedding of Q and K, with K and V written straight
+// into their paged block slots.
+//
+// The caller of the paged kernels produces the store's input with a chain of element-wise passes
+// just before it (nanoPD/engine/model_runner.py:97-115: q_norm, k_norm, three transposes, rotary
+// embedding on Q and K, then paged_kv_store at :142-149 / :188-194).  Here one launch reads the
+// projection output once and writes the rotated Q (token-major, the layout the attention kernels
+// take) and the K/V page slots: bytes moved = T*(Hq+2*Hkv)*D*e read + the same written, instead of
+// a round trip through HBM per pass.
+//
+// Arithmetic follows the Hugging Face modules the reference calls, rounding where they round:
+//   RMSNorm (Qwen3RMSNorm): x32 = float(x); y = T(x32 * rsqrt(mean(x32^2) + eps)); y = T(w * y)
+//   rotary (apply_rotary_pos_emb): out = T(T(y * cos) + T(rotate_half(y) * sin)),
+//   rotate_half(y) = concat(-y[D/2:], y[:D/2]),   T(.) = round to the tensor's 16-bit type.
+// One warp per (token, head) row; a lane owns EPL consecutive elements of each half of the row, so
+// the two elements a rotation pairs sit in the same lane and the mean of squares is one warp
+// reduction.  HBM-bound, launch-latency bound at decode sizes.
+#include "npd_common.cuh"
+
+namespace {
+
+struct RopeStoreParams {
+    void *q_out;
+    const void *q, *k, *v;
+    const void *q_w, *k_w;          // per-head-dim norm weights or nullptr
+    const void *cos, *sin;          // [T, D]
+    void *k_cache, *v_cache;
+    const int32_t *block_tables;
+    const int32_t *positions;
+    int32_t *status;
+    float eps;
+    long long num_tokens;
+    int num_q_heads, num_kv_heads;
+    int block_size, num_blocks, max_blocks_per_seq;
+    long long cache_block_stride;   // elements
+    long long q_token_stride, k_token_stride, v_token_stride, q_out_token_stride, cs_row_stride;   // elements
+    long long bt_row_stride;
+};
+
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+// round to T and back: where the 16-bit reference arithmetic rounds
+template <typename T> __device__ __forceinline__ float rt(float x) { return to_f<T>(from_f<T>(x)); }
+
+template <typename T, int EPL> struct Vec { T v[EPL]; };
+
+template <typename T, int EPL>
+__device__ __forceinline__ void load_vec(const T *p, float (&out)[EPL]) {
+    using V = Vec<T, EPL>;
+    const V raw = *reinterpret_cast<const V *>(p);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) out[i] = to_f<T>(raw.v[i]);
+}
+template <typename T, int EPL>
+__device__ __forceinline__ void store_vec(T *p, const float (&in)[EPL]) {
+    using V = Vec<T, EPL>;
+    V raw;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) raw.v[i] = from_f<T>(in[i]);
+    *reinterpret_cast<V *>(p) = raw;
+}
+
+// EPL elements per lane per half row: head_dim = 64 * EPL.
+template <typename T, int EPL>
+__global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStoreParams p) {
+    constexpr int D = 64 * EPL;
+    const int lane = threadIdx.x & 31;
+    const int rows_per_token = p.num_q_heads + 2 * p.num_kv_heads;
+    const long long total = p.num_tokens * rows_per_token;
+    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long w = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); w < total; w += warps) {
+        const long long t = w / rows_per_token;
+        const int r = static_cast<int>(w - t * rows_per_token);
+        const int kind = r < p.num_q_heads ? 0 : (r < p.num_q_heads + p.num_kv_heads ? 1 : 2);   // q, k, v
+        const int h = kind == 0 ? r : (kind == 1 ? r - p.num_q_heads : r - p.num_q_heads - p.num_kv_heads);
+
+        // destination of a k or v row: its page slot
+        T *dst;
+        if (kind == 0) {
+            dst = static_cast<T *>(p.q_out) + t * p.q_out_token_stride + (long long)h * D;
+        } else {
+            const int pos = __ldg(p.positions + t);
+            const int blk_idx = pos / p.block_size;
+            const int off = pos - blk_idx * p.block_size;
+            if (pos < 0 || blk_idx >= p.max_blocks_per_seq) {
+                if (p.status && lane == 0) atomicOr(p.status, NPD_STATUS_BAD_POSITION);
+                continue;
+            }
+            const int phys = __ldg(p.block_tables + t * p.bt_row_stride + blk_idx);
+            if (phys < 0 || phys >= p.num_blocks) {
+                if (p.status && lane == 0) atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
+                continue;
+            }
+            dst = static_cast<T *>(kind == 1 ? p.k_cache : p.v_cache) + phys * p.cache_block_stride +
+                  ((long long)h * p.block_size + off) * D;
+        }
+        const T *src = kind == 0 ? static_cast<const T *>(p.q) + t * p.q_token_stride
+                     : kind == 1 ? static_cast<const T *>(p.k) + t * p.k_token_stride
+                                 : static_cast<const T *>(p.v) + t * p.v_token_stride;
+        src += (long long)h * D;
+
+        float lo[EPL], hi[EPL];
+        load_vec<T, EPL>(src + lane * EPL, lo);
+        load_vec<T, EPL>(src + D / 2 + lane * EPL, hi);
+        if (kind != 2) {
+            const T *wgt = static_cast<const T *>(kind == 0 ? p.q_w : p.k_w);
+            if (wgt != nullptr) {
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
+#pragma unroll
+                for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+                const float inv = rsqrtf(ss * (1.f / D) + p.eps);
+                float wl[EPL], wh[EPL];
+                load_vec<T, EPL>(wgt + lane * EPL, wl);
+                load_vec<T, EPL>(wgt + D / 2 + lane * EPL, wh);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    lo[i] = rt<T>(wl[i] * rt<T>(lo[i] * inv));
+                    hi[i] = rt<T>(wh[i] * rt<T>(hi[i] * inv));
+                }
+            }
+            const T *cs = static_cast<const T *>(p.cos) + t * p.cs_row_stride;
+            const T *sn = static_cast<const T *>(p.sin) + t * p.cs_row_stride;
+            float cl[EPL], ch[EPL], sl[EPL], sh[EPL];
+            load_vec<T, EPL>(cs + lane * EPL, cl);
+            load_vec<T, EPL>(cs + D / 2 + lane * EPL, ch);
+            load_vec<T, EPL>(sn + lane * EPL, sl);
+            load_vec<T, EPL>(sn + D / 2 + lane * EPL, sh);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                const float a = lo[i], b = hi[i];
+                lo[i] = rt<T>(a * cl[i]) + rt<T>(-b * sl[i]);      // rotate_half: the first half pairs with -second
+                hi[i] = rt<T>(b * ch[i]) + rt<T>(a * sh[i]);
+            }
+        }
+        store_vec<T, EPL>(dst + lane * EPL, lo);
+        store_vec<T, EPL>(dst + D / 2 + lane * EPL, hi);
+    }
+}
+
+template <typename T>
+int launch(const RopeStoreParams &p, int head_dim, int device, cudaStream_t stream) {
+    const long long total = p.num_tokens * (p.num_q_heads + 2 * p.num_kv_heads);
+    const int threads = 256;
+    long long blocks = (total + 7) / 8;
+    const long long cap = (long long)npd::sm_count(device) * 8;
+    if (blocks > cap) blocks = cap;
+    switch (head_dim) {
+        case 64: qk_norm_rope_store_kernel<T, 1><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
+        case 128: qk_norm_rope_store_kernel<T, 2><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
+        case 256: qk_norm_rope_store_kernel<T, 4><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
+        default: return npd::fail(NPD_ERR_UNSUPPORTED, "npd_qk_norm_rope_store: head_dim %d not in {64,128,256}", head_dim);
+    }
+    NPD_CUDA_TRY(cudaGetLastError());
+    return NPD_OK;
+}
+
+}  // namespace
+
+extern "C" int npd_qk_norm_rope_store(void *q_out, const void *q, const void *k, const void *v,
+                                      const void *q_norm_weight, const void *k_norm_weight,
+                                      const void *cos, const void *sin, float eps,
+                                      void *k_cache, void *v_cache, const int32_t *block_tables,
+                                      const int32_t *positions, int64_t num_tokens, int64_t num_q_heads,
+                                      int64_t num_kv_heads, int64_t head_dim, int64_t block_size,
+                                      int64_t num_blocks, int64_t max_blocks_per_seq, int64_t cache_block_stride,
+                                      int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
+                                      int64_t q_out_token_stride, int64_t cos_sin_row_stride,
+                                      int64_t bt_row_stride, int dtype, int32_t *status, void *stream) {
+    NPD_REQUIRE(dtype == NPD_DTYPE_F16 || dtype == NPD_DTYPE_BF16, NPD_ERR_UNSUPPORTED,
+                "npd_qk_norm_rope_store: unsupported dtype code %d", dtype);
+    NPD_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, NPD_ERR_UNSUPPORTED,
+                "npd_qk_norm_rope_store: head_dim %lld not in {64,128,256}", (long long)head_dim);
+    NPD_REQUIRE(num_tokens >= 0 && num_q_heads > 0 && num_kv_heads > 0 && block_size > 0 && num_blocks > 0 &&
+                    max_blocks_per_seq > 0,
+                NPD_ERR_INVALID_ARG, "npd_qk_norm_rope_store: non-positive dimension");
+    if (num_tokens == 0) return NPD_OK;
+    NPD_REQUIRE(q_out && q && k && v && cos && sin && k_cache && v_cache && block_tables && positions,
+                NPD_ERR_INVALID_ARG, "npd_qk_norm_rope_store: NULL pointer");
+    NPD_REQUIRE(npd::aligned16(q_out) && npd::aligned16(q) && npd::aligned16(k) && npd::aligned16(v) &&
+                    npd::aligned16(cos) && npd::aligned16(sin) && npd::aligned16(k_cache) && npd::aligned16(v_cache) &&
+                    (q_norm_weight == nullptr || npd::aligned16(q_norm_weight)) &&
+                    (k_norm_weight == nullptr || npd::aligned16(k_norm_weight)),
+                NPD_ERR_INVALID_ARG, "npd_qk_norm_rope_store: pointers must be 16-byte aligned");
+    NPD_REQUIRE(q_token_stride % 8 == 0 && k_token_stride % 8 == 0 && v_token_stride % 8 == 0 &&
+                    q_out_token_stride % 8 == 0 && cos_sin_row_stride % 8 == 0 && cache_block_stride % 8 == 0,
+                NPD_ERR_INVALID_ARG, "npd_qk_norm_rope_store: strides must be multiples of 16 bytes");
+    NPD_REQUIRE(q_token_stride >= num_q_heads * head_dim && q_out_token_stride >= num_q_heads * head_dim &&
+                    k_token_stride >= num_kv_heads * head_dim && v_token_stride >= num_kv_heads * head_dim &&
+                    cos_sin_row_stride >= 0,
+                NPD_ERR_INVALID_ARG, "npd_qk_norm_rope_store: token stride smaller than one token's heads");
+    NPD_REQUIRE(cache_block_stride >= num_kv_heads * block_size * head_dim, NPD_ERR_INVALID_ARG,
+                "npd_qk_norm_rope_store: cache block stride smaller than one block");
+    NPD_REQUIRE(num_blocks <= INT32_MAX && max_blocks_per_seq <= INT32_MAX && block_size <= INT32_MAX &&
+                    num_q_heads <= INT32_MAX / 4 && num_kv_heads <= INT32_MAX / 4,
+                NPD_ERR_INVALID_ARG, "npd_qk_norm_rope_store: dimension exceeds int32");
+
+    RopeStoreParams p;
+    p.q_out = q_out;
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.q_w = q_norm_weight;
+    p.k_w = k_norm_weight;
+    p.cos = cos;
+    p.sin = sin;
+    p.k_cache = k_cache;
+    p.v_cache = v_cache;
+    p.block_tables = block_tables;
+    p.positions = positions;
+    p.status = status;
+    p.eps = eps;
+    p.num_tokens = num_tokens;
+    p.num_q_heads = static_cast<int>(num_q_heads);
+    p.num_kv_heads = static_cast<int>(num_kv_heads);
+    p.block_size = static_cast<int>(block_size);
+    p.num_blocks = static_cast<int>(num_blocks);
+    p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
+    p.cache_block_stride = cache_block_stride;
+    p.q_token_stride = q_token_stride;
+    p.k_token_stride = k_token_stride;
+    p.v_token_stride = v_token_stride;
+    p.q_out_token_stride = q_out_token_stride;
+    p.cs_row_stride = cos_sin_row_stride;
+    p.bt_row_stride = bt_row_stride;
+
+    int dev = 0;
+    NPD_CUDA_TRY(cudaGetDevice(&dev));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == NPD_DTYPE_BF16 ? launch<__nv_bfloat16>(p, static_cast<int>(head_dim), dev, st)
+                                   : launch<__half>(p, static_cast<int>(head_dim), dev, st);
+}

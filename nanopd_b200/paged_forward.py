@@ -147,3 +147,44 @@ def paged_attention_step(sc: StepContext, q: torch.Tensor, k: torch.Tensor, v: t
         paged_kernels.paged_attention_forward(out[P:], q_d, k_cache, v_cache, sc.decode_tables, sc.decode_seq_lens,
                                               scale, bs, sc.decode_tables.size(1))
     return out.view(1, total, hq * d)
+
+
+def paged_attention_step_fused(sc: StepContext, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                               cos: torch.Tensor, sin: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                               scale: float, q_norm_weight=None, k_norm_weight=None, eps: float = 1e-6) -> torch.Tensor:
+    """The same step starting one stage earlier: from the projection outputs.
+
+    ``q`` ``[total, Hq, D]``, ``k``/``v`` ``[total, Hkv, D]`` are the token-major views of ``q_proj``/``k_proj``/
+    ``v_proj`` (nanoPD/engine/model_runner.py:84-99) — or of one fused projection — BEFORE the per-head norm and
+    the rotary embedding; ``cos``/``sin`` ``[total, D]`` are the rotary tables of the step's positions.  Norm,
+    rotary embedding and the store run as one launch per prompt chunk plus one for all decode tokens
+    (``paged_qk_norm_rope_store``), the rotated queries stay token-major, and the attention kernels read them
+    in place: no transposes, no ``contiguous()`` copies.  Returns ``[1, total, Hq*D]``.
+    """
+    P, Dn = sc.num_prefill_tokens, sc.num_decode_tokens
+    total = P + Dn
+    tq, hq, d = q.shape
+    if tq != total or k.size(0) != total or v.size(0) != total:
+        raise RuntimeError("q/k/v token count does not match the step context")
+    if cos.dim() == 3:
+        cos, sin = cos[0], sin[0]
+    bs = k_cache.size(2)
+    out = torch.empty(total, hq, d, dtype=q.dtype, device=q.device)
+    q_rot = torch.empty(total, hq, d, dtype=q.dtype, device=q.device)
+    for i, (off, n) in enumerate(zip(sc.prefill_offsets, sc.prefill_tokens)):
+        paged_kernels.paged_qk_norm_rope_store(
+            q[off:off + n], k[off:off + n], v[off:off + n], cos[off:off + n], sin[off:off + n], k_cache, v_cache,
+            sc.prefill_tables[i:i + 1].expand(n, -1), sc.prefill_positions[off:off + n],
+            q_norm_weight, k_norm_weight, eps, q_out=q_rot[off:off + n])
+    if Dn > 0:
+        paged_kernels.paged_qk_norm_rope_store(
+            q[P:], k[P:], v[P:], cos[P:], sin[P:], k_cache, v_cache, sc.decode_tables, sc.decode_positions,
+            q_norm_weight, k_norm_weight, eps, q_out=q_rot[P:])
+    if P > 0:
+        paged_kernels.paged_prefill_attention(out[:P], q_rot[:P], k_cache, v_cache, sc.prefill_tables,
+                                              sc.prefill_offsets, sc.prefill_tokens, sc.prefill_starts,
+                                              scale, bs, sc.prefill_tables.size(1))
+    if Dn > 0:
+        paged_kernels.paged_attention_forward(out[P:], q_rot[P:], k_cache, v_cache, sc.decode_tables,
+                                              sc.decode_seq_lens, scale, bs, sc.decode_tables.size(1))
+    return out.view(1, total, hq * d)

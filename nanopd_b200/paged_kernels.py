@@ -149,6 +149,77 @@ def paged_kv_store(k_cache, v_cache, k_src, v_src, block_tables, positions) -> N
 
 
 # ---------------------------------------------------------------------------
+# (1b) fused QK-norm + rotary embedding + KV store
+# ---------------------------------------------------------------------------
+def paged_qk_norm_rope_store(q, k, v, cos, sin, k_cache, v_cache, block_tables, positions,
+                             q_norm_weight=None, k_norm_weight=None, eps: float = 1e-6, q_out=None):
+    """Per-head RMSNorm (when weights are given) and rotary embedding of Q and K, K and V written into
+    their block slots, in one launch.
+
+    Stands for the passes the reference runs between the projections and the store
+    (nanoPD/engine/model_runner.py:97-115, then paged_kv_store at :142-149 / :188-194), with the
+    rounding steps of the Hugging Face modules it calls.  ``q`` ``[T, Hq, D]``, ``k``/``v``
+    ``[T, Hkv, D]`` token-major (views into a fused projection output are fine: only the last two
+    dims must be contiguous); ``cos``/``sin`` ``[T, D]`` (or ``[1, T, D]``) in the tensors' dtype;
+    ``block_tables`` int32 one row per token, ``positions`` int32 ``[T]`` as for ``paged_kv_store``.
+    Returns the rotated queries ``[T, Hq, D]`` (``q_out``, default: in place over ``q``) — the layout
+    ``paged_attention_forward`` and ``paged_prefill_attention`` take.
+    """
+    _require(q.is_cuda and k.is_cuda and v.is_cuda, "q, k and v must be on CUDA")
+    _require(q.dim() == 3 and k.dim() == 3 and v.dim() == 3, "q must be [T, Hq, D] and k, v [T, Hkv, D]")
+    T, hq, d = q.shape
+    _require(k.shape == v.shape and k.size(0) == T and k.size(2) == d, "k and v must be [T, Hkv, D] with q's T and D")
+    hkv = k.size(1)
+    dev = q.device
+    if cos.dim() == 3 and cos.size(0) == 1:
+        cos, sin = cos[0], sin[0]
+    _require(cos.shape == sin.shape and cos.dim() == 2 and cos.size(1) == d and cos.size(0) in (1, T),
+             "cos and sin must be [T, D]")
+    if q_out is None:
+        q_out = q
+    _require(q_out.shape == q.shape, "q_out must have q's shape")
+    for name, t_ in (("q", q), ("k", k), ("v", v), ("q_out", q_out)):
+        _require(t_.stride(2) == 1 and t_.stride(1) == d, f"{name}: the last two dims must be contiguous")
+    _require(cos.stride(1) == 1 and sin.stride(1) == 1 and cos.stride(0) == sin.stride(0), "cos/sin rows must be contiguous")
+    _require(q.dtype in (torch.float16, torch.bfloat16), f"unsupported dtype {q.dtype}")
+    _require(all(t_.dtype == q.dtype for t_ in (k, v, cos, sin, q_out, k_cache, v_cache)), "dtypes differ")
+    _require(all(t_.device == dev for t_ in (k, v, cos, sin, q_out, k_cache, v_cache, block_tables, positions)),
+             "all tensors must be on the same CUDA device")
+    for w_ in (q_norm_weight, k_norm_weight):
+        _require(w_ is None or (w_.dtype == q.dtype and w_.device == dev and w_.numel() == d and w_.is_contiguous()),
+                 "norm weights must be contiguous [D] tensors of q's dtype")
+    if block_tables.dim() == 1:
+        block_tables = block_tables.unsqueeze(0).expand(T, -1)
+    _require(block_tables.dtype == torch.int32 and positions.dtype == torch.int32,
+             "block_tables and positions must be int32")
+    _require(block_tables.dim() == 2 and block_tables.size(0) == T and positions.dim() == 1 and positions.numel() == T,
+             "block_tables must be [num_tokens, max_blocks] and positions [num_tokens]")
+    nb, chkv, bs, cd, cstride = _cache_geometry(k_cache, "k_cache")
+    _require(_cache_geometry(v_cache, "v_cache") == (nb, chkv, bs, cd, cstride), "k_cache and v_cache layouts differ")
+    _require(chkv == hkv and cd == d, "k/v heads / head_dim do not match the cache")
+    if block_tables.stride(1) != 1 and block_tables.size(1) > 1:
+        block_tables = block_tables.contiguous()
+    if positions.stride(0) != 1:
+        positions = positions.contiguous()
+    if T == 0:
+        return q_out
+    handle = _stream_handle(dev)
+    ws = _workspace(dev, handle, 256)
+    with torch.cuda.device(dev):
+        _lib.check(_C.npd_qk_norm_rope_store(
+            q_out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            None if q_norm_weight is None else q_norm_weight.data_ptr(),
+            None if k_norm_weight is None else k_norm_weight.data_ptr(),
+            cos.data_ptr(), sin.data_ptr(), float(eps),
+            k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(), positions.data_ptr(),
+            T, hq, hkv, d, bs, nb, block_tables.size(1), cstride,
+            q.stride(0), k.stride(0), v.stride(0), q_out.stride(0),
+            0 if cos.size(0) == 1 else cos.stride(0), block_tables.stride(0),
+            _DTYPE_CODE[q.dtype], ws.data_ptr(), handle))
+    return q_out
+
+
+# ---------------------------------------------------------------------------
 # (2) decode attention
 # ---------------------------------------------------------------------------
 def paged_attention_forward(out, query, key_cache, value_cache, block_tables, seq_lens,

@@ -16,6 +16,13 @@ function has no reference implementation that reads earlier chunks from the page
 ``start_position == 0`` it is pinned against that SDPA call, for later chunks parity
 is unpinned and this oracle defines the value.
 
+``qk_norm_rope_store`` restates arithmetic that lives in a third-party dependency of the
+reference, Hugging Face transformers (``Qwen3RMSNorm.forward``, ``apply_rotary_pos_emb`` and
+``rotate_half`` of ``transformers/models/qwen3/modeling_qwen3.py``; the reference pins no version,
+README "transformers", the fixtures were made with 5.5.0), at the reference's call sites
+nanoPD/engine/model_runner.py:97-115.  It is pinned bit for bit against those functions by
+``tests/golden/make_golden_rope.py`` and the fixture ``tests/golden/qk_norm_rope_cases.npz``.
+
 Every function cites the reference file:line it follows.
 """
 from __future__ import annotations
@@ -53,6 +60,45 @@ def kv_store(k_cache, v_cache, k_src, v_src, block_tables, positions):
     for t in range(T):
         k_cache[phys[t], :, off[t], :] = k_src[:, t, :]
         v_cache[phys[t], :, off[t], :] = v_src[:, t, :]
+
+
+# ---------------------------------------------------------------------------
+# QK-norm + rotary embedding + store (the passes in front of the store)
+# ---------------------------------------------------------------------------
+def rms_norm_heads(x, weight, eps):
+    """Per-head RMSNorm as the reference's q_norm / k_norm apply it (model_runner.py:101-104 calling
+    transformers' Qwen3RMSNorm): fp32 statistics, result rounded to the input dtype, then multiplied
+    by the weight in that dtype."""
+    x32 = x.to(torch.float32)
+    var = x32.pow(2).mean(-1, keepdim=True)
+    return weight * (x32 * torch.rsqrt(var + eps)).to(x.dtype)
+
+
+def rotate_half(x):
+    half = x.shape[-1] // 2
+    return torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+
+
+def rotary(x, cos, sin):
+    """x: [T, H, D]; cos, sin: [T, D] in x's dtype.  ``(x * cos) + (rotate_half(x) * sin)`` evaluated in
+    the tensor dtype, each product and the sum rounded (model_runner.py:110-115 calling transformers'
+    apply_rotary_pos_emb)."""
+    c, s_ = cos.unsqueeze(1), sin.unsqueeze(1)
+    return (x * c) + (rotate_half(x) * s_)
+
+
+def qk_norm_rope_store(q, k, v, cos, sin, k_cache, v_cache, block_tables, positions,
+                       q_norm_weight=None, k_norm_weight=None, eps=1e-6):
+    """q [T,Hq,D], k/v [T,Hkv,D] token-major.  Returns the rotated queries [T,Hq,D]; K (normed and
+    rotated) and V go to their block slots with ``kv_store`` (model_runner.py:97-115 then :142-149)."""
+    if q_norm_weight is not None:
+        q = rms_norm_heads(q, q_norm_weight, eps)
+    if k_norm_weight is not None:
+        k = rms_norm_heads(k, k_norm_weight, eps)
+    q_rot = rotary(q, cos, sin)
+    k_rot = rotary(k, cos, sin)
+    kv_store(k_cache, v_cache, k_rot.transpose(0, 1), v.transpose(0, 1), block_tables, positions)
+    return q_rot
 
 
 # ---------------------------------------------------------------------------

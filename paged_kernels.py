@@ -8,4 +8,5 @@ from nanopd_b200.paged_kernels import (  # noqa: F401
     paged_kv_migrate,
     paged_kv_store,
     paged_prefill_attention,
+    paged_qk_norm_rope_store,
 )

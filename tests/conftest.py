@@ -56,6 +56,23 @@ def load_decode_cases():
     return cases
 
 
+def load_rope_cases():
+    """The transformers-generated norm + rotary cases of tests/golden/qk_norm_rope_cases.npz."""
+    z = np.load(GOLDEN / "qk_norm_rope_cases.npz")
+    cases = []
+    for name in z["names"].tolist():
+        bf16 = bool(z[f"{name}/is_bf16"])
+        with_norm = bool(z[f"{name}/with_norm"])
+        c = dict(name=name, dtype=torch.bfloat16 if bf16 else torch.float16, with_norm=with_norm,
+                 positions=torch.from_numpy(z[f"{name}/positions"]))
+        for key in ("q", "k", "cos", "sin", "q_ref", "k_ref"):
+            c[key] = _from_bits(z[f"{name}/{key}"], bf16)
+        for key in ("q_norm_weight", "k_norm_weight"):
+            c[key] = _from_bits(z[f"{name}/{key}"], bf16) if with_norm else None
+        cases.append(c)
+    return cases
+
+
 @pytest.fixture(scope="session")
 def decode_cases():
     return load_decode_cases()

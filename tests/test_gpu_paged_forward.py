@@ -90,3 +90,46 @@ def test_decode_only_and_prefill_only_steps(kernels):
     assert (out_d.view(1, Hq, D).float().cpu() - want_d).abs().max().item() <= TOL[torch.float16]
     want_p = paged_oracle.paged_prefill_attention(q[0].transpose(0, 1).cpu(), k_cache.cpu(), v_cache.cpu(), bt[0], 0, scale)
     assert (out_p.view(20, Hq, D).float().cpu() - want_p).abs().max().item() <= TOL[torch.float16]
+
+
+def test_fused_step_equals_unfused_step_on_rotated_inputs(kernels):
+    """paged_attention_step_fused (norm + rotary + store in one launch) against paged_attention_step fed with
+    the oracle's normed and rotated tensors: same pages (up to one rounding step of the norm) and same output."""
+    torch.manual_seed(9)
+    dtype = torch.bfloat16
+    Hq, Hkv, D, B, pool = 8, 2, 128, 16, 48
+    perm = torch.randperm(pool).tolist()
+    prefills = [{"block_table": perm[0:4], "start_position": 16, "num_tokens": 37}]
+    decodes = [{"block_table": perm[4:8], "position": 49}, {"block_table": perm[8:9], "position": 3}]
+    P, Dn = 37, 2
+    total = P + Dn
+    ctx = {"num_prefill_tokens": P, "num_decode_tokens": Dn, "prefills": prefills, "decodes": decodes}
+    k_cache = torch.randn(pool, Hkv, B, D).to(dtype)
+    v_cache = torch.randn(pool, Hkv, B, D).to(dtype)
+    q = torch.randn(total, Hq, D).to(dtype)
+    k = torch.randn(total, Hkv, D).to(dtype)
+    v = torch.randn(total, Hkv, D).to(dtype)
+    pos = torch.tensor(list(range(16, 16 + 37)) + [49, 3], dtype=torch.float32)
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = pos[:, None] * inv_freq[None, :]
+    cos = torch.cat((ang.cos(), ang.cos()), -1).to(dtype)
+    sin = torch.cat((ang.sin(), ang.sin()), -1).to(dtype)
+    qw = (1 + 0.1 * torch.randn(D)).to(dtype)
+    kw = (1 + 0.1 * torch.randn(D)).to(dtype)
+    scale = D ** -0.5
+
+    q_rot = paged_oracle.rotary(paged_oracle.rms_norm_heads(q, qw, 1e-6), cos, sin)
+    k_rot = paged_oracle.rotary(paged_oracle.rms_norm_heads(k, kw, 1e-6), cos, sin)
+    sc = paged_forward.build_step_context(ctx, DEV)
+    kc1, vc1 = k_cache.to(DEV), v_cache.to(DEV)
+    want = paged_forward.paged_attention_step(sc, q_rot.transpose(0, 1).unsqueeze(0).to(DEV),
+                                              k_rot.transpose(0, 1).unsqueeze(0).to(DEV),
+                                              v.transpose(0, 1).unsqueeze(0).to(DEV), kc1, vc1, scale)
+    kc2, vc2 = k_cache.to(DEV), v_cache.to(DEV)
+    got = paged_forward.paged_attention_step_fused(sc, q.to(DEV), k.to(DEV), v.to(DEV), cos.to(DEV), sin.to(DEV),
+                                                   kc2, vc2, scale, qw.to(DEV), kw.to(DEV), 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(vc1, vc2)
+    assert (kc1.float() - kc2.float()).abs().max().item() <= 2 ** -5          # one bf16 step at |x| < 8
+    assert float((kc1 != kc2).float().mean()) < 0.01
+    assert (got.float() - want.float()).abs().max().item() <= TOL[dtype]

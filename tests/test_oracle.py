@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN, load_decode_cases
+from conftest import GOLDEN, load_decode_cases, load_rope_cases
 from nanopd_b200 import workloads
 from oracle import paged_oracle
 
@@ -146,3 +146,34 @@ def test_algorithmic_bytes_formula():
     b = paged_oracle.decode_algorithmic_bytes([100, 33], 32, 8, 128, 16)
     assert b == 133 * 4096 + 2 * 2 * 32 * 128 * 2 + (7 + 3) * 4 + 2 * 4
     assert paged_oracle.prefill_algorithmic_flops(512, 0, 32, 128) == 4 * 32 * 128 * (512 * 513 // 2)
+
+
+@pytest.mark.parametrize("case", load_rope_cases(), ids=lambda c: c["name"])
+def test_norm_and_rotary_oracle_reproduce_transformers_bit_for_bit(case):
+    q, k = case["q"], case["k"]
+    if case["with_norm"]:
+        q = paged_oracle.rms_norm_heads(q, case["q_norm_weight"], 1e-6)
+        k = paged_oracle.rms_norm_heads(k, case["k_norm_weight"], 1e-6)
+    assert torch.equal(paged_oracle.rotary(q, case["cos"], case["sin"]), case["q_ref"])
+    assert torch.equal(paged_oracle.rotary(k, case["cos"], case["sin"]), case["k_ref"])
+
+
+def test_qk_norm_rope_store_oracle_puts_rows_in_their_slots():
+    case = load_rope_cases()[0]
+    T, Hkv, D = case["k"].shape
+    B, pool = 16, 12
+    torch.manual_seed(0)
+    v = torch.randn(T, Hkv, D).to(case["dtype"])
+    kc = torch.zeros(pool, Hkv, B, D, dtype=case["dtype"])
+    vc = torch.zeros_like(kc)
+    table = torch.randperm(pool)[:4].to(torch.int32)
+    positions = torch.arange(10, 10 + T, dtype=torch.int32)          # crosses from block 0 into block 1
+    q_rot = paged_oracle.qk_norm_rope_store(case["q"], case["k"], v, case["cos"], case["sin"], kc, vc,
+                                            table.unsqueeze(0).expand(T, -1), positions,
+                                            case["q_norm_weight"], case["k_norm_weight"], 1e-6)
+    assert torch.equal(q_rot, case["q_ref"])
+    for t in range(T):
+        pos = 10 + t
+        blk, off = int(table[pos // B]), pos % B
+        assert torch.equal(kc[blk, :, off], case["k_ref"][t]) and torch.equal(vc[blk, :, off], v[t])
+    assert int((kc != 0).any(-1).sum()) == T * Hkv
