@@ -273,6 +273,61 @@ def run_prefill_workload(args, paged_kernels, dev, timed):
             "mixed_step_ms": round(ms_mixed, 4),
             "mixed_step": "last 512-token chunk of each of 4 prompts + store + decode attention of 128 sequences"}
 
+def run_model_workload(args, dev, timed, batch, seed):
+    """Decode tokens/s at model level: a random-init stack of Qwen3-8B shape (36 layers) around the paged kernels,
+    configuration 2's batch (256 sequences, lognormal contexts) in a 36-layer pool, every step one token per
+    sequence; the whole step replayed as one CUDA graph.  Returns per-GPU numbers; the caller aggregates."""
+    import numpy as np
+    from nanopd_b200 import decoder_step
+    free, _ = torch.cuda.mem_get_info(dev)
+    if free < 95 * (1 << 30):
+        return {"skipped": f"only {free >> 30} GiB free on the device"}
+    shape = decoder_step.DecoderShape()
+    B, headroom = 16, 24
+    ctx = workloads.config2_lens(batch=batch, seed=seed)
+    nblk = (np.asarray(ctx, dtype=np.int64) + headroom + B - 1) // B
+    pool_blocks = int(nblk.sum())
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(pool_blocks)
+    tables = np.zeros((len(ctx), int(nblk.max())), dtype=np.int32)
+    o = 0
+    for i, n in enumerate(nblk.tolist()):
+        tables[i, :n] = perm[o:o + n]
+        o += n
+    model = decoder_step.SyntheticDecoder(dev, shape, torch.bfloat16, seed=seed, max_position=8192 + 64)
+    k_cache = torch.empty(shape.num_layers, pool_blocks, shape.num_kv_heads, B, shape.head_dim, dtype=torch.bfloat16, device=dev)
+    v_cache = torch.empty_like(k_cache)
+    for li in range(shape.num_layers):       # layer by layer: bounded temporaries
+        k_cache[li].normal_()
+        v_cache[li].normal_()
+    ctx_t = torch.from_numpy(np.asarray(ctx, dtype=np.int32)).to(dev)
+    tokens = torch.randint(0, shape.vocab, (len(ctx),), device=dev)
+    model.attach_batch(k_cache, v_cache, torch.from_numpy(tables).to(dev), ctx_t, tokens)
+    n_eager, n_graph = 2, 8
+    model.step()                                                  # warm-up (cuBLAS handles, workspaces)
+    ms_eager = timed(model.step, n_eager)
+    model.capture()
+    model.replay()
+    ms_graph = timed(model.replay, n_graph)
+    status = 0
+    import paged_kernels
+    status = paged_kernels.check_status(dev, raise_on_error=False)
+    S = len(ctx)
+    kv_bytes_step = int(sum(int(c) for c in ctx)) * 2 * shape.num_kv_heads * shape.head_dim * 2 * shape.num_layers
+    res = {"model": "Qwen3-8B shape, random init (36 layers, hidden 4096, FFN 12288, 32q/8kv x 128, vocab 151936), bf16",
+           "batch": S, "context_tokens": int(sum(int(c) for c in ctx)),
+           "params": shape.param_count, "kv_pool_gb": round(2 * k_cache.numel() * 2 / 1e9, 1),
+           "graph_ms_per_step": round(ms_graph, 3), "eager_ms_per_step": round(ms_eager, 3),
+           "tok_s": round(S / (ms_graph * 1e-3), 1), "tok_s_eager": round(S / (ms_eager * 1e-3), 1),
+           "kv_bytes_per_step": kv_bytes_step, "weight_bytes_per_step": 2 * (shape.param_count - shape.vocab * shape.hidden),
+           "library_launches_per_step": model.launches_per_step(),
+           "sampling": "greedy argmax on the device", "device_status": status,
+           "steps_timed": n_graph, "tokens_advance_in_place": True}
+    del model, k_cache, v_cache
+    torch.cuda.empty_cache()
+    return res
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -302,6 +357,20 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
         replicas.barrier()
         return e0.elapsed_time(e1) / n
+
+    if args.workload == "model":
+        res = run_model_workload(args, dev, timed, args.batch, args.seed)
+        ms = replicas.max_over_ranks(res.get("graph_ms_per_step", 0.0), dev)
+        toks = replicas.sum_over_ranks(res.get("batch", 0), dev)
+        if rank == 0:
+            sampler.stop()
+            if ms > 0:
+                res["n_gpus"] = world
+                res["tok_s_all_gpus"] = round(toks / (ms * 1e-3), 1)
+            print(json.dumps({"workload": "decode tokens/s at model level (secondary, not the headline metric)", **res}), flush=True)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return 0
 
     if args.workload == "prefill":
         res = run_prefill_workload(args, paged_kernels, dev, timed)
@@ -389,6 +458,20 @@ def run_gpu_arm(args):
 
     extras = {}
     cpu_baseline = None
+    if not args.no_model:
+        # decode tokens/s at model level, on every rank (replicas): aggregate = all sequences / slowest rank
+        try:
+            del stage_dev, dbuf
+            torch.cuda.empty_cache()
+            md = run_model_workload(args, dev, timed, args.batch, args.seed)
+        except Exception as exc:  # noqa: BLE001
+            md = {"error": str(exc)[:300]}
+        ms_model = replicas.max_over_ranks(float(md.get("graph_ms_per_step", 0.0)), dev)
+        toks_model = replicas.sum_over_ranks(int(md.get("batch", 0)) if ms_model > 0 else 0, dev)
+        if ms_model > 0 and "tok_s" in md:
+            md["n_gpus"] = world
+            md["tok_s_all_gpus"] = round(toks_model / (ms_model * 1e-3), 1)
+        extras["model_decode"] = md
     if rank == 0 and world == 1:
         # secondary kernels, timed briefly
         extras["attention_ms"] = round(ms_attn, 4)
@@ -410,7 +493,6 @@ def run_gpu_arm(args):
         except Exception as exc:  # noqa: BLE001
             extras["migrate_error"] = str(exc)[:200]
         try:
-            del stage_dev, dbuf
             torch.cuda.empty_cache()
             extras["prefill_cfg3"] = run_prefill_workload(args, paged_kernels, dev, timed)
         except Exception as exc:  # noqa: BLE001
@@ -466,10 +548,12 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "model"], default="decode",
                     help="decode = the headline configuration 2 (default); prefill = configuration 3's chunked prefill")
     ap.add_argument("--profile", action="store_true",
                     help="only warm up and run the timed step loop (for short ncu captures); prints no bench line")
+    ap.add_argument("--no-model", action="store_true",
+                    help="skip the model-level decode tokens/s measurement (needs ~75 GB of device memory)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
