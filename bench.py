@@ -478,6 +478,18 @@ def run_gpu_arm(args):
         extras["store_ms"] = round(ms_store, 4)
         extras["store_gbs"] = round(store_bytes / (ms_store * 1e-3) / 1e9, 2)
         try:
+            # the same launch on the interleaved cache layouts of the reference's split-K op
+            k_il = b.k_cache.view(b.k_cache.size(0), Hkv, B, D // 8, 8).permute(0, 1, 3, 2, 4).contiguous()
+            v_il = b.v_cache.permute(0, 1, 3, 2).contiguous()
+            fn_il = lambda: paged_kernels.paged_attention_forward(out, b.query, k_il, v_il, b.block_tables, seq_lens,
+                                                                  b.scale, B, max_blk)
+            for _ in range(3):
+                fn_il()
+            extras["attention_interleaved_layout_ms"] = round(timed(fn_il, min(steps, 50)), 4)
+            del k_il, v_il
+        except Exception as exc:  # noqa: BLE001
+            extras["interleaved_error"] = str(exc)[:200]
+        try:
             L, nb = 36, 96
             pool_k = torch.randn(L, nb, Hkv, B, D, device=dev).to(torch.bfloat16)
             pool_v = torch.randn(L, nb, Hkv, B, D, device=dev).to(torch.bfloat16)

@@ -42,6 +42,10 @@ extern "C" {
 
 /* Flags of npd_paged_decode_attention */
 #define NPD_DECODE_SKIP_MERGE     1   /* diagnostic: sequences split across workers stay unmerged (wrong rows for those) */
+#define NPD_DECODE_KV_INTERLEAVED 2   /* caches in the layouts of the reference's split-K op and of its kernel tests
+                                       * (csrc/paged_attention_optimized/index.h:14-31,60-75; tests/test_paged_kernels.py:39-56):
+                                       * K [num_blocks, num_kv_heads, head_dim/8, block_size, 8],
+                                       * V [num_blocks, num_kv_heads, head_dim, block_size]                           */
 
 int         npd_version(void);
 const char *npd_last_error(void);

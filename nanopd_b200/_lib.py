@@ -12,6 +12,7 @@ NPD_ERR_INVALID_ARG, NPD_ERR_UNSUPPORTED, NPD_ERR_CUDA, NPD_ERR_WORKSPACE = 1, 2
 NPD_DTYPE_F16, NPD_DTYPE_BF16, NPD_DTYPE_F32 = 0, 1, 2
 NPD_STATUS_BAD_BLOCK_ID, NPD_STATUS_BAD_POSITION, NPD_STATUS_WAIT_TIMEOUT = 1, 2, 4
 NPD_DECODE_SKIP_MERGE = 1
+NPD_DECODE_KV_INTERLEAVED = 2
 
 # name -> (restype, argtypes); the order mirrors include/nanopd_b200.h
 SIGNATURES = {

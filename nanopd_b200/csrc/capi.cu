@@ -49,7 +49,7 @@ static EncodeTiledFn resolve_encode_tiled() {
 }
 
 int encode_tiled_3d(CUtensorMap *map, const void *base, int dtype, const uint64_t dims[3],
-                    const uint64_t strides_bytes[2], const uint32_t box[3]) {
+                    const uint64_t strides_bytes[2], const uint32_t box[3], bool swizzle128) {
     EncodeTiledFn encode = resolve_encode_tiled();
     NPD_REQUIRE(encode != nullptr, NPD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     NPD_REQUIRE(aligned16(base), NPD_ERR_INVALID_ARG, "tensor base pointer must be 16-byte aligned");
@@ -62,7 +62,8 @@ int encode_tiled_3d(CUtensorMap *map, const void *base, int dtype, const uint64_
     const CUtensorMapDataType dt =
         dtype == NPD_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = encode(map, dt, 3, const_cast<void *>(base), gdims, gstrides, gbox, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     NPD_REQUIRE(r == CUDA_SUCCESS, NPD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return NPD_OK;

@@ -298,7 +298,11 @@ __device__ __forceinline__ void merge_partials(AttnState<T, D, NT> &st, const De
 // ---------------------------------------------------------------------------
 // Streaming kernel
 // ---------------------------------------------------------------------------
-template <typename T, int D, int NT>
+// IL selects the interleaved cache layouts of the reference's split-K op (K [blocks, Hkv, D/8, B, 8], V
+// [blocks, Hkv, D, B]; csrc/paged_attention_optimized/index.h:14-31,60-75): a K tile lands as [d piece][token][8]
+// and feeds ldmatrix directly (8 tokens of one piece are 128 contiguous bytes), a V tile lands as [d][token] and is
+// already the A operand of O^T = V^T . P^T, so it is read without the transposing ldmatrix.
+template <typename T, int D, int NT, bool IL>
 __global__ void __launch_bounds__(256, 1)
 paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v) {
@@ -353,6 +357,12 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
     const int k_row_off = (k_r / p.box_rows) * (NH * p.box_rows * 128) + (k_r % p.box_rows) * 128;
     const int v_row_off = (v_r / p.box_rows) * (NH * p.box_rows * 128) + (v_r % p.box_rows) * 128;
     const int half_bytes = p.box_rows * 128;
+    // interleaved layouts: a box holds box_rows tokens; K box = [D/8 pieces][box_rows][16 B], V box = [D][box_rows x 2 B]
+    const int box_bytes = p.box_rows * D * 2;
+    const int il_k_off = (k_r / p.box_rows) * box_bytes + (k_r % p.box_rows) * 16;       // + piece * box_rows * 16
+    const int il_v_tok = (mi >> 1) * 8;                                                  // token piece of this lane's matrix
+    const int il_v_off = (il_v_tok / p.box_rows) * box_bytes + (il_v_tok % p.box_rows) * 2 +
+                         ((mi & 1) * 8 + mrow) * (p.box_rows * 2);                         // + 16 j rows
 
     Cursor pc, cc;                   // producer / consumer cursors over the same range
     cursor_seek(pc, f_begin, pre, p);
@@ -385,12 +395,18 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
                 id = p.num_blocks;   // out of bounds for the tensor map: the box is zero-filled
             }
             if (lane == 0) {
-                const int row = phys_head * p.block_size + row_in_page;
+                if (IL) {
+                    const uint32_t off = static_cast<uint32_t>(k * box_bytes);
+                    tma_load_3d(kdst + off, &tm_k, bar, row_in_page * 8, phys_head * (D / 8), id);
+                    tma_load_3d(vdst + off, &tm_v, bar, row_in_page, phys_head * D, id);
+                } else {
+                    const int row = phys_head * p.block_size + row_in_page;
 #pragma unroll
-                for (int hf = 0; hf < NH; ++hf) {
-                    const uint32_t off = static_cast<uint32_t>(k * (NH * half_bytes) + hf * half_bytes);
-                    tma_load_3d(kdst + off, &tm_k, bar, hf * 64, row, id);
-                    tma_load_3d(vdst + off, &tm_v, bar, hf * 64, row, id);
+                    for (int hf = 0; hf < NH; ++hf) {
+                        const uint32_t off = static_cast<uint32_t>(k * (NH * half_bytes) + hf * half_bytes);
+                        tma_load_3d(kdst + off, &tm_k, bar, hf * 64, row, id);
+                        tma_load_3d(vdst + off, &tm_v, bar, hf * 64, row, id);
+                    }
                 }
             }
         }
@@ -451,11 +467,20 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
             if (valid < kTile) {
                 // V rows past the sequence end may hold anything (NaN included): P is exactly 0
                 // there, and 0 * NaN would still poison O, so clear them.
-                const int cnt = (kTile - valid) * NH * 8;
-                for (int idx = lane; idx < cnt; idx += 32) {
-                    const int r = valid + idx / (NH * 8);
-                    const int c = idx % (NH * 8);
-                    *reinterpret_cast<uint4 *>(vt + tile_offset<D>(r, c, p.box_rows)) = make_uint4(0, 0, 0, 0);
+                if (IL) {
+                    const int dead_toks = kTile - valid;
+                    for (int idx = lane; idx < dead_toks * D; idx += 32) {
+                        const int d = idx / dead_toks, tk = valid + idx % dead_toks;
+                        *reinterpret_cast<uint16_t *>(vt + (tk / p.box_rows) * box_bytes + d * (p.box_rows * 2) +
+                                                      (tk % p.box_rows) * 2) = 0;
+                    }
+                } else {
+                    const int cnt = (kTile - valid) * NH * 8;
+                    for (int idx = lane; idx < cnt; idx += 32) {
+                        const int r = valid + idx / (NH * 8);
+                        const int c = idx % (NH * 8);
+                        *reinterpret_cast<uint4 *>(vt + tile_offset<D>(r, c, p.box_rows)) = make_uint4(0, 0, 0, 0);
+                    }
                 }
                 __syncwarp();
             }
@@ -470,7 +495,8 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
             for (int ks = 0; ks < KS; ++ks) {
                 uint32_t a[4];
                 const int c = 2 * ks + (mi >> 1);
-                ldmatrix_x4(a, ks_addr + k_row_off + (c >> 3) * half_bytes + (((c & 7) ^ (k_r & 7)) << 4));
+                if (IL) ldmatrix_x4(a, ks_addr + il_k_off + c * (p.box_rows * 16));
+                else ldmatrix_x4(a, ks_addr + k_row_off + (c >> 3) * half_bytes + (((c & 7) ^ (k_r & 7)) << 4));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     if (ks & 1) Elem<T>::mma16816(sb[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
@@ -517,7 +543,8 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
             for (int j = 0; j < KS; ++j) {
                 uint32_t a[4];
                 const int c = 2 * j + (mi & 1);
-                ldmatrix_x4_trans(a, vs_addr + v_row_off + (c >> 3) * half_bytes + (((c & 7) ^ (v_r & 7)) << 4));
+                if (IL) ldmatrix_x4(a, vs_addr + il_v_off + j * 16 * (p.box_rows * 2));
+                else ldmatrix_x4_trans(a, vs_addr + v_row_off + (c >> 3) * half_bytes + (((c & 7) ^ (v_r & 7)) << 4));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) Elem<T>::mma16816(st.o[nt][j], a, pb[nt][0], pb[nt][1]);
             }
@@ -610,26 +637,26 @@ int choose_kv_rep(int group, int max_heads) {
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-template <typename T, int D, int NT>
+template <typename T, int D, int NT, bool IL>
 int launch_decode(const DecodeParams &p, const CUtensorMap &tk, const CUtensorMap &tv, const LaunchShape &ls,
                   cudaStream_t stream) {
     constexpr int STAGE_BYTES = 2 * kTile * D * 2;
     const size_t smem = 1024 + (size_t)ls.nwarps * ls.nstages * (STAGE_BYTES + 8) + ((size_t)p.num_seqs + 1) * 4 + 16;
-    auto kern = paged_decode_stream_kernel<T, D, NT>;
+    auto kern = paged_decode_stream_kernel<T, D, NT, IL>;
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<ls.grid, ls.nwarps * 32, smem, stream>>>(p, tk, tv);
     NPD_CUDA_TRY(cudaGetLastError());
     return NPD_OK;
 }
 
-template <typename T>
+template <typename T, bool IL>
 int dispatch_decode(int head_dim, int nt, const DecodeParams &p, const CUtensorMap &tk, const CUtensorMap &tv,
                     const LaunchShape &ls, cudaStream_t stream) {
-    if (head_dim == 64 && nt == 1) return launch_decode<T, 64, 1>(p, tk, tv, ls, stream);
-    if (head_dim == 64 && nt == 2) return launch_decode<T, 64, 2>(p, tk, tv, ls, stream);
-    if (head_dim == 128 && nt == 1) return launch_decode<T, 128, 1>(p, tk, tv, ls, stream);
-    if (head_dim == 128 && nt == 2) return launch_decode<T, 128, 2>(p, tk, tv, ls, stream);
-    if (head_dim == 256 && nt == 1) return launch_decode<T, 256, 1>(p, tk, tv, ls, stream);
+    if (head_dim == 64 && nt == 1) return launch_decode<T, 64, 1, IL>(p, tk, tv, ls, stream);
+    if (head_dim == 64 && nt == 2) return launch_decode<T, 64, 2, IL>(p, tk, tv, ls, stream);
+    if (head_dim == 128 && nt == 1) return launch_decode<T, 128, 1, IL>(p, tk, tv, ls, stream);
+    if (head_dim == 128 && nt == 2) return launch_decode<T, 128, 2, IL>(p, tk, tv, ls, stream);
+    if (head_dim == 256 && nt == 1) return launch_decode<T, 256, 1, IL>(p, tk, tv, ls, stream);
     return npd::fail(NPD_ERR_UNSUPPORTED, "decode attention: no kernel for head_dim %d with %d head tiles", head_dim, nt);
 }
 
@@ -706,12 +733,29 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
 
     CUtensorMap tk, tv;
     const int box_rows = block_size < 16 ? static_cast<int>(block_size) : 16;
-    int rc = npd::encode_cache_tensor_map(&tk, k_cache, dtype, head_dim, num_kv_heads * block_size, num_blocks,
+    const bool interleaved = (flags & NPD_DECODE_KV_INTERLEAVED) != 0;
+    int rc;
+    if (interleaved) {
+        // K [blocks, Hkv, D/8, B, 8]: rows of B*8 elements, one per (kv head, 8-element piece of the head dim);
+        // V [blocks, Hkv, D, B]: rows of B elements, one per (kv head, head-dim element).  No swizzle.
+        const uint64_t kdims[3] = {(uint64_t)block_size * 8, (uint64_t)(num_kv_heads * head_dim / 8), (uint64_t)num_blocks};
+        const uint64_t kstr[2] = {(uint64_t)block_size * 16, (uint64_t)cache_block_stride * 2};
+        const uint32_t kbox[3] = {(uint32_t)box_rows * 8, (uint32_t)(head_dim / 8), 1u};
+        rc = npd::encode_tiled_3d(&tk, k_cache, dtype, kdims, kstr, kbox, false);
+        if (rc != NPD_OK) return rc;
+        const uint64_t vdims[3] = {(uint64_t)block_size, (uint64_t)(num_kv_heads * head_dim), (uint64_t)num_blocks};
+        const uint64_t vstr[2] = {(uint64_t)block_size * 2, (uint64_t)cache_block_stride * 2};
+        const uint32_t vbox[3] = {(uint32_t)box_rows, (uint32_t)head_dim, 1u};
+        rc = npd::encode_tiled_3d(&tv, v_cache, dtype, vdims, vstr, vbox, false);
+        if (rc != NPD_OK) return rc;
+    } else {
+        rc = npd::encode_cache_tensor_map(&tk, k_cache, dtype, head_dim, num_kv_heads * block_size, num_blocks,
                                           cache_block_stride, box_rows);
-    if (rc != NPD_OK) return rc;
-    rc = npd::encode_cache_tensor_map(&tv, v_cache, dtype, head_dim, num_kv_heads * block_size, num_blocks,
-                                      cache_block_stride, box_rows);
-    if (rc != NPD_OK) return rc;
+        if (rc != NPD_OK) return rc;
+        rc = npd::encode_cache_tensor_map(&tv, v_cache, dtype, head_dim, num_kv_heads * block_size, num_blocks,
+                                          cache_block_stride, box_rows);
+        if (rc != NPD_OK) return rc;
+    }
 
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     DecodeParams p;
@@ -746,9 +790,13 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
         p.q = static_cast<const uint8_t *>(q) + (size_t)s0 * num_q_heads * head_dim * elem;
         p.block_tables = block_tables + s0 * bt_row_stride;
         p.seq_lens = seq_lens + s0;
-        rc = dtype == NPD_DTYPE_F16
-                 ? dispatch_decode<__half>(static_cast<int>(head_dim), wp.nt, p, tk, tv, ls, st)
-                 : dispatch_decode<__nv_bfloat16>(static_cast<int>(head_dim), wp.nt, p, tk, tv, ls, st);
+        const int hd = static_cast<int>(head_dim);
+        if (interleaved)
+            rc = dtype == NPD_DTYPE_F16 ? dispatch_decode<__half, true>(hd, wp.nt, p, tk, tv, ls, st)
+                                        : dispatch_decode<__nv_bfloat16, true>(hd, wp.nt, p, tk, tv, ls, st);
+        else
+            rc = dtype == NPD_DTYPE_F16 ? dispatch_decode<__half, false>(hd, wp.nt, p, tk, tv, ls, st)
+                                        : dispatch_decode<__nv_bfloat16, false>(hd, wp.nt, p, tk, tv, ls, st);
         if (rc != NPD_OK) return rc;
     }
     return NPD_OK;

@@ -52,9 +52,9 @@ int sm_count(int device);
 // 2-byte elements with 128-byte swizzle; box = 64 elements x box_rows rows x 1 block.
 // Resolved through cudaGetDriverEntryPoint so the library has no link-time dependency
 // on libcuda and loads on machines without a driver.
-// General rank-3 tiled map of 2-byte elements with 128-byte swizzle (box[0] must be 64).
+// General rank-3 tiled map of 2-byte elements; with the 128-byte swizzle (box[0] must be 64) or without.
 int encode_tiled_3d(CUtensorMap *map, const void *base, int dtype, const uint64_t dims[3],
-                    const uint64_t strides_bytes[2], const uint32_t box[3]);
+                    const uint64_t strides_bytes[2], const uint32_t box[3], bool swizzle128 = true);
 int encode_cache_tensor_map(CUtensorMap *map, const void *base, int dtype, int64_t head_dim,
                             int64_t rows_per_block, int64_t num_blocks,
                             int64_t block_stride_elems, int box_rows);

@@ -234,10 +234,17 @@ def paged_attention_forward(out, query, key_cache, value_cache, block_tables, se
     (pinned by tests/test_paged_kernels.py:218-227).  As in the reference's pointer math
     (paged_attention_kernel.cu:72), row ``s`` of a contiguous table starts at
     ``s * max_num_blocks_per_seq``.
+
+    The interleaved layouts the reference's split-K op and its kernel tests use are accepted under the
+    same name (csrc/paged_attention_optimized/paged_attention_optimized_ops.cu:33-34,
+    tests/test_paged_kernels.py:39-56): a 5-D ``key_cache`` ``[blocks, Hkv, D/8, B, 8]`` goes with a
+    ``value_cache`` ``[blocks, Hkv, D, B]``.
     """
     _require(query.is_cuda, "query is must be on CUDA")
     _require(query.dim() == 3, "query must be [num seqs, num_heads, head_size]")
-    _require(key_cache.dim() == 4, "key_cache must be [num_blocks, num_kv_heads, block_size, head_size]")
+    _require(key_cache.dim() in (4, 5), "key_cache must be [num_blocks, num_kv_heads, block_size, head_size] "
+                                        "or [num_blocks, num_kv_heads, head_size/8, block_size, 8]")
+    interleaved = key_cache.dim() == 5
     _require(block_tables.dtype == torch.int32, "block_tables must be int32")
     _require(seq_lens.dtype == torch.int32, "seq_lens must be int32")
     dev = query.device
@@ -250,9 +257,19 @@ def paged_attention_forward(out, query, key_cache, value_cache, block_tables, se
     _require(key_cache.dtype == query.dtype and value_cache.dtype == query.dtype, "cache dtype differs from query")
     _require(key_cache.device == dev and value_cache.device == dev and block_tables.device == dev
              and seq_lens.device == dev, "all tensors must be on the query's device")
-    nb, hkv, bs, cd, cstride = _cache_geometry(key_cache, "key_cache")
-    _require(_cache_geometry(value_cache, "value_cache") == (nb, hkv, bs, cd, cstride),
-             "key_cache and value_cache layouts differ")
+    if interleaved:
+        nb, hkv, pieces, bs, x = key_cache.shape
+        _require(x == 8 and pieces * x == d, "interleaved key_cache must be [blocks, Hkv, head_size/8, block_size, 8]")
+        _require(value_cache.dim() == 4 and tuple(value_cache.shape) == (nb, hkv, d, bs),
+                 "interleaved value_cache must be [blocks, Hkv, head_size, block_size]")
+        _require(key_cache[0].is_contiguous() and value_cache[0].is_contiguous()
+                 and key_cache.stride(0) == value_cache.stride(0), "interleaved caches must be contiguous per block")
+        cd, cstride = d, key_cache.stride(0)
+        _flags = int(_flags) | _lib.NPD_DECODE_KV_INTERLEAVED
+    else:
+        nb, hkv, bs, cd, cstride = _cache_geometry(key_cache, "key_cache")
+        _require(_cache_geometry(value_cache, "value_cache") == (nb, hkv, bs, cd, cstride),
+                 "key_cache and value_cache layouts differ")
     _require(cd == d, "head_size of query and cache differ")
     _require(int(block_size) == bs, f"block_size argument {block_size} != cache block size {bs}")
     _require(hq % hkv == 0, "num_heads must be a multiple of num_kv_heads")
