@@ -472,11 +472,72 @@ def run_gpu_arm(args):
             md["n_gpus"] = world
             md["tok_s_all_gpus"] = round(toks_model / (ms_model * 1e-3), 1)
         extras["model_decode"] = md
+    if world > 1:
+        # Page migration over NVLink: rank 0 pulls 1024 blocks x 36 layers (2.4 GB, one 16k-token request of
+        # the Qwen3-8B layout) from the next GPU's pool into its own while the other ranks wait.
+        if rank == 0:
+            try:
+                peer = (local_rank + 1) % torch.cuda.device_count()
+                L_m, nb_m = 36, 1024
+                src_k = torch.empty(L_m, nb_m, Hkv, B, D, dtype=torch.bfloat16, device=f"cuda:{peer}").normal_()
+                src_v = torch.empty(L_m, nb_m, Hkv, B, D, dtype=torch.bfloat16, device=f"cuda:{peer}").normal_()
+                dst_k = torch.empty(L_m, nb_m, Hkv, B, D, dtype=torch.bfloat16, device=dev)
+                dst_v = torch.empty_like(dst_k)
+                ids = torch.randperm(nb_m).tolist()
+                torch.cuda.synchronize(peer)
+                fn = lambda: kv_transfer.transfer_kv(src_k, src_v, dst_k, dst_v, ids)
+                fn()
+                torch.cuda.synchronize(dev)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(5):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize(dev)
+                ms_mig = e0.elapsed_time(e1) / 5
+                mig_bytes = kv_transfer.migration_bytes(nb_m, src_k)
+                ok = torch.equal(dst_k[:, ids[0]].cpu(), src_k[:, ids[0]].cpu())
+                extras["migrate_nvlink"] = {"gbs_one_direction": round(mig_bytes / (ms_mig * 1e-3) / 1e9, 1),
+                                            "ms": round(ms_mig, 3), "bytes": mig_bytes, "blocks": nb_m, "layers": L_m,
+                                            "from_gpu": peer, "to_gpu": local_rank, "data_check": bool(ok),
+                                            "peak_gbs": 770.0, "peak_source": "measured peer copy on this pool"}
+                del src_k, src_v, dst_k, dst_v
+            except Exception as exc:  # noqa: BLE001
+                extras["migrate_nvlink_error"] = str(exc)[:200]
+        replicas.barrier()
     if rank == 0 and world == 1:
         # secondary kernels, timed briefly
         extras["attention_ms"] = round(ms_attn, 4)
         extras["store_ms"] = round(ms_store, 4)
         extras["store_gbs"] = round(store_bytes / (ms_store * 1e-3) / 1e9, 2)
+        try:
+            # fused QK-norm + rotary + store: the decode batch (one token per sequence) and an 8192-token prefill
+            for label, T_f in (("decode_256_tokens", S), ("prefill_8192_tokens", 8192)):
+                qkv = torch.randn(T_f, (Hq + 2 * Hkv) * D, device=dev).to(torch.bfloat16)
+                q_f = qkv[:, :Hq * D].view(T_f, Hq, D)
+                k_f = qkv[:, Hq * D:(Hq + Hkv) * D].view(T_f, Hkv, D)
+                v_f = qkv[:, (Hq + Hkv) * D:].view(T_f, Hkv, D)
+                cs = torch.randn(T_f, D, device=dev).to(torch.bfloat16)
+                wn = torch.ones(D, dtype=torch.bfloat16, device=dev)
+                q_o = torch.empty(T_f, Hq, D, dtype=torch.bfloat16, device=dev)
+                if T_f == S:
+                    bt_f, pos_f = b.block_tables, positions
+                else:       # tokens spread over the batch's sequences, T_f / S consecutive positions each
+                    per = T_f // S
+                    bt_f = b.block_tables.repeat_interleave(per, dim=0)
+                    pos_f = (torch.clamp(positions - per, min=0).repeat_interleave(per) +
+                             torch.arange(per, device=dev, dtype=torch.int32).repeat(S))
+                fn_f = lambda: paged_kernels.paged_qk_norm_rope_store(q_f, k_f, v_f, cs, cs, b.k_cache, b.v_cache, bt_f,
+                                                                      pos_f, wn, wn, 1e-6, q_out=q_o)
+                for _ in range(3):
+                    fn_f()
+                ms_f = timed(fn_f, min(steps, 50))
+                bytes_f = 2 * T_f * (Hq + 2 * Hkv) * D * 2 + 2 * T_f * D * 2 + 8 * T_f
+                extras.setdefault("fused_norm_rope_store", {})[label] = {
+                    "ms": round(ms_f, 4), "gbs": round(bytes_f / (ms_f * 1e-3) / 1e9, 1), "algorithmic_bytes": bytes_f}
+            del qkv, q_o
+        except Exception as exc:  # noqa: BLE001
+            extras["fused_norm_rope_store_error"] = str(exc)[:200]
         try:
             # the same launch on the interleaved cache layouts of the reference's split-K op
             k_il = b.k_cache.view(b.k_cache.size(0), Hkv, B, D // 8, 8).permute(0, 1, 3, 2, 4).contiguous()

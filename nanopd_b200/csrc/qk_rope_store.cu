@@ -12,9 +12,9 @@
 //   RMSNorm (Qwen3RMSNorm): x32 = float(x); y = T(x32 * rsqrt(mean(x32^2) + eps)); y = T(w * y)
 //   rotary (apply_rotary_pos_emb): out = T(T(y * cos) + T(rotate_half(y) * sin)),
 //   rotate_half(y) = concat(-y[D/2:], y[:D/2]),   T(.) = round to the tensor's 16-bit type.
-// One warp per (token, head) row; a lane owns EPL consecutive elements of each half of the row, so
-// the two elements a rotation pairs sit in the same lane and the mean of squares is one warp
-// reduction.  HBM-bound, launch-latency bound at decode sizes.
+// A (token, head) row is D/8 lanes of 16 bytes; the two elements a rotation pairs sit at the same place
+// of two lanes half a row apart (one shuffle), the mean of squares is a reduction over the row's lanes,
+// and every warp keeps two passes of rows in flight.  HBM-bound, launch-latency bound at decode sizes.
 #include "npd_common.cuh"
 
 namespace {
@@ -46,100 +46,119 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float
 // round to T and back: where the 16-bit reference arithmetic rounds
 template <typename T> __device__ __forceinline__ float rt(float x) { return to_f<T>(from_f<T>(x)); }
 
-template <typename T, int EPL> struct Vec { T v[EPL]; };
-
-template <typename T, int EPL>
-__device__ __forceinline__ void load_vec(const T *p, float (&out)[EPL]) {
-    using V = Vec<T, EPL>;
-    const V raw = *reinterpret_cast<const V *>(p);
+// 8 elements (16 bytes) of T <-> 8 floats
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4 &raw, float (&out)[8]) {
+    const T *e = reinterpret_cast<const T *>(&raw);
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) out[i] = to_f<T>(raw.v[i]);
+    for (int i = 0; i < 8; ++i) out[i] = to_f<T>(e[i]);
 }
-template <typename T, int EPL>
-__device__ __forceinline__ void store_vec(T *p, const float (&in)[EPL]) {
-    using V = Vec<T, EPL>;
-    V raw;
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&in)[8]) {
+    uint4 raw;
+    T *e = reinterpret_cast<T *>(&raw);
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) raw.v[i] = from_f<T>(in[i]);
-    *reinterpret_cast<V *>(p) = raw;
+    for (int i = 0; i < 8; ++i) e[i] = from_f<T>(in[i]);
+    return raw;
 }
 
-// EPL elements per lane per half row: head_dim = 64 * EPL.
-template <typename T, int EPL>
+// A row of D elements is D/8 pieces of 16 bytes, one per lane: LPR = D/8 lanes per row, 32/LPR rows per warp pass,
+// the lower LPR/2 lanes of a row hold its first half and the upper ones the second half, so the element a rotation
+// pairs with sits at the same place of lane ^ (LPR/2).  Two passes are kept in flight (loads of both first).
+template <typename T, int D>
 __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStoreParams p) {
-    constexpr int D = 64 * EPL;
+    constexpr int LPR = D / 8;                 // lanes per row
+    constexpr int RPW = 32 / LPR;              // rows per warp pass
+    constexpr int UNROLL = 2;
     const int lane = threadIdx.x & 31;
+    const int sub = lane % LPR, row_in_pass = lane / LPR;
+    const bool upper = sub >= LPR / 2;
     const int rows_per_token = p.num_q_heads + 2 * p.num_kv_heads;
     const long long total = p.num_tokens * rows_per_token;
     const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long w = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); w < total; w += warps) {
-        const long long t = w / rows_per_token;
-        const int r = static_cast<int>(w - t * rows_per_token);
-        const int kind = r < p.num_q_heads ? 0 : (r < p.num_q_heads + p.num_kv_heads ? 1 : 2);   // q, k, v
-        const int h = kind == 0 ? r : (kind == 1 ? r - p.num_q_heads : r - p.num_q_heads - p.num_kv_heads);
-
-        // destination of a k or v row: its page slot
-        T *dst;
-        if (kind == 0) {
-            dst = static_cast<T *>(p.q_out) + t * p.q_out_token_stride + (long long)h * D;
-        } else {
-            const int pos = __ldg(p.positions + t);
-            const int blk_idx = pos / p.block_size;
-            const int off = pos - blk_idx * p.block_size;
-            if (pos < 0 || blk_idx >= p.max_blocks_per_seq) {
-                if (p.status && lane == 0) atomicOr(p.status, NPD_STATUS_BAD_POSITION);
-                continue;
+    const long long w0 = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    for (long long base = w0 * (RPW * UNROLL); base < total; base += warps * (RPW * UNROLL)) {
+        uint4 raw[UNROLL], craw[UNROLL], sraw[UNROLL];
+        T *dst[UNROLL];
+        int kind[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const long long w = base + u * RPW + row_in_pass;
+            dst[u] = nullptr;
+            kind[u] = 2;
+            raw[u] = craw[u] = sraw[u] = make_uint4(0, 0, 0, 0);
+            if (w >= total) continue;
+            const long long t = w / rows_per_token;
+            const int r = static_cast<int>(w - t * rows_per_token);
+            const int kd = r < p.num_q_heads ? 0 : (r < p.num_q_heads + p.num_kv_heads ? 1 : 2);   // q, k, v
+            const int h = kd == 0 ? r : (kd == 1 ? r - p.num_q_heads : r - p.num_q_heads - p.num_kv_heads);
+            kind[u] = kd;
+            const T *src = kd == 0 ? static_cast<const T *>(p.q) + t * p.q_token_stride
+                         : kd == 1 ? static_cast<const T *>(p.k) + t * p.k_token_stride
+                                   : static_cast<const T *>(p.v) + t * p.v_token_stride;
+            raw[u] = __ldg(reinterpret_cast<const uint4 *>(src + (long long)h * D + sub * 8));
+            if (kd != 2) {
+                craw[u] = __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.cos) + t * p.cs_row_stride + sub * 8));
+                sraw[u] = __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.sin) + t * p.cs_row_stride + sub * 8));
             }
-            const int phys = __ldg(p.block_tables + t * p.bt_row_stride + blk_idx);
-            if (phys < 0 || phys >= p.num_blocks) {
-                if (p.status && lane == 0) atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
-                continue;
-            }
-            dst = static_cast<T *>(kind == 1 ? p.k_cache : p.v_cache) + phys * p.cache_block_stride +
-                  ((long long)h * p.block_size + off) * D;
-        }
-        const T *src = kind == 0 ? static_cast<const T *>(p.q) + t * p.q_token_stride
-                     : kind == 1 ? static_cast<const T *>(p.k) + t * p.k_token_stride
-                                 : static_cast<const T *>(p.v) + t * p.v_token_stride;
-        src += (long long)h * D;
-
-        float lo[EPL], hi[EPL];
-        load_vec<T, EPL>(src + lane * EPL, lo);
-        load_vec<T, EPL>(src + D / 2 + lane * EPL, hi);
-        if (kind != 2) {
-            const T *wgt = static_cast<const T *>(kind == 0 ? p.q_w : p.k_w);
-            if (wgt != nullptr) {
-                float ss = 0.f;
-#pragma unroll
-                for (int i = 0; i < EPL; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
-#pragma unroll
-                for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
-                const float inv = rsqrtf(ss * (1.f / D) + p.eps);
-                float wl[EPL], wh[EPL];
-                load_vec<T, EPL>(wgt + lane * EPL, wl);
-                load_vec<T, EPL>(wgt + D / 2 + lane * EPL, wh);
-#pragma unroll
-                for (int i = 0; i < EPL; ++i) {
-                    lo[i] = rt<T>(wl[i] * rt<T>(lo[i] * inv));
-                    hi[i] = rt<T>(wh[i] * rt<T>(hi[i] * inv));
+            if (kd == 0) {
+                dst[u] = static_cast<T *>(p.q_out) + t * p.q_out_token_stride + (long long)h * D + sub * 8;
+            } else {
+                // destination of a k or v row: its page slot
+                const int pos = __ldg(p.positions + t);
+                const int blk_idx = pos / p.block_size;
+                const int off = pos - blk_idx * p.block_size;
+                if (pos < 0 || blk_idx >= p.max_blocks_per_seq) {
+                    if (p.status && sub == 0) atomicOr(p.status, NPD_STATUS_BAD_POSITION);
+                    continue;
                 }
-            }
-            const T *cs = static_cast<const T *>(p.cos) + t * p.cs_row_stride;
-            const T *sn = static_cast<const T *>(p.sin) + t * p.cs_row_stride;
-            float cl[EPL], ch[EPL], sl[EPL], sh[EPL];
-            load_vec<T, EPL>(cs + lane * EPL, cl);
-            load_vec<T, EPL>(cs + D / 2 + lane * EPL, ch);
-            load_vec<T, EPL>(sn + lane * EPL, sl);
-            load_vec<T, EPL>(sn + D / 2 + lane * EPL, sh);
-#pragma unroll
-            for (int i = 0; i < EPL; ++i) {
-                const float a = lo[i], b = hi[i];
-                lo[i] = rt<T>(a * cl[i]) + rt<T>(-b * sl[i]);      // rotate_half: the first half pairs with -second
-                hi[i] = rt<T>(b * ch[i]) + rt<T>(a * sh[i]);
+                const int phys = __ldg(p.block_tables + t * p.bt_row_stride + blk_idx);
+                if (phys < 0 || phys >= p.num_blocks) {
+                    if (p.status && sub == 0) atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
+                    continue;
+                }
+                dst[u] = static_cast<T *>(kd == 1 ? p.k_cache : p.v_cache) + phys * p.cache_block_stride +
+                         ((long long)h * p.block_size + off) * D + sub * 8;
             }
         }
-        store_vec<T, EPL>(dst + lane * EPL, lo);
-        store_vec<T, EPL>(dst + D / 2 + lane * EPL, hi);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            // every lane takes part in the shuffles; rows without work carry zeros
+            float x[8];
+            unpack8<T>(raw[u], x);
+            const T *wgt = static_cast<const T *>(kind[u] == 0 ? p.q_w : (kind[u] == 1 ? p.k_w : nullptr));
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+            for (int s = LPR / 2; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+            if (wgt != nullptr) {
+                const float inv = rsqrtf(ss * (1.f / D) + p.eps);
+                float wv[8];
+                unpack8<T>(__ldg(reinterpret_cast<const uint4 *>(wgt + sub * 8)), wv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = rt<T>(wv[i] * rt<T>(x[i] * inv));
+            }
+            // the partner half of the row, as the 16-bit values the rotation reads
+            uint4 mine = pack8<T>(x), other;
+            other.x = __shfl_xor_sync(0xffffffffu, mine.x, LPR / 2);
+            other.y = __shfl_xor_sync(0xffffffffu, mine.y, LPR / 2);
+            other.z = __shfl_xor_sync(0xffffffffu, mine.z, LPR / 2);
+            other.w = __shfl_xor_sync(0xffffffffu, mine.w, LPR / 2);
+            if (kind[u] != 2) {
+                float y[8], c[8], sn[8];
+                unpack8<T>(other, y);
+                unpack8<T>(craw[u], c);
+                unpack8<T>(sraw[u], sn);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float rot = upper ? y[i] : -y[i];       // rotate_half: (-second half, first half)
+                    x[i] = rt<T>(x[i] * c[i]) + rt<T>(rot * sn[i]);
+                }
+                mine = pack8<T>(x);
+            }
+            if (dst[u] != nullptr) *reinterpret_cast<uint4 *>(dst[u]) = mine;
+        }
     }
 }
 
@@ -147,13 +166,14 @@ template <typename T>
 int launch(const RopeStoreParams &p, int head_dim, int device, cudaStream_t stream) {
     const long long total = p.num_tokens * (p.num_q_heads + 2 * p.num_kv_heads);
     const int threads = 256;
-    long long blocks = (total + 7) / 8;
+    const long long rows_per_block = 8LL * (32 / (head_dim / 8)) * 2;      // warps x rows per pass x passes in flight
+    long long blocks = (total + rows_per_block - 1) / rows_per_block;
     const long long cap = (long long)npd::sm_count(device) * 8;
     if (blocks > cap) blocks = cap;
     switch (head_dim) {
-        case 64: qk_norm_rope_store_kernel<T, 1><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
-        case 128: qk_norm_rope_store_kernel<T, 2><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
-        case 256: qk_norm_rope_store_kernel<T, 4><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
+        case 64: qk_norm_rope_store_kernel<T, 64><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
+        case 128: qk_norm_rope_store_kernel<T, 128><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
+        case 256: qk_norm_rope_store_kernel<T, 256><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p); break;
         default: return npd::fail(NPD_ERR_UNSUPPORTED, "npd_qk_norm_rope_store: head_dim %d not in {64,128,256}", head_dim);
     }
     NPD_CUDA_TRY(cudaGetLastError());
