@@ -37,7 +37,7 @@ using namespace npd;
 
 constexpr int kTile = 16;               // tokens per stage
 constexpr int kMaxSeqsPerLaunch = 4096; // prefix array lives in shared memory
-constexpr int kMinTilesPerWorker = 4;   // keeps tiny batches from dissolving into partials
+constexpr int kMinTilesPerWorker = 8;   // keeps tiny batches from dissolving into partials
 constexpr int kStatusBytes = 256;       // workspace header: status word + padding
 constexpr int kTicketCapacity = 1 << 18;   // ticket words (1 MiB): a FIXED region right after the header, so that no
                                         // launch shape ever puts partial records where another shape keeps tickets
@@ -263,35 +263,65 @@ __device__ __forceinline__ void write_partial(const AttnState<T, D, NT> &st, flo
 
 // Folds the partial records of workers wf..wl (one (sequence, kv head) cut by range boundaries) into `st`.
 // Records were written by other SMs during this launch: read them through L2 (ld.global.cg), never L1.
+// Two passes, so that no load waits for arithmetic on an earlier one: first the maximum over all records (eight
+// records per step, one per lane group), then the weighted sum with four records' loads in flight.  A long
+// context in a small batch is cut into a hundred and more partials per kv head; a record-by-record rescaling
+// chain made that merge longer than the streaming itself.
 template <typename T, int D, int NT>
 __device__ __forceinline__ void merge_partials(AttnState<T, D, NT> &st, const DecodeParams &p, int wf, int wl, int lane) {
     constexpr int KS = D / 16;
+    const int g = lane >> 2, t4 = lane & 3;
+    auto record = [&](int w) { return p.partials + ((size_t)w * 2 + (w == wf ? 1 : 0)) * rec_floats<D, NT>(); };
+    float mg[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mg[nt][0] = mg[nt][1] = -INFINITY;
+#pragma unroll 4
+    for (int w0 = wf; w0 <= wl; w0 += 8) {
+        const int w = w0 + g;
+        if (w <= wl) {
+            const float4 *ml4 = reinterpret_cast<const float4 *>(record(w) + NT * KS * 128);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float4 ml = __ldcg(ml4 + nt * 4 + t4);
+                mg[nt][0] = fmaxf(mg[nt][0], ml.x);
+                mg[nt][1] = fmaxf(mg[nt][1], ml.y);
+            }
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+#pragma unroll
+            for (int d = 4; d < 32; d <<= 1) mg[nt][e] = fmaxf(mg[nt][e], __shfl_xor_sync(0xffffffffu, mg[nt][e], d));
     st.reset();
+    constexpr int kInFlight = NT * KS >= 16 ? 2 : 4;      // records whose loads are issued together (register budget)
+#pragma unroll kInFlight
     for (int w = wf; w <= wl; ++w) {
-        const float *rec = p.partials + ((size_t)w * 2 + (w == wf ? 1 : 0)) * rec_floats<D, NT>();
+        const float *rec = record(w);
         const float4 *o4 = reinterpret_cast<const float4 *>(rec);
         const float4 *ml4 = reinterpret_cast<const float4 *>(rec + NT * KS * 128);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const float4 ml = __ldcg(ml4 + nt * 4 + (lane & 3));
-            const float mn0 = fmaxf(st.m[nt][0], ml.x), mn1 = fmaxf(st.m[nt][1], ml.y);
-            const float so0 = st.m[nt][0] == -INFINITY ? 0.f : fast_exp2(st.m[nt][0] - mn0);
-            const float so1 = st.m[nt][1] == -INFINITY ? 0.f : fast_exp2(st.m[nt][1] - mn1);
-            const float sn0 = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - mn0);
-            const float sn1 = ml.y == -INFINITY ? 0.f : fast_exp2(ml.y - mn1);
-            st.l[nt][0] = st.l[nt][0] * so0 + ml.z * sn0;
-            st.l[nt][1] = st.l[nt][1] * so1 + ml.w * sn1;
-            st.m[nt][0] = mn0;
-            st.m[nt][1] = mn1;
+            const float4 ml = __ldcg(ml4 + nt * 4 + t4);
+            const float sn0 = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - mg[nt][0]);
+            const float sn1 = ml.y == -INFINITY ? 0.f : fast_exp2(ml.y - mg[nt][1]);
+            st.l[nt][0] += ml.z * sn0;
+            st.l[nt][1] += ml.w * sn1;
 #pragma unroll
             for (int j = 0; j < KS; ++j) {
                 const float4 o = __ldcg(o4 + (nt * KS + j) * 32 + lane);
-                st.o[nt][j][0] = st.o[nt][j][0] * so0 + o.x * sn0;
-                st.o[nt][j][1] = st.o[nt][j][1] * so1 + o.y * sn1;
-                st.o[nt][j][2] = st.o[nt][j][2] * so0 + o.z * sn0;
-                st.o[nt][j][3] = st.o[nt][j][3] * so1 + o.w * sn1;
+                st.o[nt][j][0] += o.x * sn0;
+                st.o[nt][j][1] += o.y * sn1;
+                st.o[nt][j][2] += o.z * sn0;
+                st.o[nt][j][3] += o.w * sn1;
             }
         }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        st.m[nt][0] = mg[nt][0];
+        st.m[nt][1] = mg[nt][1];
     }
 }
 
