@@ -261,6 +261,25 @@ def run_prefill_workload(args, paged_kernels, dev, timed):
     for _ in range(3):
         mixed_step()
     ms_mixed = timed(mixed_step, steps)
+    # the same mixed step with the two attention kernels side by side on two streams, each on its share of the SMs
+    from nanopd_b200 import paged_forward
+    P2, Dn2 = q2.size(0), d.query.size(0)
+    sc = paged_forward.StepContext(
+        num_prefill_tokens=P2, num_decode_tokens=Dn2, block_size=B, prefill_tables=bt2, prefill_offsets=offs2,
+        prefill_tokens=toks2, prefill_starts=starts2, decode_tables=d.block_tables, decode_positions=d.positions,
+        decode_seq_lens=seq_lens,
+        prefill_score_pairs=sum(n * s0 + n * (n + 1) // 2 for n, s0 in zip(toks2, starts2)),
+        decode_context_tokens=int(seq_lens.sum().item()))
+    q_all = torch.cat([q2, d.query]).contiguous()
+    out_all = torch.empty_like(q_all)
+    sm_share = paged_forward._sm_split(sc, Hq, d.num_kv_heads, D, 2, dev)
+
+    def mixed_step_overlapped():
+        paged_kernels.paged_kv_store(d.k_cache, d.v_cache, d.k_new, d.v_new, d.block_tables, d.positions)
+        paged_forward._attend(sc, out_all, q_all, d.k_cache, d.v_cache, d.scale, True)
+    for _ in range(3):
+        mixed_step_overlapped()
+    ms_mixed_overlapped = timed(mixed_step_overlapped, steps)
     ms_last = timed(lambda: paged_kernels.paged_prefill_attention(out2, q2, d.k_cache, d.v_cache, bt2, offs2, toks2,
                                                                   starts2, d.scale, B, bt2.size(1)), steps)
     peak, src = measured_peak_tflops()
@@ -271,6 +290,7 @@ def run_prefill_workload(args, paged_kernels, dev, timed):
             "last_chunks_ms": round(ms_last, 4),
             "last_chunks_tflops": round(prefill_flops(last, Hq, D) / (ms_last * 1e-3) / 1e12, 1),
             "mixed_step_ms": round(ms_mixed, 4),
+            "mixed_step_two_streams_ms": round(ms_mixed_overlapped, 4), "prefill_sm_share": sm_share,
             "mixed_step": "last 512-token chunk of each of 4 prompts + store + decode attention of 128 sequences"}
 
 def run_model_workload(args, dev, timed, batch, seed):

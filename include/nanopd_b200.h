@@ -40,7 +40,11 @@ extern "C" {
 #define NPD_STATUS_BAD_POSITION   2   /* a position / seq_len beyond the table's capacity; clamped or skipped */
 #define NPD_STATUS_WAIT_TIMEOUT   4   /* a bounded wait on an in-kernel barrier ran out                       */
 
-/* Flags of npd_paged_decode_attention */
+/* Flags of npd_paged_decode_attention and npd_paged_prefill_attention.  Both kernels are persistent, one CTA per
+ * SM; NPD_FLAG_MAX_CTAS(n) caps the grid at n CTAs (0 = no cap) so that two of them — a prompt chunk and the
+ * decode batch of the same scheduler step — can run side by side on two streams, each on its share of the SMs. */
+#define NPD_FLAG_MAX_CTAS(n)      (((n) & 0xffff) << 8)
+
 #define NPD_DECODE_SKIP_MERGE     1   /* diagnostic: sequences split across workers stay unmerged (wrong rows for those) */
 #define NPD_DECODE_KV_INTERLEAVED 2   /* caches in the layouts of the reference's split-K op and of its kernel tests
                                        * (csrc/paged_attention_optimized/index.h:14-31,60-75; tests/test_paged_kernels.py:39-56):

@@ -754,7 +754,9 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
 
     int dev = 0;
     NPD_CUDA_TRY(cudaGetDevice(&dev));
-    const LaunchShape ls = launch_shape(static_cast<int>(head_dim), dev);
+    LaunchShape ls = launch_shape(static_cast<int>(head_dim), dev);
+    const int cta_cap = (flags >> 8) & 0xffff;
+    if (cta_cap > 0 && cta_cap < ls.grid) ls.grid = cta_cap;
     const WorkspacePlan wp = plan_workspace(num_seqs, num_q_heads, num_kv_heads, head_dim, ls);
     NPD_REQUIRE(workspace != nullptr && workspace_bytes >= wp.total, NPD_ERR_WORKSPACE,
                 "decode attention: workspace of %zu bytes given, %zu needed", workspace_bytes, wp.total);

@@ -860,7 +860,7 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
         p.num_blocks = static_cast<int>(num_blocks);
         p.bt_row_stride = bt_row_stride;
-        p.debug_flags = flags;
+        p.debug_flags = flags & 0xff;
 #ifdef NPD_PREFILL_TRACE
         p.trace = workspace_bytes >= 256 + 11 * 4096 * sizeof(long long)
                       ? reinterpret_cast<long long *>(static_cast<uint8_t *>(workspace) + 256) : nullptr;
@@ -890,7 +890,9 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
             p.work_counter = reinterpret_cast<int *>(static_cast<uint8_t *>(workspace) + 64);
             NPD_CUDA_TRY(cudaMemsetAsync(p.work_counter, 0, sizeof(int), launch_stream));
             const long long items = (long long)ne * num_kv_heads;
-            const long long grid = items < sms ? items : sms;     // persistent: one CTA per SM
+            long long grid = items < sms ? items : sms;           // persistent: one CTA per SM
+            const int cta_cap = (flags >> 8) & 0xffff;
+            if (cta_cap > 0 && cta_cap < grid) grid = cta_cap;
             kern<<<static_cast<unsigned>(grid), kThreads, smem, launch_stream>>>(p, tq_map, tk, tv);
             NPD_CUDA_TRY(cudaGetLastError());
         }

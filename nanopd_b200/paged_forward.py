@@ -41,6 +41,9 @@ class StepContext:
     decode_positions: Optional[torch.Tensor] = None    # int32 [Dn]
     decode_seq_lens: Optional[torch.Tensor] = None     # int32 [Dn] = position + 1
     h2d_bytes: int = 0
+    # host-side work estimates behind the SM split of a mixed step
+    prefill_score_pairs: int = 0                       # sum over prompt chunks of n*start + n(n+1)/2
+    decode_context_tokens: int = 0                     # sum over decode sequences of position + 1
 
 
 def _padded_table(rows: List[List[int]]) -> np.ndarray:
@@ -81,6 +84,7 @@ def build_step_context(ctx: Dict, device, block_size: int = 16) -> StepContext:
             sc.prefill_offsets.append(off)
             sc.prefill_tokens.append(n)
             sc.prefill_starts.append(start)
+            sc.prefill_score_pairs += n * start + n * (n + 1) // 2
             off += n
         parts["prefill_positions"] = np.concatenate(pos) if pos else np.zeros(0, np.int32)
     if decodes:
@@ -91,6 +95,7 @@ def build_step_context(ctx: Dict, device, block_size: int = 16) -> StepContext:
                 raise RuntimeError("a decode position lies beyond its block table")
         parts["decode_positions"] = positions
         parts["decode_seq_lens"] = positions + 1
+        sc.decode_context_tokens = int(positions.sum()) + len(decodes)
 
     # one staging buffer, 256-byte aligned sections, one copy
     offsets, total = {}, 0
@@ -114,8 +119,68 @@ def build_step_context(ctx: Dict, device, block_size: int = 16) -> StepContext:
     return sc
 
 
+# ---- a mixed step on two streams ---------------------------------------------------------------------------
+# The prompt chunks' attention is tensor-bound and the decode batch's HBM-bound; both kernels are persistent with
+# one CTA per SM.  Run one after the other, each leaves the other's resource idle.  In a mixed step they are
+# launched side by side instead, each capped to its share of the SMs, the shares in proportion to estimated times.
+_PREFILL_FLOPS_PER_S = 0.95e15     # measured rates of the two kernels on a B200, only used for the split
+_DECODE_BYTES_PER_S = 6.0e12
+_MIN_OVERLAP_SECONDS = 15e-6       # below this much estimated work on either side, fork and join cost more than they save
+_side_streams: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def _sm_split(sc: StepContext, hq: int, hkv: int, d: int, elem: int, device) -> Optional[int]:
+    """SMs for the prompt chunks in a mixed step (the rest go to the decode batch); None = run them in turn."""
+    if sc.num_prefill_tokens == 0 or sc.num_decode_tokens == 0:
+        return None
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    t_p = 4.0 * hq * d * sc.prefill_score_pairs / _PREFILL_FLOPS_PER_S
+    t_d = 2.0 * hkv * d * elem * sc.decode_context_tokens / _DECODE_BYTES_PER_S
+    if min(t_p, t_d) < _MIN_OVERLAP_SECONDS:
+        return None
+    share = int(round(sms * t_p / (t_p + t_d)))
+    return max(16, min(sms - 32, share))
+
+
+def _attend(sc: StepContext, out, q_tokens_major, k_cache, v_cache, scale, overlap: bool):
+    """Prompt-chunk attention over rows [:P] and decode attention over rows [P:] of token-major queries."""
+    P, Dn = sc.num_prefill_tokens, sc.num_decode_tokens
+    bs = k_cache.size(2)
+    _, hq, d = q_tokens_major.shape
+    dev = q_tokens_major.device
+    share = _sm_split(sc, hq, k_cache.size(1), d, q_tokens_major.element_size(), dev) if overlap else None
+
+    def prefill(max_ctas=0):
+        paged_kernels.paged_prefill_attention(out[:P], q_tokens_major[:P], k_cache, v_cache, sc.prefill_tables,
+                                              sc.prefill_offsets, sc.prefill_tokens, sc.prefill_starts,
+                                              scale, bs, sc.prefill_tables.size(1), max_ctas=max_ctas)
+
+    def decode(max_ctas=0):
+        paged_kernels.paged_attention_forward(out[P:], q_tokens_major[P:], k_cache, v_cache, sc.decode_tables,
+                                              sc.decode_seq_lens, scale, bs, sc.decode_tables.size(1),
+                                              max_ctas=max_ctas)
+
+    if share is None:
+        if P > 0:
+            prefill()
+        if Dn > 0:
+            decode()
+        return
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    main = torch.cuda.current_stream(dev)
+    side = _side_streams.get(dev.index)
+    if side is None:
+        side = _side_streams[dev.index] = torch.cuda.Stream(device=dev)
+    side.wait_stream(main)                       # the stores and q are ready
+    with torch.cuda.stream(side):
+        prefill(max_ctas=share)
+    decode(max_ctas=sms - share)
+    main.wait_stream(side)
+
+
 def paged_attention_step(sc: StepContext, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-                         k_cache: torch.Tensor, v_cache: torch.Tensor, scale: float) -> torch.Tensor:
+                         k_cache: torch.Tensor, v_cache: torch.Tensor, scale: float,
+                         overlap: bool = True) -> torch.Tensor:
     """Store + attention of one layer for one step.
 
     ``q`` is ``[1, Hq, total, D]``, ``k``/``v`` ``[1, Hkv, total, D]`` after the rotary embedding (the tensors
@@ -124,34 +189,30 @@ def paged_attention_step(sc: StepContext, q: torch.Tensor, k: torch.Tensor, v: t
     ``[blocks, Hkv, B, D]`` pools.  Returns ``[1, total, Hq*D]`` like the reference's ``attn_out``
     (model_runner.py:210) — with one difference the reference's tests do not cover: a chunk with
     ``start_position > 0`` attends to the earlier chunks' keys in the pages as well.
+    In a mixed step the two attention kernels run side by side on two streams, each on its share of the SMs
+    (``overlap=False`` runs them in turn).
     """
     P, Dn = sc.num_prefill_tokens, sc.num_decode_tokens
     total = P + Dn
     _, hq, tq, d = q.shape
     if tq != total or k.size(2) != total or v.size(2) != total:
         raise RuntimeError("q/k/v token count does not match the step context")
-    bs = k_cache.size(2)
     out = torch.empty(total, hq, d, dtype=q.dtype, device=q.device)
     if P > 0:
         for i, (off, n) in enumerate(zip(sc.prefill_offsets, sc.prefill_tokens)):
             # the prompt's table row, read in place for every token of the chunk (stride-0 expand)
             paged_kernels.paged_kv_store(k_cache, v_cache, k[0, :, off:off + n], v[0, :, off:off + n],
                                          sc.prefill_tables[i:i + 1].expand(n, -1), sc.prefill_positions[off:off + n])
-        q_p = q[0, :, :P].transpose(0, 1).contiguous()
-        paged_kernels.paged_prefill_attention(out[:P], q_p, k_cache, v_cache, sc.prefill_tables,
-                                              sc.prefill_offsets, sc.prefill_tokens, sc.prefill_starts,
-                                              scale, bs, sc.prefill_tables.size(1))
     if Dn > 0:
         paged_kernels.paged_kv_store(k_cache, v_cache, k[0, :, P:], v[0, :, P:], sc.decode_tables, sc.decode_positions)
-        q_d = q[0, :, P:].transpose(0, 1).contiguous()
-        paged_kernels.paged_attention_forward(out[P:], q_d, k_cache, v_cache, sc.decode_tables, sc.decode_seq_lens,
-                                              scale, bs, sc.decode_tables.size(1))
+    _attend(sc, out, q[0].transpose(0, 1).contiguous(), k_cache, v_cache, scale, overlap)
     return out.view(1, total, hq * d)
 
 
 def paged_attention_step_fused(sc: StepContext, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                                cos: torch.Tensor, sin: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                               scale: float, q_norm_weight=None, k_norm_weight=None, eps: float = 1e-6) -> torch.Tensor:
+                               scale: float, q_norm_weight=None, k_norm_weight=None, eps: float = 1e-6,
+                               overlap: bool = True) -> torch.Tensor:
     """The same step starting one stage earlier: from the projection outputs.
 
     ``q`` ``[total, Hq, D]``, ``k``/``v`` ``[total, Hkv, D]`` are the token-major views of ``q_proj``/``k_proj``/
@@ -180,11 +241,5 @@ def paged_attention_step_fused(sc: StepContext, q: torch.Tensor, k: torch.Tensor
         paged_kernels.paged_qk_norm_rope_store(
             q[P:], k[P:], v[P:], cos[P:], sin[P:], k_cache, v_cache, sc.decode_tables, sc.decode_positions,
             q_norm_weight, k_norm_weight, eps, q_out=q_rot[P:])
-    if P > 0:
-        paged_kernels.paged_prefill_attention(out[:P], q_rot[:P], k_cache, v_cache, sc.prefill_tables,
-                                              sc.prefill_offsets, sc.prefill_tokens, sc.prefill_starts,
-                                              scale, bs, sc.prefill_tables.size(1))
-    if Dn > 0:
-        paged_kernels.paged_attention_forward(out[P:], q_rot[P:], k_cache, v_cache, sc.decode_tables,
-                                              sc.decode_seq_lens, scale, bs, sc.decode_tables.size(1))
+    _attend(sc, out, q_rot, k_cache, v_cache, scale, overlap)
     return out.view(1, total, hq * d)

@@ -224,7 +224,7 @@ def paged_qk_norm_rope_store(q, k, v, cos, sin, k_cache, v_cache, block_tables, 
 # ---------------------------------------------------------------------------
 def paged_attention_forward(out, query, key_cache, value_cache, block_tables, seq_lens,
                             scale: float, block_size: int, max_num_blocks_per_seq: int,
-                            _flags: int = 0) -> None:
+                            _flags: int = 0, max_ctas: int = 0) -> None:
     """``out[s, h] = softmax(scale * q[s, h] . K_s^T) . V_s`` over paged K/V, written in place.
 
     Same contract as the reference op (nanoPD/paged_attention/csrc/attention/paged_attention.h:24-34,
@@ -239,6 +239,9 @@ def paged_attention_forward(out, query, key_cache, value_cache, block_tables, se
     same name (csrc/paged_attention_optimized/paged_attention_optimized_ops.cu:33-34,
     tests/test_paged_kernels.py:39-56): a 5-D ``key_cache`` ``[blocks, Hkv, D/8, B, 8]`` goes with a
     ``value_cache`` ``[blocks, Hkv, D, B]``.
+
+    ``max_ctas`` (an addition, 0 = one CTA per SM) caps the persistent grid so that the call can share the GPU
+    with another kernel on a second stream (see ``paged_forward.paged_attention_step``).
     """
     _require(query.is_cuda, "query is must be on CUDA")
     _require(query.dim() == 3, "query must be [num seqs, num_heads, head_size]")
@@ -293,7 +296,8 @@ def paged_attention_forward(out, query, key_cache, value_cache, block_tables, se
             out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
             block_tables.data_ptr(), seq_lens.data_ptr(), float(scale),
             S, hq, hkv, d, bs, max_blk, nb, cstride, row_stride,
-            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(), int(_flags), handle))
+            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(),
+            int(_flags) | ((int(max_ctas) & 0xffff) << 8), handle))
 
 
 # ---------------------------------------------------------------------------
@@ -302,7 +306,7 @@ def paged_attention_forward(out, query, key_cache, value_cache, block_tables, se
 def paged_prefill_attention(out, query, key_cache, value_cache, block_tables,
                             chunk_q_offsets: Sequence[int], chunk_tokens: Sequence[int],
                             chunk_starts: Sequence[int], scale: float, block_size: int,
-                            max_num_blocks_per_seq: int, _flags: int = 0) -> None:
+                            max_num_blocks_per_seq: int, _flags: int = 0, max_ctas: int = 0) -> None:
     """Causal attention of prompt chunks over their paged K/V (the chunk's own rows included).
 
     Replaces the prefill branch of ``paged_forward`` (nanoPD/engine/model_runner.py:152-169).
@@ -343,7 +347,8 @@ def paged_prefill_attention(out, query, key_cache, value_cache, block_tables,
             out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
             block_tables.data_ptr(), arr(*chunk_q_offsets), arr(*chunk_tokens), arr(*chunk_starts),
             nchunks, float(scale), hq, hkv, d, bs, max_blk, nb, cstride, block_tables.stride(0),
-            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(), int(_flags), handle))
+            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(),
+            int(_flags) | ((int(max_ctas) & 0xffff) << 8), handle))
 
 
 # ---------------------------------------------------------------------------

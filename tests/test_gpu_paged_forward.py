@@ -133,3 +133,53 @@ def test_fused_step_equals_unfused_step_on_rotated_inputs(kernels):
     assert (kc1.float() - kc2.float()).abs().max().item() <= 2 ** -5          # one bf16 step at |x| < 8
     assert float((kc1 != kc2).float().mean()) < 0.01
     assert (got.float() - want.float()).abs().max().item() <= TOL[dtype]
+
+
+def test_mixed_step_on_two_streams_equals_the_step_in_turn(kernels, monkeypatch):
+    """The side-by-side launch of the two attention kernels (each on its share of the SMs) gives what running them
+    one after the other gives, and both match the oracle."""
+    monkeypatch.setattr(paged_forward, "_MIN_OVERLAP_SECONDS", 0.0)      # force the two-stream path at test size
+    torch.manual_seed(12)
+    dtype = torch.bfloat16
+    Hq, Hkv, D, B = 8, 2, 128, 16
+    n_chunk, start = 150, 310
+    dec_pos = [700, 33, 1500, 64, 255, 1023, 12, 480]
+    nblk_p = (start + n_chunk + B - 1) // B
+    nblk_d = [(p + 1 + B - 1) // B for p in dec_pos]
+    pool = nblk_p + sum(nblk_d) + 4
+    perm = torch.randperm(pool).tolist()
+    prefills = [{"block_table": perm[:nblk_p], "start_position": start, "num_tokens": n_chunk}]
+    decodes, o = [], nblk_p
+    for p_, n_ in zip(dec_pos, nblk_d):
+        decodes.append({"block_table": perm[o:o + n_], "position": p_})
+        o += n_
+    P, Dn = n_chunk, len(dec_pos)
+    ctx = {"num_prefill_tokens": P, "num_decode_tokens": Dn, "prefills": prefills, "decodes": decodes}
+    k_cache = torch.randn(pool, Hkv, B, D).to(dtype)
+    v_cache = torch.randn(pool, Hkv, B, D).to(dtype)
+    q = torch.randn(1, Hq, P + Dn, D).to(dtype)
+    k = torch.randn(1, Hkv, P + Dn, D).to(dtype)
+    v = torch.randn(1, Hkv, P + Dn, D).to(dtype)
+    scale = D ** -0.5
+    sc = paged_forward.build_step_context(ctx, DEV)
+    assert paged_forward._sm_split(sc, Hq, Hkv, D, 2, torch.device(DEV)) is not None
+    outs = []
+    for overlap in (False, True):
+        kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+        outs.append(paged_forward.paged_attention_step(sc, q.to(DEV), k.to(DEV), v.to(DEV), kc, vc, scale, overlap=overlap))
+        torch.cuda.synchronize()
+    assert torch.equal(outs[0][:, :P], outs[1][:, :P])                     # prompt rows: same kernel, same tiles
+    assert (outs[0].float() - outs[1].float()).abs().max().item() <= TOL[dtype]
+
+    kc_ref, vc_ref = k_cache.clone(), v_cache.clone()
+    bt = torch.tensor(prefills[0]["block_table"], dtype=torch.int32)
+    paged_oracle.kv_store(kc_ref, vc_ref, k[0, :, :P], v[0, :, :P], bt.unsqueeze(0).expand(P, -1),
+                          torch.arange(start, start + P, dtype=torch.int32))
+    sc_cpu = paged_forward.build_step_context(ctx, "cpu")
+    paged_oracle.kv_store(kc_ref, vc_ref, k[0, :, P:], v[0, :, P:], sc_cpu.decode_tables, sc_cpu.decode_positions)
+    want = torch.zeros(P + Dn, Hq, D)
+    want[:P] = paged_oracle.paged_prefill_attention(q[0, :, :P].transpose(0, 1), kc_ref, vc_ref, bt, start, scale)
+    want[P:] = paged_oracle.paged_decode_attention(q[0, :, P:].transpose(0, 1), kc_ref, vc_ref, sc_cpu.decode_tables,
+                                                   sc_cpu.decode_seq_lens, scale)
+    err = (outs[1].float().cpu().view(P + Dn, Hq, D) - want).abs().max().item()
+    assert err <= TOL[dtype], err
