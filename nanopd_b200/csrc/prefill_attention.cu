@@ -168,18 +168,6 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // the scarcest resource of the softmax).  x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic
 // (max relative error 1.0e-4, far below the rounding of P to a 16-bit type); n is added to the exponent
 // field.  x is clamped at -125 (result ~2e-38, i.e. 0 for every purpose here).
-__device__ __forceinline__ float2 exp2_poly_pair(float2 x) {
-    x.x = fmaxf(x.x, -125.f);
-    x.y = fmaxf(x.y, -125.f);
-    const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));          // low mantissa bits = n
-    const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
-    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-    float2 q = __ffma2_rn(make_float2(0.05583828f, 0.05583828f), f, make_float2(0.24263948f, 0.24263948f));
-    q = __ffma2_rn(q, f, make_float2(0.69313675f, 0.69313675f));
-    q = __ffma2_rn(q, f, make_float2(0.99992454f, 0.99992454f));
-    return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23)),
-                       __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23)));
-}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -695,17 +683,44 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) {
                     uint32_t packed[16];
+                    // The chunk's 16 pairs: the first kPolyPairsOf8 * 2 even-numbered ones take the polynomial on the
+                    // FMA pipes, stage by stage so that their dependent chains interleave; the others the SFU.
+                    constexpr int NP = kPolyPairsOf8 * 2;
+                    float2 xs[16];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float2 xs = __ffma2_rn(make_float2(sc[cc][i], sc[cc][i + 1]), scale2, negm2);
+                    for (int i = 0; i < 16; ++i)
+                        xs[i] = __ffma2_rn(make_float2(sc[cc][2 * i], sc[cc][2 * i + 1]), scale2, negm2);
+                    float2 pt[NP > 0 ? NP : 1], pf[NP > 0 ? NP : 1], pq[NP > 0 ? NP : 1];
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) {
+                        pf[j].x = fmaxf(xs[2 * j].x, -125.f);
+                        pf[j].y = fmaxf(xs[2 * j].y, -125.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) pt[j] = __fadd2_rn(pf[j], make_float2(12582912.f, 12582912.f));
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) pq[j] = __fadd2_rn(pt[j], make_float2(-12582912.f, -12582912.f));
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) pf[j] = __ffma2_rn(pq[j], make_float2(-1.f, -1.f), pf[j]);
+#pragma unroll
+                    for (int j = 0; j < NP; ++j)
+                        pq[j] = __ffma2_rn(make_float2(0.05583828f, 0.05583828f), pf[j], make_float2(0.24263948f, 0.24263948f));
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) pq[j] = __ffma2_rn(pq[j], pf[j], make_float2(0.69313675f, 0.69313675f));
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) pq[j] = __ffma2_rn(pq[j], pf[j], make_float2(0.99992454f, 0.99992454f));
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
                         float2 pr;
-                        if (((i >> 1) & 7) < kPolyPairsOf8) {   // compile-time pattern: some pairs avoid the SFU
-                            pr = exp2_poly_pair(xs);
+                        if ((i & 1) == 0 && (i >> 1) < NP) {
+                            const int j = i >> 1;
+                            pr = make_float2(__uint_as_float(__float_as_uint(pq[j].x) + (__float_as_uint(pt[j].x) << 23)),
+                                             __uint_as_float(__float_as_uint(pq[j].y) + (__float_as_uint(pt[j].y) << 23)));
                         } else {
-                            pr = make_float2(fast_exp2(xs.x), fast_exp2(xs.y));
+                            pr = make_float2(fast_exp2(xs[i].x), fast_exp2(xs[i].y));
                         }
-                        acc2[(i >> 1) & 1] = __fadd2_rn(acc2[(i >> 1) & 1], pr);
-                        packed[i >> 1] = Elem<T>::pack2(pr.x, pr.y);
+                        acc2[i & 1] = __fadd2_rn(acc2[i & 1], pr);
+                        packed[i] = Elem<T>::pack2(pr.x, pr.y);
                     }
                     tmem_st16(t_sx + cc * 16, packed);
                     if (cc == 1) {               // first 64 keys done: their PV MMAs may start
