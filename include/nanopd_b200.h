@@ -110,7 +110,7 @@ int npd_paged_decode_attention(void *out, const void *q, const void *k_cache,
  * a worker whose HBM went entirely to the KV pool and weights at start-up, a step loop
  * that forbids allocation after initialisation, a foreign runtime binding this ABI with no
  * device allocator (cudaMalloc/cudaFree would also stall the whole device).  The scratch is a
- * 20 MiB device array inside the library image (npd_decode_static_scratch_bytes()); every
+ * 32 MiB device array inside the library image (npd_decode_static_scratch_bytes()); every
  * GPU that loads the library holds it until the process exits.  The call allocates and
  * frees nothing.  Shapes whose scratch need (npd_decode_workspace_bytes) exceeds the array
  * are refused with NPD_ERR_WORKSPACE; on a B200 every supported shape fits.

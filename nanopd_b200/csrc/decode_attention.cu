@@ -333,7 +333,10 @@ __device__ __forceinline__ void merge_partials(AttnState<T, D, NT> &st, const De
 // and feeds ldmatrix directly (8 tokens of one piece are 128 contiguous bytes), a V tile lands as [d][token] and is
 // already the A operand of O^T = V^T . P^T, so it is read without the transposing ldmatrix.
 template <typename T, int D, int NT, bool IL>
-__global__ void __launch_bounds__(256, 1)
+#ifndef NPD_DECODE_MAX_WARPS
+#define NPD_DECODE_MAX_WARPS 12
+#endif
+__global__ void __launch_bounds__(NPD_DECODE_MAX_WARPS * 32, 1)
 paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v) {
     constexpr int NH = D / 64;
@@ -550,20 +553,26 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
                     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, d));
                 }
                 const float mn0 = fmaxf(st.m[nt][0], mx0), mn1 = fmaxf(st.m[nt][1], mx1);
-                const float a0 = fast_exp2(st.m[nt][0] - mn0), a1 = fast_exp2(st.m[nt][1] - mn1);
                 const float p0 = fast_exp2(x0 - mn0), p1 = fast_exp2(x1 - mn1);
                 const float p2 = fast_exp2(x2 - mn0), p3 = fast_exp2(x3 - mn1);
-                st.l[nt][0] = st.l[nt][0] * a0 + p0 + p2;
-                st.l[nt][1] = st.l[nt][1] * a1 + p1 + p3;
-                st.m[nt][0] = mn0;
-                st.m[nt][1] = mn1;
+                // O and l are rescaled only in tiles where some head's maximum grew (warp-uniform test): deep
+                // into a sequence that is the exception, and the 4*KS multiplies are the bulk of the softmax code
+                if (__any_sync(0xffffffffu, mn0 != st.m[nt][0] || mn1 != st.m[nt][1])) {
+                    const float a0 = fast_exp2(st.m[nt][0] - mn0), a1 = fast_exp2(st.m[nt][1] - mn1);
+                    st.l[nt][0] *= a0;
+                    st.l[nt][1] *= a1;
+                    st.m[nt][0] = mn0;
+                    st.m[nt][1] = mn1;
 #pragma unroll
-                for (int j = 0; j < KS; ++j) {
-                    st.o[nt][j][0] *= a0;
-                    st.o[nt][j][1] *= a1;
-                    st.o[nt][j][2] *= a0;
-                    st.o[nt][j][3] *= a1;
+                    for (int j = 0; j < KS; ++j) {
+                        st.o[nt][j][0] *= a0;
+                        st.o[nt][j][1] *= a1;
+                        st.o[nt][j][2] *= a0;
+                        st.o[nt][j][3] *= a1;
+                    }
                 }
+                st.l[nt][0] += p0 + p2;
+                st.l[nt][1] += p1 + p3;
                 pb[nt][0] = movmatrix_trans(Elem<T>::pack2(p0, p1));
                 pb[nt][1] = movmatrix_trans(Elem<T>::pack2(p2, p3));
             }
@@ -646,15 +655,31 @@ int env_int(const char *name, int fallback) {
     return x > 0 ? x : fallback;
 }
 
-LaunchShape launch_shape(int head_dim, int device) {
+// Warps per CTA and ring depth.  A warp is bound by the latency of its own instruction chain (a tile every
+// ~1.4 us), so the SM's bandwidth comes from the number of warps, not from deeper rings: two stages do as well as
+// three.  Measured on a B200 (microseconds per launch; configuration 2 unless noted):
+//   D=128, full grid:   8 warps 238-240, 12 warps 249 (more request streams than HBM serves well)
+//   D=128, 100 CTAs:    8 warps 323,     12 warps 243 -> a capped grid (a mixed step sharing the SMs) takes 12
+//   D=128, block 8:     8 warps 263,     12 warps 235
+//   D=64:               8 warps 107,     12 warps 81
+//   D=256:              4 warps x 3 stages 135, 8 warps x 1 stage 122
+//   D=128, one sequence of 8k / 64k tokens: 3 stages 29 / 76, 2 stages 36 / 86
+LaunchShape launch_shape(int head_dim, int block_size, int cta_cap, long long num_seq_heads, int device) {
     LaunchShape ls;
     const int stage_bytes = 2 * kTile * head_dim * 2;
-    ls.nwarps = env_int("NPD_DECODE_WARPS", head_dim == 256 ? 4 : 8);
-    if (ls.nwarps > 8) ls.nwarps = 8;   // the kernel is compiled for at most 256 threads
-    int nst = env_int("NPD_DECODE_STAGES", head_dim == 64 ? 4 : 3);
+    const int sms = npd::sm_count(device);
+    ls.grid = env_int("NPD_DECODE_CTAS", sms);
+    if (cta_cap > 0 && cta_cap < ls.grid) ls.grid = cta_cap;
+    int warps = 8, stages = 2;
+    if (head_dim == 256) stages = 1;
+    // a handful of long sequences: every worker has few tiles and the launch is latency-bound, a deeper ring helps
+    if (head_dim == 128 && num_seq_heads < 64) stages = 3;
+    if (head_dim == 64 || (head_dim == 128 && (block_size < 16 || ls.grid * 100 < sms * 85))) warps = 12;
+    ls.nwarps = env_int("NPD_DECODE_WARPS", warps);
+    if (ls.nwarps > NPD_DECODE_MAX_WARPS) ls.nwarps = NPD_DECODE_MAX_WARPS;   // the kernel's launch bound
+    int nst = env_int("NPD_DECODE_STAGES", stages);
     while (nst > 1 && (long long)ls.nwarps * nst * stage_bytes > 192 * 1024) --nst;
     ls.nstages = nst;
-    ls.grid = env_int("NPD_DECODE_CTAS", npd::sm_count(device));
     return ls;
 }
 
@@ -718,8 +743,8 @@ extern "C" size_t npd_decode_workspace_bytes(int64_t num_seqs, int64_t num_q_hea
                                              int64_t head_dim, int device) {
     if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
     // Sized for the largest grid/warp shape the launcher may pick, so tuning knobs never outgrow it.
-    LaunchShape ls = launch_shape(static_cast<int>(head_dim), device);
-    if (ls.nwarps < 8) ls.nwarps = 8;
+    LaunchShape ls = launch_shape(static_cast<int>(head_dim), 16, 0, 1 << 20, device);
+    if (ls.nwarps < NPD_DECODE_MAX_WARPS) ls.nwarps = NPD_DECODE_MAX_WARPS;
     return plan_workspace(num_seqs, num_q_heads, num_kv_heads, head_dim, ls).total;
 }
 
@@ -754,9 +779,8 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
 
     int dev = 0;
     NPD_CUDA_TRY(cudaGetDevice(&dev));
-    LaunchShape ls = launch_shape(static_cast<int>(head_dim), dev);
-    const int cta_cap = (flags >> 8) & 0xffff;
-    if (cta_cap > 0 && cta_cap < ls.grid) ls.grid = cta_cap;
+    const LaunchShape ls = launch_shape(static_cast<int>(head_dim), static_cast<int>(block_size), (flags >> 8) & 0xffff,
+                                        (long long)num_seqs * num_kv_heads, dev);
     const WorkspacePlan wp = plan_workspace(num_seqs, num_q_heads, num_kv_heads, head_dim, ls);
     NPD_REQUIRE(workspace != nullptr && workspace_bytes >= wp.total, NPD_ERR_WORKSPACE,
                 "decode attention: workspace of %zu bytes given, %zu needed", workspace_bytes, wp.total);
@@ -842,9 +866,9 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
 // after initialisation" rule, or a foreign-language runtime binding the C ABI without a device
 // allocator of its own (and cudaMalloc / cudaFree would stall every stream of the device
 // anyway).  For them the scratch below is part of the library image: every GPU that loads the
-// library holds these 20 MiB until the process exits.  It is large enough for every supported
-// shape on a B200 (148 SMs x 8 workers x 2 partial records of at most 8320 B, plus the header).
-#define NPD_STATIC_SCRATCH_BYTES (20u << 20)
+// library holds these 32 MiB until the process exits.  It is large enough for every supported
+// shape on a B200 (148 SMs x 12 workers x 2 partial records of at most 8320 B, plus the ticket region and header).
+#define NPD_STATIC_SCRATCH_BYTES (32u << 20)
 static __device__ __align__(256) unsigned char g_decode_static_scratch[NPD_STATIC_SCRATCH_BYTES];
 
 namespace {
