@@ -272,7 +272,7 @@ def run_prefill_workload(args, paged_kernels, dev, timed):
         decode_context_tokens=int(seq_lens.sum().item()))
     q_all = torch.cat([q2, d.query]).contiguous()
     out_all = torch.empty_like(q_all)
-    sm_share = paged_forward._sm_split(sc, Hq, d.num_kv_heads, D, 2, dev)
+    sm_share = paged_forward._sm_split(sc, Hq, d.num_kv_heads, D, 2, torch.cuda.get_device_properties(dev).multi_processor_count)
 
     def mixed_step_overlapped():
         paged_kernels.paged_kv_store(d.k_cache, d.v_cache, d.k_new, d.v_new, d.block_tables, d.positions)

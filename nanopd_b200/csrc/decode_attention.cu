@@ -332,11 +332,13 @@ __device__ __forceinline__ void merge_partials(AttnState<T, D, NT> &st, const De
 // [blocks, Hkv, D, B]; csrc/paged_attention_optimized/index.h:14-31,60-75): a K tile lands as [d piece][token][8]
 // and feeds ldmatrix directly (8 tokens of one piece are 128 contiguous bytes), a V tile lands as [d][token] and is
 // already the A operand of O^T = V^T . P^T, so it is read without the transposing ldmatrix.
-template <typename T, int D, int NT, bool IL>
+// MAXW (8 or 12) is the launch bound in warps: the 8-warp instances keep the whole register file for the merge
+// of split sequences (four records' loads in flight), the 12-warp instances trade that for more warps.
 #ifndef NPD_DECODE_MAX_WARPS
 #define NPD_DECODE_MAX_WARPS 12
 #endif
-__global__ void __launch_bounds__(NPD_DECODE_MAX_WARPS * 32, 1)
+template <typename T, int D, int NT, bool IL, int MAXW>
+__global__ void __launch_bounds__(MAXW * 32, 1)
 paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v) {
     constexpr int NH = D / 64;
@@ -697,9 +699,15 @@ int launch_decode(const DecodeParams &p, const CUtensorMap &tk, const CUtensorMa
                   cudaStream_t stream) {
     constexpr int STAGE_BYTES = 2 * kTile * D * 2;
     const size_t smem = 1024 + (size_t)ls.nwarps * ls.nstages * (STAGE_BYTES + 8) + ((size_t)p.num_seqs + 1) * 4 + 16;
-    auto kern = paged_decode_stream_kernel<T, D, NT, IL>;
-    NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<ls.grid, ls.nwarps * 32, smem, stream>>>(p, tk, tv);
+    if (ls.nwarps <= 8) {
+        auto kern = paged_decode_stream_kernel<T, D, NT, IL, 8>;
+        NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<ls.grid, ls.nwarps * 32, smem, stream>>>(p, tk, tv);
+    } else {
+        auto kern = paged_decode_stream_kernel<T, D, NT, IL, NPD_DECODE_MAX_WARPS>;
+        NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<ls.grid, ls.nwarps * 32, smem, stream>>>(p, tk, tv);
+    }
     NPD_CUDA_TRY(cudaGetLastError());
     return NPD_OK;
 }

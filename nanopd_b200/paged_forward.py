@@ -130,11 +130,11 @@ _MIN_OVERLAP_SECONDS = 15e-6       # below this much estimated work on either si
 _side_streams: Dict[int, "torch.cuda.Stream"] = {}
 
 
-def _sm_split(sc: StepContext, hq: int, hkv: int, d: int, elem: int, device) -> Optional[int]:
-    """SMs for the prompt chunks in a mixed step (the rest go to the decode batch); None = run them in turn."""
-    if sc.num_prefill_tokens == 0 or sc.num_decode_tokens == 0:
+def _sm_split(sc: StepContext, hq: int, hkv: int, d: int, elem: int, sms: int) -> Optional[int]:
+    """Of ``sms`` SMs, how many the prompt chunks get in a mixed step (the rest go to the decode batch);
+    None = run the two kernels in turn."""
+    if sc.num_prefill_tokens == 0 or sc.num_decode_tokens == 0 or sms < 64:
         return None
-    sms = torch.cuda.get_device_properties(device).multi_processor_count
     t_p = 4.0 * hq * d * sc.prefill_score_pairs / _PREFILL_FLOPS_PER_S
     t_d = 2.0 * hkv * d * elem * sc.decode_context_tokens / _DECODE_BYTES_PER_S
     if min(t_p, t_d) < _MIN_OVERLAP_SECONDS:
@@ -158,7 +158,8 @@ def _attend(sc: StepContext, out, q_tokens_major, k_cache, v_cache, scale, overl
     bs = k_cache.size(2)
     _, hq, d = q_tokens_major.shape
     dev = q_tokens_major.device
-    share = _sm_split(sc, hq, k_cache.size(1), d, q_tokens_major.element_size(), dev) if overlap else None
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    share = _sm_split(sc, hq, k_cache.size(1), d, q_tokens_major.element_size(), sms) if overlap else None
 
     def prefill(max_ctas=0):
         paged_kernels.paged_prefill_attention(out[:P], q_tokens_major[:P], k_cache, v_cache, sc.prefill_tables,
@@ -176,7 +177,6 @@ def _attend(sc: StepContext, out, q_tokens_major, k_cache, v_cache, scale, overl
         if Dn > 0:
             decode()
         return
-    sms = torch.cuda.get_device_properties(dev).multi_processor_count
     main = torch.cuda.current_stream(dev)
     side = _side_streams.get(dev.index)
     if side is None:

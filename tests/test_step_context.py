@@ -56,3 +56,24 @@ def test_inconsistent_contexts_raise():
         paged_forward.build_step_context({"num_prefill_tokens": 20, "num_decode_tokens": 0,
                                           "prefills": [{"block_table": [0], "start_position": 0, "num_tokens": 20}],
                                           "decodes": []}, "cpu")
+
+
+def _ctx(chunk_tokens, chunk_start, decode_positions):
+    prefills = [{"block_table": list(range(400)), "start_position": chunk_start, "num_tokens": chunk_tokens}] if chunk_tokens else []
+    decodes = [{"block_table": list(range(400)), "position": p} for p in decode_positions]
+    return {"num_prefill_tokens": chunk_tokens, "num_decode_tokens": len(decodes), "prefills": prefills, "decodes": decodes}
+
+
+def test_sm_split_of_a_mixed_step():
+    split = lambda ctx: paged_forward._sm_split(paged_forward.build_step_context(ctx, "cpu"), 32, 8, 128, 2, 148)
+    assert split(_ctx(0, 0, [1000] * 64)) is None                     # decode only
+    assert split(_ctx(512, 2048, [])) is None                         # prefill only
+    assert split(_ctx(16, 0, [5] * 4)) is None                        # too little work to pay for a fork and join
+    # configuration 3's shape: a 512-token chunk deep into its prompt + 128 long decode sequences
+    share = split(_ctx(512, 2048, [2200] * 128))
+    assert share is not None and 16 <= share <= 148 - 32
+    assert 148 - share >= 100                                         # decode keeps enough SMs to stay HBM-bound
+    # more prompt work moves SMs to the chunk kernel, never the other way
+    shares = [split(_ctx(512, start, [2200] * 128)) for start in (2048, 4096, 5600)]
+    assert shares == sorted(shares)
+    assert paged_forward._sm_split(paged_forward.build_step_context(_ctx(512, 2048, [2200] * 128), "cpu"), 32, 8, 128, 2, 32) is None
