@@ -70,8 +70,6 @@ struct PrefillParams {
     int max_blocks_per_seq;
     int num_blocks;
     long long bt_row_stride;
-    int debug_flags;        // only read when built with -DNPD_PREFILL_EXPERIMENTS (timing experiments that give
-                            // wrong results): 1 = skip softmax math, 2 = skip MMA issue, 4 = skip K/V loads
     int chunk_q_offset[kMaxChunks];
     int chunk_tokens[kMaxChunks];
     int chunk_start[kMaxChunks];
@@ -203,12 +201,6 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     }
     return true;
 }
-
-#ifdef NPD_PREFILL_EXPERIMENTS
-#define NPD_EXPERIMENT_FLAGS(p) ((p).debug_flags)
-#else
-#define NPD_EXPERIMENT_FLAGS(p) 0
-#endif
 
 // Optional phase tracing for performance work (compiled out unless NPD_PREFILL_TRACE is defined):
 // the CTA with blockIdx.x == 0 appends (tag, key tile, clock) triples to the workspace after its header.
@@ -421,11 +413,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (!__all_sync(0xffffffffu, ok)) break;
                 if (lane == 0) {
                     NPD_TRACE(0, 1, t);
-                    if (NPD_EXPERIMENT_FLAGS(p) & 4) mbar_arrive(smem_u32(&ctrl->k_full[stage]));
-                    else mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
+                    mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (!(NPD_EXPERIMENT_FLAGS(p) & 4) && role == 0 && gi < ngroups)
+                if (role == 0 && gi < ngroups)
                     tma_load_3d(smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
                                 hf * 64, row, id);
                 if (t == 0 && !(ok = load_q(1))) break;
@@ -433,11 +424,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
                 if (!__all_sync(0xffffffffu, ok)) break;
                 if (lane == 0) {
-                    if (NPD_EXPERIMENT_FLAGS(p) & 4) mbar_arrive(smem_u32(&ctrl->v_full[stage]));
-                    else mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
+                    mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (!(NPD_EXPERIMENT_FLAGS(p) & 4) && role == 1 && gi < ngroups)
+                if (role == 1 && gi < ngroups)
                     tma_load_3d(smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
                                 hf * 64, row, id);
             }
@@ -474,7 +464,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kD / 16; ++ks) {
-                        if (NPD_EXPERIMENT_FLAGS(p) & 2) break;
                         const uint64_t a_off = static_cast<uint64_t>(((ks >> 2) * kQHalfBytes + (ks & 3) * 32) >> 4);
                         const uint64_t b_off = static_cast<uint64_t>(((ks >> 2) * kKvHalfBytes + (ks & 3) * 32) >> 4);
                         tc_mma_ss(t_sx, q_desc + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
@@ -491,9 +480,8 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = half * (kKeys / 32); ks < (half + 1) * (kKeys / 32); ++ks)
-                        if (!(NPD_EXPERIMENT_FLAGS(p) & 2))
-                            tc_mma_ts(t_o, t_sx + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
-                                      (!first || ks > 0) ? 1u : 0u);
+                        tc_mma_ts(t_o, t_sx + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
+                                  (!first || ks > 0) ? 1u : 0u);
                     if (last && half == 1) tc_commit(smem_u32(&ctrl->o_full[x]));
                 }
                 __syncwarp();
@@ -622,13 +610,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 for (int cc = 0; cc < 4; ++cc) tmem_ld32(t_sx + cc * 32, sc[cc]);
                 tmem_wait_ld();
                 if (lane == 0) NPD_TRACE_FINE(sm_role, 22, t);
-                if (NPD_EXPERIMENT_FLAGS(p) & 1) {
-                    tc_fence_before();
-                    mbar_arrive(smem_u32(&ctrl->p_half[x]));
-                    mbar_arrive(smem_u32(&ctrl->p_full[x]));
-                    l_run = 1.f;
-                    continue;
-                }
                 if (key0 + kKeys - 1 > it.start + it.tok0[x]) {  // only tiles that reach past the first row's diagonal
 #pragma unroll
                     for (int cc = 0; cc < 4; ++cc)
@@ -875,7 +856,6 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
         p.num_blocks = static_cast<int>(num_blocks);
         p.bt_row_stride = bt_row_stride;
-        p.debug_flags = flags & 0xff;
 #ifdef NPD_PREFILL_TRACE
         p.trace = workspace_bytes >= 256 + 11 * 4096 * sizeof(long long)
                       ? reinterpret_cast<long long *>(static_cast<uint8_t *>(workspace) + 256) : nullptr;

@@ -183,3 +183,44 @@ def test_mixed_step_on_two_streams_equals_the_step_in_turn(kernels, monkeypatch)
                                                    sc_cpu.decode_seq_lens, scale)
     err = (outs[1].float().cpu().view(P + Dn, Hq, D) - want).abs().max().item()
     assert err <= TOL[dtype], err
+
+
+def test_prefill_in_the_same_step_does_not_change_the_decode_rows(kernels):
+    """The reference's engine test asks that a mixed batch leaves the decode tokens unchanged
+    (nanoPD/engine/test/test_mixed_batch.py:10-30).  Here: the decode rows of a mixed step, run in turn, equal the
+    rows of the same decode batch stepped alone, bit for bit; with the two kernels side by side (another split of
+    the decode work) they agree within the attention tolerance."""
+    torch.manual_seed(21)
+    dtype = torch.float16
+    Hq, Hkv, D, B, pool = 12, 2, 128, 16, 40
+    perm = torch.randperm(pool).tolist()
+    decodes = [{"block_table": perm[0:6], "position": 90}, {"block_table": perm[6:7], "position": 7},
+               {"block_table": perm[7:17], "position": 150}]
+    prefills = [{"block_table": perm[17:25], "start_position": 32, "num_tokens": 70}]
+    Dn, P = len(decodes), 70
+    k_cache = torch.randn(pool, Hkv, B, D).to(dtype)
+    v_cache = torch.randn(pool, Hkv, B, D).to(dtype)
+    q_d, k_d, v_d = (torch.randn(1, h, Dn, D).to(dtype) for h in (Hq, Hkv, Hkv))
+    q_p, k_p, v_p = (torch.randn(1, h, P, D).to(dtype) for h in (Hq, Hkv, Hkv))
+    scale = D ** -0.5
+
+    def run(ctx, q, k, v, overlap):
+        sc = paged_forward.build_step_context(ctx, DEV)
+        kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+        out = paged_forward.paged_attention_step(sc, q.to(DEV), k.to(DEV), v.to(DEV), kc, vc, scale, overlap=overlap)
+        torch.cuda.synchronize()
+        return out[0].cpu()
+
+    alone = run({"num_prefill_tokens": 0, "num_decode_tokens": Dn, "prefills": [], "decodes": decodes}, q_d, k_d, v_d, False)
+    mixed_ctx = {"num_prefill_tokens": P, "num_decode_tokens": Dn, "prefills": prefills, "decodes": decodes}
+    cat = lambda a, b: torch.cat((a, b), dim=2)
+    in_turn = run(mixed_ctx, cat(q_p, q_d), cat(k_p, k_d), cat(v_p, v_d), False)
+    assert torch.equal(in_turn[P:], alone)
+    prev = paged_forward._MIN_OVERLAP_SECONDS
+    paged_forward._MIN_OVERLAP_SECONDS = 0.0
+    try:
+        side_by_side = run(mixed_ctx, cat(q_p, q_d), cat(k_p, k_d), cat(v_p, v_d), True)
+    finally:
+        paged_forward._MIN_OVERLAP_SECONDS = prev
+    assert torch.equal(side_by_side[:P], in_turn[:P])
+    assert (side_by_side[P:].float() - alone.float()).abs().max().item() <= TOL[dtype]
