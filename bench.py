@@ -293,6 +293,81 @@ def run_prefill_workload(args, paged_kernels, dev, timed):
             "mixed_step_two_streams_ms": round(ms_mixed_overlapped, 4), "prefill_sm_share": sm_share,
             "mixed_step": "last 512-token chunk of each of 4 prompts + store + decode attention of 128 sequences"}
 
+def run_model_tables(args, dev, timed):
+    """The reference's model-level timing tables (nanoPD/cost_model/record_no_kvstorekernel_naive_pagedattention.txt:
+    T_decode(kv_len, batch), T_prefill(L), extra decode latency from a co-scheduled prompt chunk; measured there
+    on an RTX 4090 with real Qwen3-8B weights) on the random-init stack of the same shape around this library."""
+    import numpy as np
+    from nanopd_b200 import decoder_step
+    free, _ = torch.cuda.mem_get_info(dev)
+    if free < 60 * (1 << 30):
+        return {"skipped": f"only {free >> 30} GiB free on the device"}
+    shape = decoder_step.DecoderShape()
+    B, pool_blocks = 16, 6144
+    model = decoder_step.SyntheticDecoder(dev, shape, torch.bfloat16, seed=args.seed, max_position=4096)
+    k_cache = torch.empty(shape.num_layers, pool_blocks, shape.num_kv_heads, B, shape.head_dim, dtype=torch.bfloat16, device=dev)
+    v_cache = torch.empty_like(k_cache)
+    for li in range(shape.num_layers):
+        k_cache[li].normal_()
+        v_cache[li].normal_()
+    rng = np.random.default_rng(args.seed)
+
+    def tables_for(batch, kv_len, headroom=16):
+        nblk = (kv_len + headroom + B - 1) // B
+        perm = rng.permutation(pool_blocks)[:batch * nblk].astype(np.int32).reshape(batch, nblk)
+        return perm
+
+    t_decode = {}
+    for batch in (1, 4, 8, 16, 32):
+        for kv in (128, 512, 1024, 2048):
+            tb = torch.from_numpy(tables_for(batch, kv)).to(dev)
+            ctx = torch.full((batch,), kv, dtype=torch.int32, device=dev)
+            model.attach_batch(k_cache, v_cache, tb, ctx, torch.randint(0, shape.vocab, (batch,), device=dev))
+            model.capture()
+            model.replay()
+            t_decode[f"B{batch}_kv{kv}"] = round(timed(model.replay, 5), 3)
+    t_prefill = {}
+    for L in (64, 128, 256, 512, 1024, 2048):
+        table = tables_for(1, L, 0)[0].tolist()
+        ctx = {"num_prefill_tokens": L, "num_decode_tokens": 0, "decodes": [],
+               "prefills": [{"block_table": table, "start_position": 0, "num_tokens": L}]}
+        toks = torch.randint(0, shape.vocab, (L,), device=dev)
+        fn = lambda: model.mixed_step(ctx, toks, k_cache, v_cache)
+        fn()
+        t_prefill[f"L{L}"] = round(timed(fn, 3), 3)
+    interference = {}
+    for batch in (4, 16):
+        kv = 1024
+        tb = tables_for(batch, kv)
+        decodes = [{"block_table": tb[i].tolist(), "position": kv} for i in range(batch)]
+        d_ctx = {"num_prefill_tokens": 0, "num_decode_tokens": batch, "prefills": [], "decodes": decodes}
+        d_toks = torch.randint(0, shape.vocab, (batch,), device=dev)
+        fn_d = lambda: model.mixed_step(d_ctx, d_toks, k_cache, v_cache)
+        fn_d()
+        base = timed(fn_d, 3)
+        for chunk in (64, 128, 256, 512):
+            table = tables_for(1, chunk, 0)[0].tolist()
+            m_ctx = {"num_prefill_tokens": chunk, "num_decode_tokens": batch, "decodes": decodes,
+                     "prefills": [{"block_table": table, "start_position": 0, "num_tokens": chunk}]}
+            m_toks = torch.randint(0, shape.vocab, (chunk + batch,), device=dev)
+            fn_m = lambda: model.mixed_step(m_ctx, m_toks, k_cache, v_cache)
+            fn_m()
+            interference[f"B{batch}_chunk{chunk}"] = round(timed(fn_m, 3) - base, 3)
+        interference[f"B{batch}_decode_only_eager_ms"] = round(base, 3)
+    import paged_kernels
+    status = paged_kernels.check_status(dev, raise_on_error=False)
+    del model, k_cache, v_cache
+    torch.cuda.empty_cache()
+    return {"model": "Qwen3-8B shape, random init, bf16", "unit": "ms per step",
+            "t_decode_graph": t_decode, "t_prefill_eager": t_prefill, "extra_decode_ms_from_prompt_chunk": interference,
+            "reference_rtx4090_fp16_ms": {
+                "source": "nanoPD/cost_model/record_no_kvstorekernel_naive_pagedattention.txt:5-88 (other hardware, real weights)",
+                "t_decode": {"B1_kv128": 49.0, "B1_kv2048": 64.3, "B8_kv1024": 83.9, "B32_kv128": 192.2, "B32_kv2048": 226.7},
+                "t_prefill": {"L64": 218, "L128": 394, "L256": 742, "L512": 1442, "L1024": 2847, "L2048": 5641},
+                "extra_decode_ms_from_prompt_chunk": {"chunk64": 179, "chunk128": 352, "chunk256": 702, "chunk512": 1400}},
+            "device_status": status}
+
+
 def run_model_workload(args, dev, timed, batch, seed):
     """Decode tokens/s at model level: a random-init stack of Qwen3-8B shape (36 layers) around the paged kernels,
     configuration 2's batch (256 sequences, lognormal contexts) in a 36-layer pool, every step one token per
@@ -377,6 +452,15 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
         replicas.barrier()
         return e0.elapsed_time(e1) / n
+
+    if args.workload == "model-tables":
+        res = run_model_tables(args, dev, timed)
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"workload": "model-level timing tables (secondary, not the headline metric)", **res}), flush=True)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return 0
 
     if args.workload == "model":
         res = run_model_workload(args, dev, timed, args.batch, args.seed)
@@ -641,7 +725,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--workload", choices=["decode", "prefill", "model"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "model", "model-tables"], default="decode",
                     help="decode = the headline configuration 2 (default); prefill = configuration 3's chunked prefill")
     ap.add_argument("--profile", action="store_true",
                     help="only warm up and run the timed step loop (for short ncu captures); prints no bench line")

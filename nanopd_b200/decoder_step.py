@@ -165,3 +165,42 @@ class SyntheticDecoder:
     def launches_per_step(self) -> int:
         """This library's kernels per step: one fused norm/rotary/store and one attention launch per layer."""
         return 2 * self.shape.num_layers
+
+    # ---- one scheduler step with prompt chunks and decode sequences -----------------------------------------
+    def mixed_step(self, ctx: dict, token_ids: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   overlap: bool = True) -> torch.Tensor:
+        """Runs the scheduler's step ``ctx`` (the reference's context dict, nanoPD/engine/engine.py:68-90) through
+        all layers: ``token_ids`` int64 ``[num_prefill_tokens + num_decode_tokens]`` are the packed prompt-chunk
+        tokens followed by one token per decode sequence, ``k_cache``/``v_cache`` the ``[L, blocks, Hkv, B, D]``
+        pools.  Tables and positions go to the device once (``build_step_context``); every layer then runs the
+        fused norm/rotary/store launches and the two attention kernels (side by side in a mixed step).  Returns
+        the logits of the last token of every prompt chunk followed by those of the decode sequences, as the
+        reference samples them (nanoPD/engine/engine.py:96-108).  Eager: the chunk lists are host data."""
+        from . import paged_forward
+        s = self.shape
+        sc = paged_forward.build_step_context(ctx, self.device, block_size=k_cache.size(3))
+        total = sc.num_prefill_tokens + sc.num_decode_tokens
+        if token_ids.numel() != total:
+            raise RuntimeError("token_ids does not match the step's token count")
+        pos_parts = [t for t in (sc.prefill_positions, sc.decode_positions) if t is not None]
+        positions = torch.cat(pos_parts) if len(pos_parts) > 1 else pos_parts[0]
+        cos = self.cos_table.index_select(0, positions)
+        sin = self.sin_table.index_select(0, positions)
+        hq_d, hkv_d = s.num_q_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        x = self.embed.index_select(0, token_ids)
+        for li, L in enumerate(self.layers):
+            h = F.rms_norm(x, (s.hidden,), L["in_norm"], s.eps)
+            qkv = F.linear(h, L["w_qkv"])
+            q = qkv[:, :hq_d].view(total, s.num_q_heads, s.head_dim)
+            k = qkv[:, hq_d:hq_d + hkv_d].view(total, s.num_kv_heads, s.head_dim)
+            v = qkv[:, hq_d + hkv_d:].view(total, s.num_kv_heads, s.head_dim)
+            attn = paged_forward.paged_attention_step_fused(sc, q, k, v, cos, sin, k_cache[li], v_cache[li], self.scale,
+                                                            L["q_norm"], L["k_norm"], s.eps, overlap=overlap)
+            x = x + F.linear(attn.view(total, hq_d), L["w_o"])
+            h = F.rms_norm(x, (s.hidden,), L["post_norm"], s.eps)
+            gu = F.linear(h, L["w_gate_up"])
+            x = x + F.linear(F.silu(gu[:, :s.ffn]) * gu[:, s.ffn:], L["w_down"])
+        last_rows = [off + n - 1 for off, n in zip(sc.prefill_offsets, sc.prefill_tokens)]
+        last_rows += list(range(sc.num_prefill_tokens, total))
+        rows = torch.tensor(last_rows, dtype=torch.int64, device=self.device)
+        return F.linear(F.rms_norm(x.index_select(0, rows), (s.hidden,), self.final_norm, s.eps), self.lm_head)

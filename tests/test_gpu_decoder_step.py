@@ -13,7 +13,12 @@ SHAPE = decoder_step.DecoderShape(num_layers=2, hidden=256, ffn=512, vocab=1000,
                                   head_dim=64, rope_theta=1e4)
 
 
-def make_batch(dtype, steps_ahead=4, seed=0):
+SHAPE128 = decoder_step.DecoderShape(num_layers=2, hidden=256, ffn=512, vocab=1000, num_q_heads=4, num_kv_heads=2,
+                                     head_dim=128, rope_theta=1e4)     # the chunked-prefill kernel takes head_dim 128
+
+
+def make_batch(dtype, steps_ahead=4, seed=0, shape=SHAPE):
+    SHAPE = shape
     torch.manual_seed(seed)
     B = 16
     ctx = torch.tensor([5, 31, 16, 70], dtype=torch.int32)
@@ -94,3 +99,43 @@ def test_graph_replays_equal_eager_steps(kernels):
     assert torch.equal(model.k_cache, kc_eager)
     assert torch.equal(model.positions.cpu(), ctx + 3)
     assert model.launches_per_step() == 2 * SHAPE.num_layers
+
+
+def test_mixed_step_decode_rows_equal_the_decode_only_step(kernels):
+    """A step with a prompt chunk next to the decode batch gives the decode sequences the logits the decode-only
+    step gives them, and a prompt processed in two chunks ends in the same logits as in one."""
+    dtype = torch.bfloat16
+    model = decoder_step.SyntheticDecoder(DEV, SHAPE128, dtype, seed=4, max_position=512)
+    kc, vc, tables, ctx, tokens = make_batch(dtype, seed=5, shape=SHAPE128)
+    B = 16
+    decodes = [{"block_table": tables[i, :(int(ctx[i]) + B) // B].tolist(), "position": int(ctx[i])} for i in range(len(ctx))]
+    # a prompt in pool blocks nobody else uses
+    pool = kc.size(1)
+    extra = 6
+    kc = torch.cat((kc, torch.zeros(kc.size(0), extra, *kc.shape[2:], dtype=dtype)), dim=1)
+    vc = torch.cat((vc, torch.zeros(vc.size(0), extra, *vc.shape[2:], dtype=dtype)), dim=1)
+    prompt_table = list(range(pool, pool + extra))
+    prompt = torch.randint(0, SHAPE128.vocab, (70,))
+    dec_ctx = {"num_prefill_tokens": 0, "num_decode_tokens": len(decodes), "prefills": [], "decodes": decodes}
+    mixed_ctx = {"num_prefill_tokens": 70, "num_decode_tokens": len(decodes), "decodes": decodes,
+                 "prefills": [{"block_table": prompt_table, "start_position": 0, "num_tokens": 70}]}
+    alone = model.mixed_step(dec_ctx, tokens.to(DEV), kc.to(DEV), vc.to(DEV), overlap=False)
+    kc_m, vc_m = kc.to(DEV), vc.to(DEV)
+    mixed = model.mixed_step(mixed_ctx, torch.cat((prompt, tokens)).to(DEV), kc_m, vc_m, overlap=False)
+    torch.cuda.synchronize()
+    assert mixed.shape == (1 + len(decodes), SHAPE128.vocab)
+    # GEMMs over another row count may pick another algorithm: same values up to the dtype's rounding
+    assert F.cosine_similarity(mixed[1:].float(), alone.float(), dim=-1).min().item() > 0.999
+
+    # the same prompt in two chunks (40 + 30 tokens): the second chunk reads the first one's pages
+    kc_c, vc_c = kc.to(DEV), vc.to(DEV)
+    first = {"num_prefill_tokens": 40, "num_decode_tokens": 0, "decodes": [],
+             "prefills": [{"block_table": prompt_table, "start_position": 0, "num_tokens": 40}]}
+    second = {"num_prefill_tokens": 30, "num_decode_tokens": 0, "decodes": [],
+              "prefills": [{"block_table": prompt_table, "start_position": 40, "num_tokens": 30}]}
+    model.mixed_step(first, prompt[:40].to(DEV), kc_c, vc_c)
+    chunked = model.mixed_step(second, prompt[40:].to(DEV), kc_c, vc_c)
+    torch.cuda.synchronize()
+    assert F.cosine_similarity(chunked[0].float(), mixed[0].float(), dim=-1).item() > 0.999
+    assert (kc_c[:, pool:].float() - kc_m[:, pool:].float()).abs().max().item() < 0.1     # same pages either way
+    assert paged_kernels.check_status(DEV, raise_on_error=False) == 0
