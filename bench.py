@@ -293,6 +293,68 @@ def run_prefill_workload(args, paged_kernels, dev, timed):
             "mixed_step_two_streams_ms": round(ms_mixed_overlapped, 4), "prefill_sm_share": sm_share,
             "mixed_step": "last 512-token chunk of each of 4 prompts + store + decode attention of 128 sequences"}
 
+def run_reference_grid(args, paged_kernels, dev):
+    """The shape grid of the reference's own micro-benchmark (nanoPD/paged_attention/tests/
+    benchmark_paged_attention_optim.py:110-137: small uniform-length batches, and whole-prompt stores), as device
+    time per launch: 20 launches captured in one CUDA graph, so the Python call overhead of these microsecond-sized
+    problems is not part of the number.  The reference prints such a table at run time and publishes none."""
+    attn_cfgs = [(1, 32, 32, 128, 128, 16, torch.float16), (1, 32, 32, 128, 512, 16, torch.float16),
+                 (1, 32, 32, 128, 1024, 16, torch.float16), (8, 32, 32, 128, 256, 16, torch.float16),
+                 (16, 32, 32, 128, 256, 16, torch.float16), (32, 32, 32, 128, 256, 16, torch.float16),
+                 (1, 32, 8, 128, 512, 16, torch.float16), (8, 32, 8, 128, 512, 16, torch.float16),
+                 (16, 32, 8, 128, 512, 16, torch.float16), (8, 32, 32, 128, 256, 16, torch.bfloat16)]
+    store_cfgs = [(8, 128, 128, 16, torch.float16), (8, 512, 128, 16, torch.float16), (8, 1024, 128, 16, torch.float16),
+                  (8, 2048, 128, 16, torch.float16), (8, 512, 128, 32, torch.float16), (32, 512, 128, 16, torch.float16),
+                  (8, 512, 128, 16, torch.bfloat16)]
+    inner = 20
+
+    def graph_time(fn):
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(inner):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (5 * inner) * 1e3          # microseconds per launch
+
+    rows_a, rows_s = [], []
+    for (S, Hq, Hkv, D, L, B, dt) in attn_cfgs:
+        b = workloads.make_decode_batch([L] * S, Hq, Hkv, D, B, dt, device=dev, seed=args.seed)
+        out = torch.zeros_like(b.query)
+        us = graph_time(lambda: paged_kernels.paged_attention_forward(out, b.query, b.k_cache, b.v_cache, b.block_tables,
+                                                                      b.ctx_lens, b.scale, B, b.max_blocks))
+        by, _ = algorithmic_bytes([L] * S, Hq, Hkv, D, B)
+        rows_a.append({"num_seqs": S, "heads": Hq, "kv_heads": Hkv, "head_size": D, "seq_len": L, "block": B,
+                       "dtype": str(dt).replace("torch.", ""), "us": round(us, 2), "gbs": round(by / us / 1e3, 1),
+                       "tflops_reference_formula": round(S * Hq * 4 * L * D / us / 1e6, 3)})
+    for (Hkv, T, D, B, dt) in store_cfgs:
+        nblk = (T + B - 1) // B
+        kc = torch.zeros(nblk, Hkv, B, D, dtype=dt, device=dev)
+        vc = torch.zeros_like(kc)
+        k_src = torch.randn(Hkv, T, D, device=dev).to(dt)
+        v_src = torch.randn(Hkv, T, D, device=dev).to(dt)
+        table = torch.arange(nblk, dtype=torch.int32, device=dev).unsqueeze(0).expand(T, -1)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        us = graph_time(lambda: paged_kernels.paged_kv_store(kc, vc, k_src, v_src, table, pos))
+        written = 2 * T * Hkv * D * 2
+        rows_s.append({"kv_heads": Hkv, "seq_len": T, "head_dim": D, "block": B, "dtype": str(dt).replace("torch.", ""),
+                       "us": round(us, 2), "gbs_written_reference_formula": round(written / us / 1e3, 1)})
+    return {"attention": rows_a, "kv_store": rows_s, "timing": f"{inner} launches per CUDA graph, 5 replays, CUDA events",
+            "device_status": paged_kernels.check_status(dev, raise_on_error=False)}
+
+
 def run_model_tables(args, dev, timed):
     """The reference's model-level timing tables (nanoPD/cost_model/record_no_kvstorekernel_naive_pagedattention.txt:
     T_decode(kv_len, batch), T_prefill(L), extra decode latency from a co-scheduled prompt chunk; measured there
@@ -452,6 +514,15 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
         replicas.barrier()
         return e0.elapsed_time(e1) / n
+
+    if args.workload == "reference-grid":
+        res = run_reference_grid(args, paged_kernels, dev)
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"workload": "the reference micro-benchmark's shape grid (secondary, not the headline metric)", **res}), flush=True)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return 0
 
     if args.workload == "model-tables":
         res = run_model_tables(args, dev, timed)
@@ -725,7 +796,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--workload", choices=["decode", "prefill", "model", "model-tables"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "model", "model-tables", "reference-grid"], default="decode",
                     help="decode = the headline configuration 2 (default); prefill = configuration 3's chunked prefill")
     ap.add_argument("--profile", action="store_true",
                     help="only warm up and run the timed step loop (for short ncu captures); prints no bench line")

@@ -37,7 +37,7 @@ using namespace npd;
 
 constexpr int kTile = 16;               // tokens per stage
 constexpr int kMaxSeqsPerLaunch = 4096; // prefix array lives in shared memory
-constexpr int kMinTilesPerWorker = 8;   // keeps tiny batches from dissolving into partials
+constexpr int kMaxFloorTilesPerWorker = 16;   // upper end of the floor on tiles per worker (see tiles_per_worker)
 constexpr int kStatusBytes = 256;       // workspace header: status word + padding
 constexpr int kTicketCapacity = 1 << 18;   // ticket words (1 MiB): a FIXED region right after the header, so that no
                                         // launch shape ever puts partial records where another shape keeps tickets
@@ -74,9 +74,17 @@ __device__ __forceinline__ int clamped_len(const DecodeParams &p, int s) {
     return len;
 }
 
-__device__ __forceinline__ long long tiles_per_worker(long long total, int num_workers) {
-    long long w = (total + num_workers - 1) / num_workers;
-    return w < kMinTilesPerWorker ? kMinTilesPerWorker : w;
+// Tiles per worker: the equal split over all workers, but not below a floor that keeps small batches from
+// dissolving into partials.  A worker needs ~0.7 us per tile and the merge of a (sequence, kv head) ~0.45 us per
+// four partials, so for `tph` tiles per (sequence, kv head) the time W*0.7 + tph/W/4*0.45 is least near
+// W = sqrt(0.16 * tph): 1-2 tiles for the few-hundred-token batches of a micro-benchmark (every SM gets work and
+// nobody streams eight tiles in a row), 8-9 for an 8k-token context.
+__device__ __forceinline__ long long tiles_per_worker(long long total, int num_workers, long long num_seq_heads) {
+    const long long w = (total + num_workers - 1) / num_workers;
+    const float tph = static_cast<float>(total) / static_cast<float>(num_seq_heads > 0 ? num_seq_heads : 1);
+    long long floor_w = static_cast<long long>(sqrtf(0.16f * tph) + 0.5f);
+    floor_w = floor_w < 1 ? 1 : (floor_w > kMaxFloorTilesPerWorker ? kMaxFloorTilesPerWorker : floor_w);
+    return w < floor_w ? floor_w : w;
 }
 
 // pre[0..S]: exclusive prefix of ceil(len/16) over the sequences, built by the whole CTA.
@@ -378,7 +386,7 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
     }
 
     const long long total = (long long)p.num_vheads * pre[p.num_seqs];
-    const long long W = tiles_per_worker(total, p.num_workers);
+    const long long W = tiles_per_worker(total, p.num_workers, (long long)p.num_vheads * p.num_seqs);
     const int worker = blockIdx.x * nwarps + warp;
     const long long f_begin = (long long)worker * W;
     if (f_begin >= total) return;
