@@ -91,7 +91,8 @@ int npd_kv_store(void *k_cache, void *v_cache, const void *k_src, const void *v_
  * `workspace` is caller-owned device memory of at least
  * npd_decode_workspace_bytes(...) bytes, 256-byte aligned, ZEROED ONCE before first
  * use and then only touched by this library; its first int32 is the status word.
- * Two calls that may overlap on the GPU need two workspaces.                           */
+ * Two calls that may overlap on the GPU need two workspaces.  After a call that reported
+ * NPD_STATUS_WAIT_TIMEOUT zero the workspace again before reusing it.                  */
 size_t npd_decode_workspace_bytes(int64_t num_seqs, int64_t num_q_heads,
                                   int64_t num_kv_heads, int64_t head_dim, int device);
 int npd_paged_decode_attention(void *out, const void *q, const void *k_cache,
@@ -117,8 +118,8 @@ int npd_paged_decode_attention(void *out, const void *q, const void *k_cache,
  * The FIRST call on each device looks up the array's device address (one
  * cudaGetSymbolAddress, with that device current) — make that call before any stream
  * capture begins.  All calls on a device share the one array, which keeps the previous
- * call's contents; the status word is cleared at the start of each call, the rest is
- * written before it is read.  Two calls that can overlap on the GPU (different streams)
+ * call's contents; the status word and the arrival tickets are cleared at the start of each
+ * call, the rest is written before it is read.  Two calls that can overlap on the GPU (different streams)
  * race on it: serialise them, or give the concurrent ones the workspace variant.
  * `status_out` (device int32, may be NULL) receives this call's NPD_STATUS_* bits.         */
 size_t npd_decode_static_scratch_bytes(void);

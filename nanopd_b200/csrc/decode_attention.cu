@@ -930,9 +930,10 @@ extern "C" int npd_paged_decode_attention_static(void *out, const void *q, const
     const int rc_addr = static_scratch_address(&scratch);   // first call on a device: resolves the symbol
     if (rc_addr != NPD_OK) return rc_addr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // The array keeps whatever the previous call left.  Only the status word must start at zero;
-    // the tile prefix and the partial records are written before they are read.
-    NPD_CUDA_TRY(cudaMemsetAsync(scratch, 0, sizeof(int32_t), st));
+    // The array keeps whatever the previous call left.  The status word must start at zero, and so must the
+    // arrival tickets: the kernel leaves them at zero itself, except when an earlier launch gave up on a bounded
+    // wait — and this caller has no pointer to clean up with.  The partial records are written before they are read.
+    NPD_CUDA_TRY(cudaMemsetAsync(scratch, 0, kStatusBytes + (size_t)kTicketCapacity * sizeof(int32_t), st));
     const int rc = npd_paged_decode_attention(out, q, k_cache, v_cache, block_tables, seq_lens, scale, num_seqs,
                                               num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
                                               num_blocks, cache_block_stride, bt_row_stride, dtype, scratch,
