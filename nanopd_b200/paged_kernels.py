@@ -74,7 +74,8 @@ def check_status(device=None, raise_on_error: bool = True) -> int:
             _lib.check(_C.npd_read_status(ws.data_ptr(), ctypes.byref(out), stream_handle))
             bits |= out.value
             if out.value & _lib.NPD_STATUS_WAIT_TIMEOUT:
-                ws.zero_()          # a launch that gave up may have left arrival tickets behind (stream is idle here)
+                ws.zero_()          # a launch that gave up may have left arrival tickets behind
+                torch.cuda.synchronize(idx)
     if bits and raise_on_error:
         names = [n for n, b in (("bad block id", 1), ("bad position / seq_len", 2), ("wait time-out", 4)) if bits & b]
         raise RuntimeError("nanopd_b200 device status: " + ", ".join(names))
