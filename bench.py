@@ -671,10 +671,38 @@ def run_gpu_arm(args):
                 torch.cuda.synchronize(dev)
                 ms_mig = e0.elapsed_time(e1) / 5
                 mig_bytes = kv_transfer.migration_bytes(nb_m, src_k)
+                # the same pull on a side stream while the decode step loop runs on the main stream
+                side = torch.cuda.Stream(device=dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                n_during = 24
+                evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_during + 1)]
+                m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(side):
+                    m0.record()
+                for _ in range(3):
+                    kv_transfer.transfer_kv(src_k, src_v, dst_k, dst_v, ids, stream=side)
+                with torch.cuda.stream(side):
+                    m1.record()
+                evs[0].record()
+                for i in range(n_during):
+                    step()
+                    evs[i + 1].record()
+                torch.cuda.synchronize(dev)
+                t_mig_busy = m0.elapsed_time(m1) / 3
+                # steps that ended inside the migration window
+                t_end, inside = 0.0, []
+                for i in range(n_during):
+                    dt = evs[i].elapsed_time(evs[i + 1])
+                    t_end += dt
+                    if t_end <= 3 * t_mig_busy:
+                        inside.append(dt)
                 ok = torch.equal(dst_k[:, ids[0]].cpu(), src_k[:, ids[0]].cpu())
                 extras["migrate_nvlink"] = {"gbs_one_direction": round(mig_bytes / (ms_mig * 1e-3) / 1e9, 1),
                                             "ms": round(ms_mig, 3), "bytes": mig_bytes, "blocks": nb_m, "layers": L_m,
                                             "from_gpu": peer, "to_gpu": local_rank, "data_check": bool(ok),
+                                            "gbs_while_decoding": round(mig_bytes / (t_mig_busy * 1e-3) / 1e9, 1),
+                                            "decode_step_ms_during_migration": round(sum(inside) / max(1, len(inside)), 4),
+                                            "decode_step_ms_alone": round(ms_step, 4),
                                             "peak_gbs": 770.0, "peak_source": "measured peer copy on this pool"}
                 del src_k, src_v, dst_k, dst_v
             except Exception as exc:  # noqa: BLE001

@@ -169,9 +169,9 @@ int npd_paged_prefill_attention(void *out, const void *q, const void *k_cache,
  * into the current device (peer access enabled, or an IPC mapping); the copy is done by
  * the kernel itself (bulk asynchronous copies through shared memory, no multicast), so no
  * copy engine or NCCL call is involved.
- * `max_ctas` > 0 caps the grid (one warp per CTA; 0 = 32 CTAs, which saturate NVLink) so
- * a side-stream migration leaves the SMs to the compute stream; `max_ctas` < 0 selects the
- * plain load/store variant with -max_ctas CTAs of 256 threads.                          */
+ * `max_ctas` > 0 sets the grid (one warp and 64 KiB of shared memory per CTA, small enough to
+ * share an SM with a decode-attention CTA of the compute stream; 0 = 48 CTAs, which fill an
+ * NVLink); `max_ctas` < 0 selects the plain load/store variant with -max_ctas CTAs of 256 threads. */
 int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
                    const int32_t *src_blocks, const int32_t *dst_blocks, int64_t num_pairs,
                    int64_t num_layers, int64_t block_elems, int elem_bytes,

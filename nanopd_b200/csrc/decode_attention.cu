@@ -340,13 +340,15 @@ __device__ __forceinline__ void merge_partials(AttnState<T, D, NT> &st, const De
 // [blocks, Hkv, D, B]; csrc/paged_attention_optimized/index.h:14-31,60-75): a K tile lands as [d piece][token][8]
 // and feeds ldmatrix directly (8 tokens of one piece are 128 contiguous bytes), a V tile lands as [d][token] and is
 // already the A operand of O^T = V^T . P^T, so it is read without the transposing ldmatrix.
-// MAXW (8 or 12) is the launch bound in warps: the 8-warp instances keep the whole register file for the merge
-// of split sequences (four records' loads in flight), the 12-warp instances trade that for more warps.
+// MAXW (8 or 12) is the largest number of warps an instance is launched with.  The 8-warp instances are compiled
+// for at most 224 registers per thread: enough for the merge of split sequences to keep four records' loads in
+// flight, while 8 x 32 x 224 registers leave an eighth of the register file to a small CTA of another stream (the
+// page migration kernel) on the same SM.  The 12-warp instances (168 registers) trade registers for warps.
 #ifndef NPD_DECODE_MAX_WARPS
 #define NPD_DECODE_MAX_WARPS 12
 #endif
 template <typename T, int D, int NT, bool IL, int MAXW>
-__global__ void __launch_bounds__(MAXW * 32, 1)
+__global__ void __maxnreg__(MAXW <= 8 ? 224 : 168)
 paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v) {
     constexpr int NH = D / 64;
@@ -707,13 +709,17 @@ int launch_decode(const DecodeParams &p, const CUtensorMap &tk, const CUtensorMa
                   cudaStream_t stream) {
     constexpr int STAGE_BYTES = 2 * kTile * D * 2;
     const size_t smem = 1024 + (size_t)ls.nwarps * ls.nstages * (STAGE_BYTES + 8) + ((size_t)p.num_seqs + 1) * 4 + 16;
+    // Largest shared-memory carve-out on both instances: the SM then has room for a small CTA of another stream
+    // (the page migration kernel asks for the same), instead of being configured for this CTA alone.
     if (ls.nwarps <= 8) {
         auto kern = paged_decode_stream_kernel<T, D, NT, IL, 8>;
         NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         kern<<<ls.grid, ls.nwarps * 32, smem, stream>>>(p, tk, tv);
     } else {
         auto kern = paged_decode_stream_kernel<T, D, NT, IL, NPD_DECODE_MAX_WARPS>;
         NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         kern<<<ls.grid, ls.nwarps * 32, smem, stream>>>(p, tk, tv);
     }
     NPD_CUDA_TRY(cudaGetLastError());

@@ -9,16 +9,25 @@
 // Two data paths:
 //   * bulk (default): one warp per CTA; an elected lane streams units through a ring of
 //     shared-memory stages with cp.async.bulk (global -> shared on an mbarrier, shared -> global in
-//     bulk groups).  192 KiB of copies in flight per CTA without occupying registers or issue slots,
-//     so a handful of CTAs fill the link and the compute stream keeps the SMs.  No multicast.
+//     bulk groups): copies in flight without occupying registers or issue slots, in a CTA small
+//     enough (one warp, 64 KiB) to sit beside a decode-attention CTA on the same SM.  No multicast.
 //   * ld/st: 256 threads per CTA, 16-byte loads and stores, eight loads in flight per thread —
 //     used when a unit is not a multiple of 16 bytes wide enough for the bulk path.
 // Link- or HBM-bound: blocks * layers * 2 * block_bytes, one direction.
+#include <cstdlib>
+
 #include "npd_common.cuh"
 
 namespace {
 
 using namespace npd;
+
+int env_int(const char *name, int fallback) {
+    const char *v = std::getenv(name);
+    if (!v || !*v) return fallback;
+    const int x = std::atoi(v);
+    return x > 0 ? x : fallback;
+}
 
 struct MigrateParams {
     const uint8_t *src_k, *src_v;
@@ -30,13 +39,14 @@ struct MigrateParams {
     long long block_bytes;
     long long src_layer_stride, src_block_stride, dst_layer_stride, dst_block_stride;   // bytes
     int src_num_blocks, dst_num_blocks;
-    int pieces_per_unit;      // bulk path: a unit is moved in pieces of at most kPieceBytes
+    int pieces_per_unit;      // bulk path: a unit is moved in pieces of at most piece_bytes
+    int piece_bytes;          // bulk path: bytes per ring stage (a multiple of 16)
+    int stages;               // bulk path: ring depth (<= kMaxBulkStages)
 };
 
 constexpr int kThreads = 256;
 constexpr int kUnroll = 8;
-constexpr int kPieceBytes = 32 * 1024;
-constexpr int kBulkStages = 6;            // 6 x 32 KiB = 192 KiB of shared memory per CTA
+constexpr int kMaxBulkStages = 8;
 
 __device__ __forceinline__ bool locate_unit(const MigrateParams &p, long long u, const uint8_t *&src, uint8_t *&dst) {
     // Unit order: pair-major, then layer, then K|V — consecutive units work on one block.
@@ -96,11 +106,12 @@ __device__ __forceinline__ void bulk_wait_read() {     // at most N store groups
 }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// One warp per CTA; lane 0 drives a ring of kBulkStages pieces: load piece i+S-1 while piece i is stored.
+// One warp per CTA; lane 0 drives a ring of p.stages pieces: load piece i+S-1 while piece i is stored.
 __global__ void __launch_bounds__(32) kv_migrate_bulk_kernel(const MigrateParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t bars[kBulkStages];
+    __shared__ uint64_t bars[kMaxBulkStages];
     if (threadIdx.x != 0) return;
+    const int kBulkStages = p.stages, kPieceBytes = p.piece_bytes;
     for (int i = 0; i < kBulkStages; ++i) mbar_init(smem_u32(&bars[i]), 1);
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -212,7 +223,15 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
     p.dst_block_stride = dst_block_stride * elem_bytes;
     p.src_num_blocks = static_cast<int>(src_num_blocks);
     p.dst_num_blocks = static_cast<int>(dst_num_blocks);
-    p.pieces_per_unit = static_cast<int>((p.block_bytes + kPieceBytes - 1) / kPieceBytes);
+    // Ring of the bulk path: 4 stages of 16 KiB.  64 KiB of shared memory and one warp fit beside a decode-attention
+    // CTA on the same SM (132 KiB, 8 warps x 224 registers), so a migration on a side stream does not take SMs away
+    // from the compute stream; 48 such CTAs keep ~2.3 MB in flight, enough for an NVLink.
+    p.piece_bytes = env_int("NPD_MIGRATE_PIECE_KB", 16) * 1024;
+    p.stages = env_int("NPD_MIGRATE_STAGES", 4);
+    if (p.stages > kMaxBulkStages) p.stages = kMaxBulkStages;
+    if (p.stages < 2) p.stages = 2;
+    while ((long long)p.piece_bytes * p.stages > 200 * 1024 && p.piece_bytes > 4096) p.piece_bytes /= 2;
+    p.pieces_per_unit = static_cast<int>((p.block_bytes + p.piece_bytes - 1) / p.piece_bytes);
 
     int dev = 0;
     NPD_CUDA_TRY(cudaGetDevice(&dev));
@@ -222,17 +241,22 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
     // max_ctas < 0 selects the load/store path with -max_ctas CTAs (kept for comparison and as a fallback).
     if (max_ctas >= 0) {
         const long long pieces = units * p.pieces_per_unit;
-        // 32 CTAs x 192 KiB in flight saturate NVLink and most of a same-GPU copy; more only takes shared
-        // memory away from the compute stream
-        long long grid = max_ctas > 0 ? max_ctas : 32;
+        long long grid = max_ctas > 0 ? max_ctas : 48;
         if (grid > npd::sm_count(dev)) grid = npd::sm_count(dev);
         if (grid > pieces) grid = pieces;
-        const size_t smem = (size_t)kBulkStages * kPieceBytes;
+        const size_t smem = (size_t)p.stages * p.piece_bytes;
         NPD_CUDA_TRY(cudaFuncSetAttribute(kv_migrate_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // Ask for the largest shared-memory carve-out: an SM configured for this small CTA alone could not take a
+        // decode-attention CTA of the compute stream beside it, and a persistent kernel that is one CTA short
+        // runs in two waves.
+        NPD_CUDA_TRY(cudaFuncSetAttribute(kv_migrate_bulk_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          cudaSharedmemCarveoutMaxShared));
         kv_migrate_bulk_kernel<<<static_cast<unsigned>(grid), 32, smem, st>>>(p);
     } else {
         long long grid = -static_cast<long long>(max_ctas);
         if (grid > units) grid = units;
+        NPD_CUDA_TRY(cudaFuncSetAttribute(kv_migrate_ldst_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          cudaSharedmemCarveoutMaxShared));
         kv_migrate_ldst_kernel<<<static_cast<unsigned>(grid), kThreads, 0, st>>>(p);
     }
     NPD_CUDA_TRY(cudaGetLastError());
