@@ -226,8 +226,16 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
     // Ring of the bulk path: 4 stages of 16 KiB.  64 KiB of shared memory and one warp fit beside a decode-attention
     // CTA on the same SM (132 KiB, 8 warps x 224 registers), so a migration on a side stream does not take SMs away
     // from the compute stream; 48 such CTAs keep ~2.3 MB in flight, enough for an NVLink.
-    p.piece_bytes = env_int("NPD_MIGRATE_PIECE_KB", 16) * 1024;
-    p.stages = env_int("NPD_MIGRATE_STAGES", 4);
+    // A copy between two pools of ONE GPU has three times an NVLink's bandwidth to fill and nothing to gain from
+    // being small: it takes the larger ring (6 x 32 KiB).
+    cudaPointerAttributes src_attr{}, dst_attr{};
+    const bool same_gpu = cudaPointerGetAttributes(&src_attr, src_k) == cudaSuccess &&
+                          cudaPointerGetAttributes(&dst_attr, dst_k) == cudaSuccess &&
+                          src_attr.type == cudaMemoryTypeDevice && dst_attr.type == cudaMemoryTypeDevice &&
+                          src_attr.device == dst_attr.device;
+    (void)cudaGetLastError();
+    p.piece_bytes = env_int("NPD_MIGRATE_PIECE_KB", same_gpu ? 32 : 16) * 1024;
+    p.stages = env_int("NPD_MIGRATE_STAGES", same_gpu ? 6 : 4);
     if (p.stages > kMaxBulkStages) p.stages = kMaxBulkStages;
     if (p.stages < 2) p.stages = 2;
     while ((long long)p.piece_bytes * p.stages > 200 * 1024 && p.piece_bytes > 4096) p.piece_bytes /= 2;
