@@ -14,7 +14,8 @@
 //   rotate_half(y) = concat(-y[D/2:], y[:D/2]),   T(.) = round to the tensor's 16-bit type.
 // A (token, head) row is D/8 lanes of 16 bytes; the two elements a rotation pairs sit at the same place
 // of two lanes half a row apart (one shuffle), the mean of squares is a reduction over the row's lanes,
-// and every warp keeps two passes of rows in flight.  HBM-bound, launch-latency bound at decode sizes.
+// every warp keeps two passes of rows in flight, and the products and sums that the reference rounds to
+// 16 bits are packed 16-bit instructions.  HBM-bound, launch-latency bound at decode sizes.
 #include "npd_common.cuh"
 
 namespace {
@@ -43,8 +44,6 @@ template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x
 template <typename T> __device__ __forceinline__ T from_f(float x);
 template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
-// round to T and back: where the 16-bit reference arithmetic rounds
-template <typename T> __device__ __forceinline__ float rt(float x) { return to_f<T>(from_f<T>(x)); }
 
 // 8 elements (16 bytes) of T <-> 8 floats
 template <typename T>
@@ -62,6 +61,25 @@ __device__ __forceinline__ uint4 pack8(const float (&in)[8]) {
     return raw;
 }
 
+// Packed 16-bit arithmetic: one instruction per pair, one rounding per operation — what the 16-bit tensor
+// arithmetic of the reference does (a product of two 16-bit values is exact in fp32, so "multiply in fp32 and
+// round" and the native packed multiply give the same bits; likewise for the sum).
+template <typename T> struct Pair;
+template <> struct Pair<__half> { using type = __half2; };
+template <> struct Pair<__nv_bfloat16> { using type = __nv_bfloat162; };
+template <typename T>
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+    using P = typename Pair<T>::type;
+    P r = __hmul2_rn(*reinterpret_cast<P *>(&a), *reinterpret_cast<P *>(&b));     // _rn: never fused with the add
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+template <typename T>
+__device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+    using P = typename Pair<T>::type;
+    P r = __hadd2_rn(*reinterpret_cast<P *>(&a), *reinterpret_cast<P *>(&b));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
 // A row of D elements is D/8 pieces of 16 bytes, one per lane: LPR = D/8 lanes per row, 32/LPR rows per warp pass,
 // the lower LPR/2 lanes of a row hold its first half and the upper ones the second half, so the element a rotation
 // pairs with sits at the same place of lane ^ (LPR/2).  Two passes are kept in flight (loads of both first).
@@ -73,23 +91,25 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStore
     const int lane = threadIdx.x & 31;
     const int sub = lane % LPR, row_in_pass = lane / LPR;
     const bool upper = sub >= LPR / 2;
-    const int rows_per_token = p.num_q_heads + 2 * p.num_kv_heads;
-    const long long total = p.num_tokens * rows_per_token;
-    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
-    const long long w0 = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
-    for (long long base = w0 * (RPW * UNROLL); base < total; base += warps * (RPW * UNROLL)) {
+    const unsigned rows_per_token = static_cast<unsigned>(p.num_q_heads + 2 * p.num_kv_heads);
+    const unsigned total = static_cast<unsigned>(p.num_tokens) * rows_per_token;      // < 2^31, checked by the host
+    const unsigned warps = gridDim.x * (blockDim.x >> 5);
+    const unsigned w0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t sign = upper ? 0u : 0x80008000u;            // rotate_half: (-second half, first half)
+    for (unsigned base = w0 * (RPW * UNROLL); base < total; base += warps * (RPW * UNROLL)) {
         uint4 raw[UNROLL], craw[UNROLL], sraw[UNROLL];
         T *dst[UNROLL];
         int kind[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const long long w = base + u * RPW + row_in_pass;
+            const unsigned w = base + u * RPW + row_in_pass;
             dst[u] = nullptr;
             kind[u] = 2;
             raw[u] = craw[u] = sraw[u] = make_uint4(0, 0, 0, 0);
             if (w >= total) continue;
-            const long long t = w / rows_per_token;
-            const int r = static_cast<int>(w - t * rows_per_token);
+            const unsigned t32 = w / rows_per_token;
+            const int r = static_cast<int>(w - t32 * rows_per_token);
+            const long long t = t32;
             const int kd = r < p.num_q_heads ? 0 : (r < p.num_q_heads + p.num_kv_heads ? 1 : 2);   // q, k, v
             const int h = kd == 0 ? r : (kd == 1 ? r - p.num_q_heads : r - p.num_q_heads - p.num_kv_heads);
             kind[u] = kd;
@@ -132,30 +152,27 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStore
             for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
 #pragma unroll
             for (int s = LPR / 2; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+            uint4 mine = raw[u];
             if (wgt != nullptr) {
                 const float inv = rsqrtf(ss * (1.f / D) + p.eps);
-                float wv[8];
-                unpack8<T>(__ldg(reinterpret_cast<const uint4 *>(wgt + sub * 8)), wv);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) x[i] = rt<T>(wv[i] * rt<T>(x[i] * inv));
+                for (int i = 0; i < 8; ++i) x[i] *= inv;
+                const uint4 y = pack8<T>(x);                       // rounded to T, as the norm module does
+                const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(wgt + sub * 8));
+                mine = make_uint4(mul2<T>(wv.x, y.x), mul2<T>(wv.y, y.y), mul2<T>(wv.z, y.z), mul2<T>(wv.w, y.w));
             }
             // the partner half of the row, as the 16-bit values the rotation reads
-            uint4 mine = pack8<T>(x), other;
+            uint4 other;
             other.x = __shfl_xor_sync(0xffffffffu, mine.x, LPR / 2);
             other.y = __shfl_xor_sync(0xffffffffu, mine.y, LPR / 2);
             other.z = __shfl_xor_sync(0xffffffffu, mine.z, LPR / 2);
             other.w = __shfl_xor_sync(0xffffffffu, mine.w, LPR / 2);
             if (kind[u] != 2) {
-                float y[8], c[8], sn[8];
-                unpack8<T>(other, y);
-                unpack8<T>(craw[u], c);
-                unpack8<T>(sraw[u], sn);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float rot = upper ? y[i] : -y[i];       // rotate_half: (-second half, first half)
-                    x[i] = rt<T>(x[i] * c[i]) + rt<T>(rot * sn[i]);
-                }
-                mine = pack8<T>(x);
+                const uint4 c = craw[u], sn = sraw[u];
+                mine.x = add2<T>(mul2<T>(mine.x, c.x), mul2<T>(other.x ^ sign, sn.x));
+                mine.y = add2<T>(mul2<T>(mine.y, c.y), mul2<T>(other.y ^ sign, sn.y));
+                mine.z = add2<T>(mul2<T>(mine.z, c.z), mul2<T>(other.z ^ sign, sn.z));
+                mine.w = add2<T>(mul2<T>(mine.w, c.w), mul2<T>(other.w ^ sign, sn.w));
             }
             if (dst[u] != nullptr) *reinterpret_cast<uint4 *>(dst[u]) = mine;
         }
@@ -219,6 +236,8 @@ extern "C" int npd_qk_norm_rope_store(void *q_out, const void *q, const void *k,
     NPD_REQUIRE(num_blocks <= INT32_MAX && max_blocks_per_seq <= INT32_MAX && block_size <= INT32_MAX &&
                     num_q_heads <= INT32_MAX / 4 && num_kv_heads <= INT32_MAX / 4,
                 NPD_ERR_INVALID_ARG, "npd_qk_norm_rope_store: dimension exceeds int32");
+    NPD_REQUIRE(num_tokens * (num_q_heads + 2 * num_kv_heads) < (1LL << 31) - 4096, NPD_ERR_INVALID_ARG,
+                "npd_qk_norm_rope_store: more than 2^31 (token, head) rows in one call");
 
     RopeStoreParams p;
     p.q_out = q_out;
