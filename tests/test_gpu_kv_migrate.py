@@ -136,3 +136,68 @@ def test_peer_to_peer_pull_over_nvlink(kernels):
     assert torch.equal(ddk.cpu(), dk) and torch.equal(ddv.cpu(), dv)
     with torch.cuda.device(1):
         assert kernels.check_status(raise_on_error=False) == 0
+
+
+@pytest.mark.parametrize("two_gpus", [False, True])
+def test_prefill_here_decode_there(kernels, two_gpus):
+    """The disaggregated hand-off end to end at the attention level: a prompt's K/V is written into the prefill
+    side's pool (store kernel), its pages move to OTHER block ids of the decode side's pool (migration kernel, over
+    NVLink when two GPUs are present), and decode attention over the moved pages — after storing one more token
+    there — matches the oracle run on the prompt as a whole."""
+    if two_gpus and torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from conftest import TOL
+    paged_kernels = kernels
+    from nanopd_b200 import kv_transfer
+    from oracle import paged_oracle
+    torch.manual_seed(31)
+    dtype = torch.bfloat16
+    p_dev, d_dev = "cuda:0", ("cuda:1" if two_gpus else "cuda:0")
+    L, Hq, Hkv, D, B = 2, 8, 2, 128, 16
+    n_prompt = 203
+    nblk = (n_prompt + 1 + B - 1) // B
+    p_pool, d_pool = 40, 64
+    k_prompt = torch.randn(L, Hkv, n_prompt, D).to(dtype)
+    v_prompt = torch.randn(L, Hkv, n_prompt, D).to(dtype)
+    # prefill side: store the prompt layer by layer
+    pk_cache = torch.zeros(L, p_pool, Hkv, B, D, dtype=dtype, device=p_dev)
+    pv_cache = torch.zeros_like(pk_cache)
+    src_ids = torch.randperm(p_pool)[:nblk].tolist()
+    with torch.cuda.device(p_dev):
+        for li in range(L):
+            paged_kernels.paged_kv_store(pk_cache[li], pv_cache[li], k_prompt[li].to(p_dev), v_prompt[li].to(p_dev),
+                                         torch.tensor(src_ids, dtype=torch.int32, device=p_dev), 0)
+    torch.cuda.synchronize(p_dev)
+    # decode side: pull the pages into its own ids
+    dk_cache = torch.randn(L, d_pool, Hkv, B, D, device=d_dev).to(dtype)       # other requests' pages
+    dv_cache = torch.randn(L, d_pool, Hkv, B, D, device=d_dev).to(dtype)
+    dst_ids = torch.randperm(d_pool)[:nblk].tolist()
+    assert kv_transfer.transfer_kv(pk_cache, pv_cache, dk_cache, dv_cache, src_ids, dst_block_table=dst_ids) == "p2p"
+    # one decode step there: store token n_prompt, attend over n_prompt + 1 tokens
+    q = torch.randn(1, Hq, D).to(dtype)
+    k_new, v_new = torch.randn(L, Hkv, 1, D).to(dtype), torch.randn(L, Hkv, 1, D).to(dtype)
+    table = torch.tensor([dst_ids], dtype=torch.int32, device=d_dev)
+    pos = torch.tensor([n_prompt], dtype=torch.int32, device=d_dev)
+    out = torch.zeros(L, 1, Hq, D, dtype=dtype, device=d_dev)
+    with torch.cuda.device(d_dev):
+        for li in range(L):
+            paged_kernels.paged_kv_store(dk_cache[li], dv_cache[li], k_new[li].to(d_dev), v_new[li].to(d_dev), table, pos)
+            paged_kernels.paged_attention_forward(out[li], q.to(d_dev), dk_cache[li], dv_cache[li], table, pos + 1,
+                                                  D ** -0.5, B, table.size(1))
+    torch.cuda.synchronize(d_dev)
+    # oracle: the same sequence in one contiguous pool
+    for li in range(L):
+        kc = torch.zeros(nblk, Hkv, B, D, dtype=dtype)
+        vc = torch.zeros_like(kc)
+        ids = torch.arange(nblk, dtype=torch.int32)
+        k_all = torch.cat((k_prompt[li], k_new[li]), dim=1)
+        v_all = torch.cat((v_prompt[li], v_new[li]), dim=1)
+        paged_oracle.kv_store(kc, vc, k_all, v_all, ids.unsqueeze(0).expand(n_prompt + 1, -1),
+                              torch.arange(n_prompt + 1, dtype=torch.int32))
+        want = paged_oracle.paged_decode_attention(q, kc, vc, ids.unsqueeze(0), torch.tensor([n_prompt + 1], dtype=torch.int32),
+                                                   D ** -0.5)
+        assert (out[li].float().cpu() - want).abs().max().item() <= TOL[dtype]
+        # the moved pages are bit-identical to what the prefill side wrote
+        assert torch.equal(dk_cache[li, dst_ids[0]].cpu(), pk_cache[li, src_ids[0]].cpu())
+    for d in {p_dev, d_dev}:
+        assert paged_kernels.check_status(d, raise_on_error=False) == 0
