@@ -366,7 +366,7 @@ def run_model_tables(args, dev, timed):
         return {"skipped": f"only {free >> 30} GiB free on the device"}
     shape = decoder_step.DecoderShape()
     B, pool_blocks = 16, 6144
-    model = decoder_step.SyntheticDecoder(dev, shape, torch.bfloat16, seed=args.seed, max_position=4096)
+    model = decoder_step.SyntheticDecoder(dev, shape, torch.bfloat16, seed=args.seed, max_position=16384 + 64)
     k_cache = torch.empty(shape.num_layers, pool_blocks, shape.num_kv_heads, B, shape.head_dim, dtype=torch.bfloat16, device=dev)
     v_cache = torch.empty_like(k_cache)
     for li in range(shape.num_layers):
@@ -389,14 +389,14 @@ def run_model_tables(args, dev, timed):
             model.replay()
             t_decode[f"B{batch}_kv{kv}"] = round(timed(model.replay, 5), 3)
     t_prefill = {}
-    for L in (64, 128, 256, 512, 1024, 2048):
+    for L in (64, 128, 256, 512, 1024, 2048, 8192, 16384):
         table = tables_for(1, L, 0)[0].tolist()
         ctx = {"num_prefill_tokens": L, "num_decode_tokens": 0, "decodes": [],
                "prefills": [{"block_table": table, "start_position": 0, "num_tokens": L}]}
         toks = torch.randint(0, shape.vocab, (L,), device=dev)
         fn = lambda: model.mixed_step(ctx, toks, k_cache, v_cache)
         fn()
-        t_prefill[f"L{L}"] = round(timed(fn, 3), 3)
+        t_prefill[f"L{L}"] = round(timed(fn, 3 if L <= 2048 else 2), 3)
     interference = {}
     for batch in (4, 16):
         kv = 1024
