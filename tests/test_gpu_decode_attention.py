@@ -199,3 +199,17 @@ def test_skip_merge_flag_only_affects_split_sequences(kernels):
     kernels.paged_attention_forward(out, q, kc, vc, bt, sl, scale, 16, bt.size(1), 1)
     torch.cuda.synchronize()
     assert torch.isfinite(out).all()
+
+
+def test_more_sequences_than_one_launch_takes(kernels):
+    """Batches beyond the shared-memory prefix capacity (4096 sequences) run as consecutive launches over the same
+    workspace: 5000 short ragged sequences, some of them empty."""
+    torch.manual_seed(41)
+    S, Hq, Hkv, D, B = 5000, 4, 2, 64, 16
+    lens = torch.randint(0, 41, (S,)).tolist()
+    b = workloads.make_decode_batch(lens, Hq, Hkv, D, B, torch.float16, device="cpu", seed=41)
+    check(kernels, b.query, b.k_cache, b.v_cache, b.block_tables, b.ctx_lens, b.scale)
+    got = run_kernel(kernels, b.query.to(DEV), b.k_cache.to(DEV), b.v_cache.to(DEV), b.block_tables.to(DEV),
+                     b.ctx_lens.to(DEV), b.scale)
+    empty = (b.ctx_lens == 0)
+    assert int(empty.sum()) > 0 and torch.count_nonzero(got[empty.to(DEV)]) == 0

@@ -182,3 +182,36 @@ def test_argument_errors(kernels):
     kc64 = torch.zeros(4, 2, 16, 64, dtype=torch.float16, device=DEV)
     with pytest.raises(RuntimeError):   # head_dim 64 is outside the tensor-core kernel's set
         kernels.paged_prefill_attention(torch.zeros_like(q64), q64, kc64, kc64, bt, [0], [16], [0], 1.0, 16, 4)
+
+
+def test_more_chunks_than_one_launch_takes(kernels):
+    """A call with more prompt chunks than fit the kernel's parameter arrays (64) is split into launches: 150 short
+    prompts, whole-prompt prefill of each (the packing PrefillWorker uses, nanoPD/workers/prefill_worker.py:47-64)."""
+    torch.manual_seed(42)
+    dtype, Hq, Hkv, D, B = torch.float16, 4, 2, 128, 16
+    n_prompts = 150
+    lens = torch.randint(1, 50, (n_prompts,)).tolist()
+    nblk = [(l + B - 1) // B for l in lens]
+    pool = sum(nblk) + 2
+    perm = torch.randperm(pool)
+    tables = torch.zeros(n_prompts, max(nblk), dtype=torch.int32)
+    kc = torch.zeros(pool, Hkv, B, D, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    qs, want, offs, o, pb = [], [], [], 0, 0
+    scale = D ** -0.5
+    for i, (l, nb) in enumerate(zip(lens, nblk)):
+        tables[i, :nb] = perm[pb:pb + nb].to(torch.int32)
+        pb += nb
+        q = torch.randn(l, Hq, D).to(dtype)
+        k = torch.randn(Hkv, l, D).to(dtype)
+        v = torch.randn(Hkv, l, D).to(dtype)
+        paged_oracle.kv_store(kc, vc, k, v, tables[i:i + 1].expand(l, -1), torch.arange(l, dtype=torch.int32))
+        qs.append(q)
+        offs.append(o)
+        o += l
+    for i, l in enumerate(lens):
+        want.append(paged_oracle.paged_prefill_attention(qs[i], kc, vc, tables[i], 0, scale))
+    got = run_chunks(kernels, torch.cat(qs).to(DEV), kc.to(DEV), vc.to(DEV), tables.to(DEV), offs, lens, [0] * n_prompts,
+                     scale, B).float().cpu()
+    err = (got - torch.cat(want)).abs().max().item()
+    assert err <= TOL[dtype], err
