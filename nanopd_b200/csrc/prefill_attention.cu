@@ -35,12 +35,15 @@ constexpr int kMaxPairs = 2048;    // query-tile pairs per launch (kernel-parame
 constexpr int kSchedSlots = 4;     // work items the producer may publish ahead of the slowest consumer
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
 constexpr int kKeys = 128;         // keys per tile (UMMA N of the score MMA, K extent of the PV MMA)
-constexpr int kD = 128;            // head_dim
 constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA for A, 10 MMA for B, 11 idle
 constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
-constexpr int kQTileBytes = 2 * kQHalfBytes;        // 32 KiB
 constexpr int kKvHalfBytes = kKeys * 128;           // one 64-element half of a 128-key K or V tile
-constexpr int kKvTileBytes = 2 * kKvHalfBytes;      // 32 KiB
+// head_dim kD = 64 * kHalves (64 or 128): a tile is kHalves halves of 16 KiB
+template <int kD> struct TileBytes {
+    static constexpr int kHalves = kD / 64;
+    static constexpr int q = kHalves * kQHalfBytes;     // 32 KiB at head_dim 128
+    static constexpr int kv = kHalves * kKvHalfBytes;   // 32 KiB at head_dim 128
+};
 constexpr int kStages = 2;                          // K ring and V ring depth
 constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; the packed probabilities of a key
                                    // tile overwrite the first 64 columns of its scores
@@ -277,7 +280,7 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, int item) {
 // ragged chunks balance across the SMs.  All barrier phases are driven by running counters: the producer
 // already loads the next item's K/V tiles (and, once the last score MMA has been issued, its query tiles) while
 // the current item drains, and the epilogue of an item overlaps the first MMAs of the next one.
-template <typename T>
+template <typename T, int kD>
 __global__ void __launch_bounds__(kThreads, 1)
 paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -285,9 +288,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
     uint8_t *sbase = smem_raw + pad;
-    uint8_t *q_tiles = sbase;                                   // 2 x 32 KiB (query tiles A and B)
-    uint8_t *k_ring = q_tiles + 2 * kQTileBytes;                // kStages x 16 KiB
-    uint8_t *v_ring = k_ring + kStages * kKvTileBytes;          // kStages x 16 KiB
+    constexpr int kHalves = TileBytes<kD>::kHalves;
+    constexpr int kQTileBytes = TileBytes<kD>::q, kKvTileBytes = TileBytes<kD>::kv;
+    uint8_t *q_tiles = sbase;                                   // query tiles A and B
+    uint8_t *k_ring = q_tiles + 2 * kQTileBytes;                // kStages K tiles
+    uint8_t *v_ring = k_ring + kStages * kKvTileBytes;          // kStages V tiles
     SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStages * kKvTileBytes);
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -374,8 +379,8 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 ++q_loads[x];
                 if (lane == 0) {
                     const uint32_t qbar = smem_u32(&ctrl->q_full[x]);
-                    mbar_expect_tx(qbar, static_cast<uint32_t>(2 * p.tq * p.group * 128));
-                    for (int h2 = 0; h2 < 2; ++h2)
+                    mbar_expect_tx(qbar, static_cast<uint32_t>(kHalves * p.tq * p.group * 128));
+                    for (int h2 = 0; h2 < kHalves; ++h2)
                         tma_load_3d(smem_u32(q_tiles + x * kQTileBytes + h2 * kQHalfBytes), &tm_q, qbar, h2 * 64,
                                     it.h * p.group, it.qoff + it.tok0[x]);
                 }
@@ -404,7 +409,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 // 16-key row groups holding at least one written key; the rest is never loaded
                 int ngroups = 0;
                 for (int g2 = 0; g2 < kKeys / 16; ++g2) ngroups += (key0 + g2 * 16 < it.ctx_end) ? 1 : 0;
-                const uint32_t bytes = static_cast<uint32_t>(ngroups * 2 * 16 * 128);
+                const uint32_t bytes = static_cast<uint32_t>(ngroups * kHalves * 16 * 128);
                 const int row = it.h * p.block_size + ((key0 + gi * 16) % p.block_size);
                 const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048);
                 const uint32_t par = ((g / kStages) - 1) & 1;
@@ -416,7 +421,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (role == 0 && gi < ngroups)
+                if (role == 0 && gi < ngroups && hf < kHalves)
                     tma_load_3d(smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
                                 hf * 64, row, id);
                 if (t == 0 && !(ok = load_q(1))) break;
@@ -427,7 +432,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (role == 1 && gi < ngroups)
+                if (role == 1 && gi < ngroups && hf < kHalves)
                     tma_load_3d(smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
                                 hf * 64, row, id);
             }
@@ -590,9 +595,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (gt / kStages) & 1, abort_flag, p.status))) break;
                     uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
                     const int first = max(it.ctx_end - key0, 0);
-                    const int n16 = (kKeys - first) * 16;        // 16-byte pieces: 2 halves x 8 per row
+                    constexpr int kPieces = kHalves * 8;           // 16-byte pieces per row
+                    const int n16 = (kKeys - first) * kPieces;
                     for (int idx = threadIdx.x & 127; idx < n16; idx += 128) {
-                        const int r = first + idx / 16, piece = idx % 16;
+                        const int r = first + idx / kPieces, piece = idx % kPieces;
                         *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kKvHalfBytes + r * 128 + ((piece & 7) << 4)) =
                             make_uint4(0, 0, 0, 0);
                     }
@@ -640,7 +646,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     if (__any_sync(0xffffffffu, grow)) {
                         const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
 #pragma unroll 1
-                        for (int cc = 0; cc < 4; ++cc) {
+                        for (int cc = 0; cc < kD / 32; ++cc) {
                             float o[32];
                             tmem_ld32(t_o + cc * 32, o);
                             tmem_wait_ld();
@@ -734,11 +740,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     T *dst = static_cast<T *>(p.out) +
                              ((long long)(it.qoff + it.tok0[x] + tq_idx) * p.num_q_heads + (long long)it.h * p.group + hg) * kD;
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
+                    for (int cc = 0; cc < kD / 32; ++cc) {
                         float o[32];
                         tmem_ld32(t_o + cc * 32, o);
                         tmem_wait_ld();
-                        if (cc == 3) {
+                        if (cc == kD / 32 - 1) {
                             // O is in registers: the next item's first PV may overwrite the accumulator
                             tc_fence_before();
                             mbar_arrive(smem_u32(&ctrl->o_free[x]));
@@ -786,7 +792,8 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                                            void *stream) {
     NPD_REQUIRE(dtype == NPD_DTYPE_F16 || dtype == NPD_DTYPE_BF16, NPD_ERR_UNSUPPORTED,
                 "prefill attention supports float16 and bfloat16 only (dtype code %d)", dtype);
-    NPD_REQUIRE(head_dim == kD, NPD_ERR_UNSUPPORTED, "prefill attention: head_dim %lld is not 128", (long long)head_dim);
+    NPD_REQUIRE(head_dim == 64 || head_dim == 128, NPD_ERR_UNSUPPORTED,
+                "prefill attention: head_dim %lld not in {64,128}", (long long)head_dim);
     NPD_REQUIRE(block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
                 "prefill attention: block_size %lld not in {16,32}", (long long)block_size);
     NPD_REQUIRE(num_chunks >= 0 && num_q_heads > 0 && num_kv_heads > 0 && max_blocks_per_seq > 0 && num_blocks > 0,
@@ -832,8 +839,11 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                                       cache_block_stride, 16);
     if (rc != NPD_OK) return rc;
 
-    const size_t smem = 1024 + 2 * (size_t)kQTileBytes + 2 * (size_t)kStages * kKvTileBytes + sizeof(SmemCtrl) + 64;
-    auto kern = dtype == NPD_DTYPE_F16 ? paged_prefill_kernel<__half> : paged_prefill_kernel<__nv_bfloat16>;
+    const size_t halves = static_cast<size_t>(head_dim / 64);
+    const size_t smem = 1024 + 2 * halves * kQHalfBytes + 2 * (size_t)kStages * halves * kKvHalfBytes + sizeof(SmemCtrl) + 64;
+    auto kern = head_dim == 128
+                    ? (dtype == NPD_DTYPE_F16 ? paged_prefill_kernel<__half, 128> : paged_prefill_kernel<__nv_bfloat16, 128>)
+                    : (dtype == NPD_DTYPE_F16 ? paged_prefill_kernel<__half, 64> : paged_prefill_kernel<__nv_bfloat16, 64>);
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -14,7 +14,7 @@ SHAPE = decoder_step.DecoderShape(num_layers=2, hidden=256, ffn=512, vocab=1000,
 
 
 SHAPE128 = decoder_step.DecoderShape(num_layers=2, hidden=256, ffn=512, vocab=1000, num_q_heads=4, num_kv_heads=2,
-                                     head_dim=128, rope_theta=1e4)     # the chunked-prefill kernel takes head_dim 128
+                                     head_dim=128, rope_theta=1e4)
 
 
 def make_batch(dtype, steps_ahead=4, seed=0, shape=SHAPE):

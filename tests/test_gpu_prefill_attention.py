@@ -36,9 +36,8 @@ def run_chunks(kernels, q_rows, k_cache, v_cache, tables, offsets, tokens, start
     return out
 
 
-def check_single(kernels, L, start, n, Hq, Hkv, B, dtype, seed=0, poison=False):
+def check_single(kernels, L, start, n, Hq, Hkv, B, dtype, seed=0, poison=False, D=128):
     """Chunk [start, start+n) of an L-token prompt; keys beyond start+n exist in the pool but must be ignored."""
-    D = 128
     q, table, kc, vc = build_prompt(L, Hq, Hkv, D, B, dtype, seed=seed, poison=poison)
     if poison:   # the contract only promises keys < start+n: poison everything later as well
         for pos in range(start + n, L):
@@ -178,10 +177,10 @@ def test_argument_errors(kernels):
         kernels.paged_prefill_attention(out, q, kc, kc, bt, [0], [16], [60], 1.0, 16, 4)
     with pytest.raises(RuntimeError):   # chunk outside q
         kernels.paged_prefill_attention(out, q, kc, kc, bt, [8], [16], [0], 1.0, 16, 4)
-    q64 = torch.zeros(16, 8, 64, dtype=torch.float16, device=DEV)
-    kc64 = torch.zeros(4, 2, 16, 64, dtype=torch.float16, device=DEV)
-    with pytest.raises(RuntimeError):   # head_dim 64 is outside the tensor-core kernel's set
-        kernels.paged_prefill_attention(torch.zeros_like(q64), q64, kc64, kc64, bt, [0], [16], [0], 1.0, 16, 4)
+    q8 = torch.zeros(16, 8, 128, dtype=torch.float16, device=DEV)
+    kc8 = torch.zeros(8, 2, 8, 128, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError):   # block size 8 is outside the tensor-core kernel's set
+        kernels.paged_prefill_attention(torch.zeros_like(q8), q8, kc8, kc8, bt, [0], [16], [0], 1.0, 8, 4)
 
 
 def test_more_chunks_than_one_launch_takes(kernels):
@@ -215,3 +214,20 @@ def test_more_chunks_than_one_launch_takes(kernels):
                      scale, B).float().cpu()
     err = (got - torch.cat(want)).abs().max().item()
     assert err <= TOL[dtype], err
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L,start,n,Hq,Hkv,B", [(40, 0, 40, 8, 2, 16), (300, 128, 100, 32, 8, 16), (700, 512, 188, 16, 4, 32),
+                                                (1500, 1000, 500, 14, 2, 16), (260, 0, 260, 4, 4, 16)])
+def test_head_dim_64(kernels, dtype, L, start, n, Hq, Hkv, B):
+    """The 64-wide variant of the kernel (one 64-element half per tile; Llama-3.2-1B / Qwen2-0.5B head size)."""
+    check_single(kernels, L, start, n, Hq, Hkv, B, dtype, seed=L, D=64)
+    check_single(kernels, L, start, n, Hq, Hkv, B, dtype, seed=L + 1, poison=True, D=64)
+
+
+def test_head_dim_256_is_refused(kernels):
+    q = torch.zeros(4, 2, 256, dtype=torch.float16, device=DEV)
+    kc = torch.zeros(2, 2, 16, 256, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError, match="head_dim"):
+        kernels.paged_prefill_attention(torch.zeros_like(q), q, kc, kc.clone(), torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                                        [0], [4], [0], 1.0, 16, 1)
