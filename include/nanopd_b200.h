@@ -204,6 +204,29 @@ int npd_qk_norm_rope_store(void *q_out, const void *q, const void *k, const void
                            int64_t q_out_token_stride, int64_t cos_sin_row_stride,
                            int64_t bt_row_stride, int dtype, int32_t *status, void *stream);
 
+/* ---- (6) batched top-k sampling -------------------------------------------------------
+ * Replaces top_k_sample (nanoPD/engine/model_runner.py:279-284), which the reference calls
+ * once per sequence and reads back with .item() (nanoPD/engine/engine.py:100-106,
+ * nanoPD/workers/decode_worker.py:110, nanoPD/workers/prefill_worker.py:79).  One launch
+ * serves all `num_rows` rows of `logits` ([num_rows, vocab], rows `row_stride` elements
+ * apart, f16 / bf16 / f32) and writes one token id per row to `out_ids` (device int64):
+ *   x = nan_to_num(row, nan = 0, posinf = 1e4, neginf = -1e4)          (in the logits' dtype)
+ *   the top_k largest x, larger first, equal values by the lower id first
+ *   p = softmax over those values, computed in fp32 and rounded to the logits' dtype
+ *   the draw: the first candidate whose running fp32 sum of p exceeds uniforms[row] * sum(p)
+ * `uniforms` (device float32 [num_rows], values in [0, 1)) supplies the randomness, so a
+ * caller's generator decides the stream; it may be NULL when top_k == 1 (the arg-max,
+ * the reference's default).  top_k in [1, NPD_SAMPLE_MAX_TOP_K], top_k <= vocab,
+ * ceil(vocab / 16384) * top_k <= 4096; rows must start on 16-byte boundaries.
+ * `workspace`: device memory of at least npd_top_k_sample_workspace_bytes(...), zeroed once
+ * by the caller and then reusable by any later call on the same stream (the kernel leaves
+ * its arrival counters at zero).                                                          */
+#define NPD_SAMPLE_MAX_TOP_K 64
+int64_t npd_top_k_sample_workspace_bytes(int64_t num_rows, int64_t vocab, int top_k);
+int npd_top_k_sample(int64_t *out_ids, const void *logits, const float *uniforms, int64_t num_rows,
+                     int64_t vocab, int64_t row_stride, int top_k, int dtype, void *workspace,
+                     int64_t workspace_bytes, void *stream);
+
 /* Enables peer access from the current device to `peer_device` (idempotent).
  * Stands in for the driver-side mapping torch's copy_ sets up in the reference
  * (nanoPD/workers/kv_transfer.py:6-14 only probes can_device_access_peer).              */

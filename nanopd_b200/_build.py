@@ -17,7 +17,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libnanopd_b200.so"
 SOURCES = ["capi.cu", "kv_store.cu", "decode_attention.cu", "prefill_attention.cu", "kv_migrate.cu",
-           "qk_rope_store.cu"]
+           "qk_rope_store.cu", "top_k_sample.cu"]
 HEADERS = [CSRC / "npd_common.cuh", PKG_DIR.parent / "include" / "nanopd_b200.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

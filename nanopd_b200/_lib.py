@@ -40,6 +40,9 @@ SIGNATURES = {
                                c_int, c_void_p, c_void_p]),
     "npd_qk_norm_rope_store": (c_int, [c_void_p] * 8 + [c_float] + [c_void_p] * 4 + [c_int64] * 14 +
                                [c_int, c_void_p, c_void_p]),
+    "npd_top_k_sample_workspace_bytes": (c_int64, [c_int64, c_int64, c_int]),
+    "npd_top_k_sample": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p,
+                                 c_int64, c_void_p]),
     "npd_enable_peer_access": (c_int, [c_int]),
 }
 

@@ -1,0 +1,536 @@
+// Batched top-k sampling over the logits of one step (sm_100a).
+//
+// Replaces the per-sequence sampler of the reference (top_k_sample, nanoPD/engine/model_runner.py:279-284,
+// called once per sequence with a device→host read of every token at nanoPD/engine/engine.py:100-106 and
+// nanoPD/workers/decode_worker.py:110): nan_to_num, the k largest logits, a softmax over them in the
+// logits' dtype, one draw.  Here one launch serves every row of the step and leaves the tokens on the device.
+//
+// The work is a single pass over T x V logits, so HBM bounds it.  A CTA walks a run of slices of one row (a whole
+// row when there are enough rows to fill the GPU); a slice is 8 x 16 bytes per thread, held in registers, and the
+// next slice's loads are in flight while the current one is examined.  The k best are found without sorting:
+//   * first slice: every group of 2 or 4 threads reduces the maximum of its logits; the k-th largest of the group
+//     maxima is a lower bound of the slice's k-th largest logit (k groups hold a logit at least that large).  The
+//     logits not below it (about -G ln(1 - k/G) on unordered data, G groups) are gathered into shared memory and
+//     ranked by counting; ranks below k are the k best so far and the k-th of them is the running threshold;
+//   * later slices: only logits ABOVE the threshold are gathered (their ids are larger than every id seen, so an
+//     equal value ranks behind) — k/(slices seen) of them on unordered data — and ranked together with the k
+//     best so far; the scan itself is one conversion and one comparison per logit.
+// Data that defeats the threshold (more than 1024 logits past it in one slice: long runs of equal or rising
+// values) takes k rounds of a block-wide arg-max over that slice instead — slower, same result.  Where a row is
+// shared by several CTAs, each writes its k best to global memory and the last to arrive (a ticket per row, reset
+// by that CTA) merges them.  One warp then computes the probabilities and draws.
+// Order everywhere: larger value first, equal values by the lower id — which makes the result independent of
+// how the row was cut.
+#include <cfloat>
+#include <climits>
+#include <cstdlib>
+
+#include "npd_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kLoads = 8;                       // 16-byte loads per thread and slice: 64 (16-bit) or 32 (fp32) logits
+constexpr int kMaxGroups = 128;
+constexpr int kMaxTopK = NPD_SAMPLE_MAX_TOP_K;
+constexpr int kSliceCandidates = 1024;          // more logits than this past the bound in one slice: arg-max rounds
+constexpr int kPool = 4096;                     // candidates of one row at the merge: chunks x k
+constexpr int kSmallestSlice = kThreads * kLoads * 4;
+constexpr int64_t kTicketBytes = 65536;         // head of the workspace: one arrival counter per row of a launch
+constexpr int64_t kRowsPerLaunch = kTicketBytes / 4;
+
+struct SampleParams {
+    const void *logits;
+    const float *uniforms;
+    int64_t *out;
+    float *cand_value;      // [rows of a launch, chunks, k]
+    int32_t *cand_id;
+    uint32_t *tickets;
+    int64_t row_stride;
+    int64_t first_row;
+    int vocab;
+    int slices;             // per row
+    int chunks;             // CTAs per row, each over a run of slices
+    int top_k;
+};
+
+__device__ __forceinline__ bool before(float va, int ia, float vb, int ib) {
+    return va > vb || (va == vb && ia < ib);
+}
+
+__device__ __forceinline__ uint4 load_streaming(const void *p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+// nan_to_num(nan = 0, posinf = 1e4, neginf = -1e4), the replacement already rounded to the logits' dtype
+__device__ __forceinline__ float replace_special(float x, float replacement) {
+    if (x != x) return 0.f;
+    if (fabsf(x) > FLT_MAX) return copysignf(replacement, x);
+    return x;
+}
+
+template <typename T> struct Logit;
+template <> struct Logit<float> {
+    static constexpr uint32_t kLowestBits = 0xff7fffffu;     // the most negative finite value: pads a ragged row end
+    static __device__ __forceinline__ float round(float x) { return x; }
+    static __device__ __forceinline__ void widen(const uint4 &raw, float *v) {
+        v[0] = __uint_as_float(raw.x); v[1] = __uint_as_float(raw.y);
+        v[2] = __uint_as_float(raw.z); v[3] = __uint_as_float(raw.w);
+    }
+    // The largest of the 16 bytes' logits and `m`; a NaN is passed over.
+    static __device__ __forceinline__ float max_of(const uint4 &raw, float m) {
+        return fmaxf(fmaxf(fmaxf(m, __uint_as_float(raw.x)), fmaxf(__uint_as_float(raw.y), __uint_as_float(raw.z))),
+                     __uint_as_float(raw.w));
+    }
+    // True when one of the 16 bytes' logits is above `limit` (not below it when `inclusive`) or is a NaN.
+    static __device__ __forceinline__ bool any_past(const uint4 &raw, float limit, bool inclusive) {
+        const float a = __uint_as_float(raw.x), b = __uint_as_float(raw.y), c = __uint_as_float(raw.z),
+                    d = __uint_as_float(raw.w);
+        return inclusive ? (!(a < limit) || !(b < limit) || !(c < limit) || !(d < limit))
+                         : (!(a <= limit) || !(b <= limit) || !(c <= limit) || !(d <= limit));
+    }
+};
+template <> struct Logit<__half> {
+    static constexpr uint32_t kLowestBits = 0xfbffu;
+    static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ void widen(const uint4 &raw, float *v) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ float max_of(const uint4 &raw, float m) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        const __half2 a = __hmax2(*reinterpret_cast<const __half2 *>(&w[0]), *reinterpret_cast<const __half2 *>(&w[1]));
+        const __half2 b = __hmax2(*reinterpret_cast<const __half2 *>(&w[2]), *reinterpret_cast<const __half2 *>(&w[3]));
+        const float2 f = __half22float2(__hmax2(a, b));
+        return fmaxf(m, fmaxf(f.x, f.y));
+    }
+    static __device__ __forceinline__ bool any_past(const uint4 &raw, float limit, bool inclusive) {
+        const __half2 l2 = __float2half2_rn(limit);         // exact: the limit is one of the logits
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        unsigned any = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 x = *reinterpret_cast<const __half2 *>(&w[i]);
+            any |= inclusive ? __hgeu2_mask(x, l2) : __hgtu2_mask(x, l2);
+        }
+        return any != 0;
+    }
+};
+template <> struct Logit<__nv_bfloat16> {
+    static constexpr uint32_t kLowestBits = 0xff7fu;
+    static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ void widen(const uint4 &raw, float *v) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ float max_of(const uint4 &raw, float m) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        const __nv_bfloat162 a = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]),
+                                         *reinterpret_cast<const __nv_bfloat162 *>(&w[1]));
+        const __nv_bfloat162 b = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&w[2]),
+                                         *reinterpret_cast<const __nv_bfloat162 *>(&w[3]));
+        const float2 f = __bfloat1622float2(__hmax2(a, b));
+        return fmaxf(m, fmaxf(f.x, f.y));
+    }
+    static __device__ __forceinline__ bool any_past(const uint4 &raw, float limit, bool inclusive) {
+        const __nv_bfloat162 l2 = __float2bfloat162_rn(limit);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        unsigned any = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162 *>(&w[i]);
+            any |= inclusive ? __hgeu2_mask(x, l2) : __hgtu2_mask(x, l2);
+        }
+        return any != 0;
+    }
+};
+
+// One slice of a row into registers: kLoads 16-byte pieces per thread, piece j of thread t at logits
+// base + (j * kThreads + t) * kVec.  Past the end of the row the most negative finite value is filled in.
+template <typename T>
+__device__ __forceinline__ void load_slice(const T *logits, int vocab, int base, int tid, uint4 (&raw)[kLoads]) {
+    constexpr int kVec = 16 / sizeof(T);
+#pragma unroll
+    for (int j = 0; j < kLoads; ++j) {
+        const int e0 = base + (j * kThreads + tid) * kVec;
+        if (e0 + kVec <= vocab) {
+            raw[j] = load_streaming(logits + e0);
+        } else {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (sizeof(T) == 4) {
+                    w[i] = e0 + i < vocab ? reinterpret_cast<const uint32_t *>(logits)[e0 + i] : Logit<T>::kLowestBits;
+                } else {
+                    const uint16_t *h = reinterpret_cast<const uint16_t *>(logits);
+                    const uint32_t lo = e0 + 2 * i < vocab ? h[e0 + 2 * i] : Logit<T>::kLowestBits;
+                    const uint32_t hi = e0 + 2 * i + 1 < vocab ? h[e0 + 2 * i + 1] : Logit<T>::kLowestBits;
+                    w[i] = lo | (hi << 16);
+                }
+            }
+            raw[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleParams p) {
+    using L = Logit<T>;
+    constexpr int kVec = 16 / sizeof(T);
+    constexpr int kSlice = kThreads * kLoads * kVec;
+    __shared__ float pool_value[kPool];
+    __shared__ int pool_id[kPool];
+    __shared__ float group_max[kMaxGroups];
+    __shared__ float warp_value[kThreads / 32];
+    __shared__ int warp_id[kThreads / 32];
+    __shared__ float top_value[2][kMaxTopK], top_prob[kMaxTopK];
+    __shared__ int top_id[2][kMaxTopK];
+    __shared__ float bound;
+    __shared__ int gathered[2];
+    __shared__ int is_last;
+
+    const int tid = threadIdx.x;
+    const int row = blockIdx.x / p.chunks;                  // within this launch
+    const int chunk = blockIdx.x - row * p.chunks;
+    const int k = p.top_k;
+    const int s_begin = static_cast<int>(static_cast<int64_t>(chunk) * p.slices / p.chunks);
+    const int s_end = static_cast<int>(static_cast<int64_t>(chunk + 1) * p.slices / p.chunks);
+    const T *logits = static_cast<const T *>(p.logits) + (p.first_row + row) * p.row_stride;
+    const float replacement = L::round(1e4f);
+    if (tid < 2) gathered[tid] = 0;
+
+    // The chunk's k best so far live in top_value[side] / top_id[side], best first; n_top of them, and `tau` is
+    // the k-th.  A later slice only has to look at logits ABOVE tau: its ids are all larger than the ids seen, so
+    // an equal value ranks behind.  What it finds collects in the pool (counter gathered[bank]) and is ranked
+    // together with the k best so far once there are k of them (enough to move tau), or at the chunk's end — an
+    // older, lower tau only lets a few more logits through.
+    int n_top = 0, side = 0, bank = 0, pooled = 0;
+    float tau = -INFINITY;
+
+    // One slice, already in registers.
+    auto examine = [&](const uint4 (&cur)[kLoads], const int s) {
+        const int base = s * kSlice;
+        const bool first = s == s_begin;
+
+        float limit = tau;
+        if (first) {
+            // A lower bound of the slice's k-th largest logit: the k-th largest of the maxima of G groups of
+            // threads (k groups hold a logit at least that large).  G = 64 for k <= 16, else 128.
+            // The maximum is taken over the logits as they are, NaNs passed over, and repaired afterwards: that
+            // can only lower a group's maximum below the one nan_to_num would give, which keeps the bound valid.
+            float m = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kLoads; ++j) m = L::max_of(cur[j], m);
+            if (m != m) m = 0.f;                            // unreachable with fmaxf; kept for a max that returns NaN
+            else if (fabsf(m) > FLT_MAX) m = copysignf(replacement, m);
+            const int group_threads = k <= 16 ? 4 : 2;
+            const int groups = kThreads / group_threads;
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            if (group_threads == 4) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            if (tid % group_threads == 0) group_max[tid / group_threads] = m;
+            __syncthreads();
+            if (tid < groups) {
+                const float mine = group_max[tid];
+                int rank = 0;
+#pragma unroll 8
+                for (int j = 0; j < groups; ++j) {
+                    const float other = group_max[j];
+                    rank += (other > mine) || (other == mine && j < tid);
+                }
+                if (rank == k - 1) bound = mine;
+            }
+            __syncthreads();
+            limit = bound;
+        }
+
+        // ---- gather the logits past the limit (not below it in the first slice, above it later) ---------------
+        // -inf only matters when its replacement, -1e4, would pass the limit.
+        const bool careful = limit < -replacement || (first && limit == -replacement);
+#pragma unroll
+        for (int j = 0; j < kLoads; ++j) {
+            if (careful || L::any_past(cur[j], limit, first)) {
+                float f[kVec];
+                L::widen(cur[j], f);
+                const int e0 = base + (j * kThreads + tid) * kVec;
+#pragma unroll
+                for (int i = 0; i < kVec; ++i) {
+                    const float x = replace_special(f[i], replacement);
+                    if ((first ? x >= limit : x > limit) && e0 + i < p.vocab) {
+                        const int pos = atomicAdd(&gathered[bank], 1);
+                        if (pos < kSliceCandidates) {
+                            pool_value[pos] = x;
+                            pool_id[pos] = e0 + i;
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        int count = gathered[bank];
+
+        if (count > kSliceCandidates) {
+            // ---- data that defeats the limit (long runs of equal or rising values): the slice's own k best by
+            // k rounds of a block-wide arg-max over the registers, placed behind what earlier slices pooled ------
+            uint64_t taken = 0;
+            count = pooled;
+            for (int r = 0; r < k; ++r) {
+                float bv = -INFINITY;
+                int bi = INT_MAX, be = 0;
+#pragma unroll
+                for (int j = 0; j < kLoads; ++j) {
+                    float f[kVec];
+                    uint4 w = cur[j];
+                    // opaque to the compiler, so that the conversions stay inside the round instead of being
+                    // hoisted into registers that every path of the kernel would then pay for
+                    asm volatile("" : "+r"(w.x), "+r"(w.y), "+r"(w.z), "+r"(w.w));
+                    L::widen(w, f);
+                    const int e0 = base + (j * kThreads + tid) * kVec;
+#pragma unroll
+                    for (int i = 0; i < kVec; ++i) {
+                        const float x = replace_special(f[i], replacement);
+                        if (!((taken >> (j * kVec + i)) & 1ull) && e0 + i < p.vocab && before(x, e0 + i, bv, bi)) {
+                            bv = x;
+                            bi = e0 + i;
+                            be = j * kVec + i;
+                        }
+                    }
+                }
+                float wv = bv;
+                int wi = bi;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, wv, off);
+                    const int oi = __shfl_xor_sync(0xffffffffu, wi, off);
+                    if (before(ov, oi, wv, wi)) {
+                        wv = ov;
+                        wi = oi;
+                    }
+                }
+                if ((tid & 31) == 0) {
+                    warp_value[tid >> 5] = wv;
+                    warp_id[tid >> 5] = wi;
+                }
+                __syncthreads();
+                wv = warp_value[0];
+                wi = warp_id[0];
+#pragma unroll
+                for (int w = 1; w < kThreads / 32; ++w) {
+                    if (before(warp_value[w], warp_id[w], wv, wi)) {
+                        wv = warp_value[w];
+                        wi = warp_id[w];
+                    }
+                }
+                if (wi != INT_MAX) {
+                    if (wi == bi) taken |= 1ull << be;
+                    if (tid == 0) {
+                        pool_value[count] = wv;
+                        pool_id[count] = wi;
+                    }
+                    ++count;
+                }
+                __syncthreads();
+            }
+        }
+        pooled = count;
+
+        if (count > 0 && (first || count >= k || s + 1 == s_end)) {
+            // ---- rank the pooled logits together with the k best so far; ranks below k are the new best ---------
+            const int all = count + n_top;
+            for (int i = tid; i < all; i += kThreads) {
+                const float mv = i < count ? pool_value[i] : top_value[side][i - count];
+                const int mi = i < count ? pool_id[i] : top_id[side][i - count];
+                int rank = 0;
+                for (int j = 0; j < count; ++j) rank += before(pool_value[j], pool_id[j], mv, mi);
+                for (int j = 0; j < n_top; ++j) rank += before(top_value[side][j], top_id[side][j], mv, mi);
+                if (rank < k) {
+                    top_value[side ^ 1][rank] = mv;
+                    top_id[side ^ 1][rank] = mi;
+                }
+            }
+            if (tid == 0) gathered[bank ^ 1] = 0;       // last read before the previous ranking's closing barrier
+            n_top = all < k ? all : k;
+            side ^= 1;
+            bank ^= 1;
+            pooled = 0;
+            __syncthreads();
+            if (n_top == k) tau = top_value[side][k - 1];
+        }
+    };
+
+    // Two register buffers take turns: while one slice is examined the next is in flight, and the buffer just
+    // examined is refilled at once with the slice after that — up to 2 x 8 x 16 bytes per thread on their way.
+    uint4 buf_a[kLoads], buf_b[kLoads];
+    load_slice<T>(logits, p.vocab, s_begin * kSlice, tid, buf_a);
+    if (s_begin + 1 < s_end) load_slice<T>(logits, p.vocab, (s_begin + 1) * kSlice, tid, buf_b);
+    for (int s = s_begin; s < s_end; s += 2) {
+        examine(buf_a, s);
+        if (s + 2 < s_end) load_slice<T>(logits, p.vocab, (s + 2) * kSlice, tid, buf_a);
+        if (s + 1 < s_end) {
+            examine(buf_b, s + 1);
+            if (s + 3 < s_end) load_slice<T>(logits, p.vocab, (s + 3) * kSlice, tid, buf_b);
+        }
+    }
+
+    if (p.chunks > 1) {
+        // ---- the last CTA of the row to arrive merges the chunks' lists ------------------------------------
+        float *list_value = p.cand_value + (static_cast<int64_t>(row) * p.chunks + chunk) * k;
+        int32_t *list_id = p.cand_id + (static_cast<int64_t>(row) * p.chunks + chunk) * k;
+        for (int r = tid; r < k; r += kThreads) {
+            list_value[r] = r < n_top ? top_value[side][r] : -INFINITY;
+            list_id[r] = r < n_top ? top_id[side][r] : -1;
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) is_last = atomicAdd(&p.tickets[row], 1u) == static_cast<uint32_t>(p.chunks - 1);
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        const int total = p.chunks * k;
+        const float *row_value = p.cand_value + static_cast<int64_t>(row) * total;
+        const int32_t *row_id = p.cand_id + static_cast<int64_t>(row) * total;
+        for (int i = tid; i < total; i += kThreads) {
+            pool_value[i] = __ldcg(row_value + i);
+            pool_id[i] = __ldcg(row_id + i);
+        }
+        __syncthreads();
+        for (int i = tid; i < total; i += kThreads) {
+            const int mi = pool_id[i];
+            if (mi < 0) continue;
+            const float mv = pool_value[i];
+            int rank = 0;
+            for (int j = 0; j < total; ++j) rank += before(pool_value[j], pool_id[j], mv, mi);   // an empty entry is -inf
+            if (rank < k) {
+                top_value[0][rank] = mv;
+                top_id[0][rank] = mi;
+            }
+        }
+        side = 0;
+        __syncthreads();
+    }
+
+    if (tid < 32) {
+        // softmax over the k values, rounded to the logits' dtype as torch.softmax returns it
+        const float mx = top_value[side][0];
+        const float e0 = tid < k ? expf(top_value[side][tid] - mx) : 0.f;
+        const float e1 = tid + 32 < k ? expf(top_value[side][tid + 32] - mx) : 0.f;
+        float sum = e0 + e1;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (tid < k) top_prob[tid] = L::round(__fdiv_rn(e0, sum));
+        if (tid + 32 < k) top_prob[tid + 32] = L::round(__fdiv_rn(e1, sum));
+        __syncwarp();
+        if (tid == 0) {
+            int pick = 0;
+            if (k > 1) {
+                // inverse CDF: the first candidate whose running sum exceeds uniform x total
+                float all = 0.f;
+                for (int j = 0; j < k; ++j) all += top_prob[j];
+                const float target = p.uniforms[p.first_row + row] * all;
+                float run = 0.f;
+                pick = k - 1;
+                for (int j = 0; j < k; ++j) {
+                    run += top_prob[j];
+                    if (run > target) {
+                        pick = j;
+                        break;
+                    }
+                }
+            }
+            p.out[p.first_row + row] = top_id[side][pick];
+            if (p.chunks > 1) p.tickets[row] = 0;       // every CTA of the row has arrived: ready for the next launch
+        }
+    }
+}
+
+int slices_of(int64_t vocab, int slice) { return static_cast<int>((vocab + slice - 1) / slice); }
+
+}  // namespace
+
+extern "C" int64_t npd_top_k_sample_workspace_bytes(int64_t num_rows, int64_t vocab, int top_k) {
+    if (num_rows <= 0 || vocab <= 0 || top_k <= 0) return kTicketBytes;
+    const int64_t rows = num_rows < kRowsPerLaunch ? num_rows : kRowsPerLaunch;
+    int64_t chunks = slices_of(vocab, kSmallestSlice);
+    if (chunks * top_k > kPool) chunks = kPool / top_k;
+    return kTicketBytes + rows * chunks * top_k * 8;
+}
+
+extern "C" int npd_top_k_sample(int64_t *out_ids, const void *logits, const float *uniforms, int64_t num_rows,
+                                int64_t vocab, int64_t row_stride, int top_k, int dtype, void *workspace,
+                                int64_t workspace_bytes, void *stream) {
+    NPD_REQUIRE(dtype == NPD_DTYPE_F16 || dtype == NPD_DTYPE_BF16 || dtype == NPD_DTYPE_F32, NPD_ERR_UNSUPPORTED,
+                "npd_top_k_sample: unsupported dtype code %d", dtype);
+    NPD_REQUIRE(num_rows >= 0 && vocab > 0, NPD_ERR_INVALID_ARG, "npd_top_k_sample: non-positive dimension");
+    NPD_REQUIRE(top_k >= 1 && top_k <= kMaxTopK, NPD_ERR_UNSUPPORTED, "npd_top_k_sample: top_k %d not in [1, %d]",
+                top_k, kMaxTopK);
+    NPD_REQUIRE(top_k <= vocab, NPD_ERR_INVALID_ARG, "npd_top_k_sample: top_k %d exceeds the vocabulary %lld", top_k,
+                (long long)vocab);
+    NPD_REQUIRE(vocab <= (1LL << 30), NPD_ERR_UNSUPPORTED, "npd_top_k_sample: vocabulary %lld too large",
+                (long long)vocab);
+    if (num_rows == 0) return NPD_OK;
+    const int elem = dtype == NPD_DTYPE_F32 ? 4 : 2;
+    NPD_REQUIRE(out_ids && logits && workspace, NPD_ERR_INVALID_ARG, "npd_top_k_sample: NULL pointer");
+    NPD_REQUIRE(uniforms || top_k == 1, NPD_ERR_INVALID_ARG, "npd_top_k_sample: top_k > 1 needs uniform numbers");
+    NPD_REQUIRE(row_stride >= vocab, NPD_ERR_INVALID_ARG, "npd_top_k_sample: row stride smaller than the vocabulary");
+    NPD_REQUIRE(npd::aligned16(logits) && (num_rows == 1 || (row_stride * elem) % 16 == 0), NPD_ERR_INVALID_ARG,
+                "npd_top_k_sample: rows of logits must start on 16-byte boundaries");
+    NPD_REQUIRE(npd::aligned16(workspace), NPD_ERR_INVALID_ARG, "npd_top_k_sample: workspace must be 16-byte aligned");
+    NPD_REQUIRE(workspace_bytes >= npd_top_k_sample_workspace_bytes(num_rows, vocab, top_k), NPD_ERR_WORKSPACE,
+                "npd_top_k_sample: workspace of %lld bytes, %lld needed", (long long)workspace_bytes,
+                (long long)npd_top_k_sample_workspace_bytes(num_rows, vocab, top_k));
+    int device = 0;
+    NPD_CUDA_TRY(cudaGetDevice(&device));
+    const int sms = npd::sm_count(device);
+
+    SampleParams p;
+    p.logits = logits;
+    p.uniforms = uniforms;
+    p.out = out_ids;
+    p.tickets = static_cast<uint32_t *>(workspace);
+    p.row_stride = row_stride;
+    p.vocab = static_cast<int>(vocab);
+    p.slices = slices_of(vocab, kThreads * kLoads * (16 / elem));
+    p.top_k = top_k;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    for (int64_t first = 0; first < num_rows; first += kRowsPerLaunch) {
+        const int64_t rows = num_rows - first < kRowsPerLaunch ? num_rows - first : kRowsPerLaunch;
+        // CTAs per row: the split that needs the fewest slice-times, counting a wave of CTAs as its slices plus one
+        // for the first bound and the hand-over, and a little per extra list to merge.
+        int64_t chunks = 1;
+        double best = 0;
+        for (int64_t c = 1; c <= p.slices && c * top_k <= kPool; ++c) {
+            const int64_t waves = (rows * c + 2 * sms - 1) / (2 * sms);          // two CTAs fit an SM
+            const double cost = static_cast<double>(waves) * ((p.slices + c - 1) / c + 1.0) + 0.05 * c;
+            if (c == 1 || cost < best) {
+                best = cost;
+                chunks = c;
+            }
+        }
+        if (const char *forced = getenv("NPD_SAMPLE_CHUNKS")) {                  // for experiments
+            const int64_t c = atoll(forced);
+            if (c >= 1 && c <= p.slices && c * top_k <= kPool) chunks = c;
+        }
+        p.chunks = static_cast<int>(chunks);
+        p.first_row = first;
+        p.cand_value = reinterpret_cast<float *>(static_cast<char *>(workspace) + kTicketBytes);
+        p.cand_id = reinterpret_cast<int32_t *>(p.cand_value + rows * chunks * top_k);
+        const unsigned grid = static_cast<unsigned>(rows * chunks);
+        if (dtype == NPD_DTYPE_F16) top_k_sample_kernel<__half><<<grid, kThreads, 0, s>>>(p);
+        else if (dtype == NPD_DTYPE_BF16) top_k_sample_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(p);
+        else top_k_sample_kernel<float><<<grid, kThreads, 0, s>>>(p);
+        NPD_CUDA_TRY(cudaGetLastError());
+    }
+    return NPD_OK;
+}

@@ -6,11 +6,12 @@ layer loop, then sampling at :279-284) with this library as the attention block:
 QKV projection → ``paged_qk_norm_rope_store`` → ``paged_attention_forward`` → output projection → MLP.  The
 projections are plain library GEMMs (``torch.nn.functional.linear``); block tables, positions and lengths live on
 the device for the whole run and advance in place, so a step has no host→device traffic and the whole step —
-36 layers, sampling and the advance of the positions — is one CUDA graph.
+36 layers, sampling (``sampling.top_k_sample``, one launch for the batch, tokens stay on the device) and the
+advance of the positions — is one CUDA graph.
 
 Weights are random (there are no checkpoints here); shapes default to Qwen3-8B (36 layers, hidden 4096, FFN 12288,
-32 query / 8 KV heads of 128, vocabulary 151 936, rope theta 1e6).  Greedy sampling stands in for the reference's
-``top_k_sample`` (one ``.item()`` per sequence there, model_runner.py:279-284).
+32 query / 8 KV heads of 128, vocabulary 151 936, rope theta 1e6).  ``top_k`` defaults to 1 as the reference's
+``top_k_sample`` does (one call and one ``.item()`` per sequence there, model_runner.py:279-284, engine.py:100-106).
 """
 from __future__ import annotations
 
@@ -20,7 +21,7 @@ from typing import List, Optional
 import torch
 import torch.nn.functional as F
 
-from . import paged_kernels
+from . import paged_kernels, sampling
 
 
 @dataclass
@@ -49,8 +50,9 @@ class SyntheticDecoder:
     lengths, KV pools of all layers); ``step`` runs one token for every sequence and advances the batch."""
 
     def __init__(self, device, shape: Optional[DecoderShape] = None, dtype=torch.bfloat16, seed: int = 0,
-                 max_position: int = 16384):
+                 max_position: int = 16384, top_k: int = 1):
         self.shape = s = shape or DecoderShape()
+        self.top_k = int(top_k)
         self.device = torch.device(device)
         self.dtype = dtype
         gen = torch.Generator(device=self.device)
@@ -103,6 +105,7 @@ class SyntheticDecoder:
         S = token_ids.numel()
         self.q_rot = torch.empty(S, s.num_q_heads, s.head_dim, dtype=self.dtype, device=self.device)
         self.attn_out = torch.empty_like(self.q_rot)
+        self.uniforms = torch.zeros(S, dtype=torch.float32, device=self.device)
         self._graph = None
 
     # ---- one decode step -----------------------------------------------------------------------------------
@@ -131,7 +134,10 @@ class SyntheticDecoder:
             x = x + F.linear(F.silu(gu[:, :s.ffn]) * gu[:, s.ffn:], L["w_down"])
         logits = F.linear(F.rms_norm(x, (s.hidden,), self.final_norm, s.eps), self.lm_head)
         self.logits = logits
-        self.token_ids.copy_(logits.argmax(dim=-1))
+        if self.top_k > 1:
+            self.uniforms.uniform_()
+        sampling.top_k_sample(logits, self.top_k, uniforms=self.uniforms if self.top_k > 1 else None,
+                              out=self.token_ids)
         self.positions.add_(1)
         self.seq_lens.add_(1)
 
@@ -163,8 +169,9 @@ class SyntheticDecoder:
         self._graph.replay()
 
     def launches_per_step(self) -> int:
-        """This library's kernels per step: one fused norm/rotary/store and one attention launch per layer."""
-        return 2 * self.shape.num_layers
+        """This library's kernels per step: one fused norm/rotary/store and one attention launch per layer, and
+        the sampler."""
+        return 2 * self.shape.num_layers + 1
 
     # ---- one scheduler step with prompt chunks and decode sequences -----------------------------------------
     def mixed_step(self, ctx: dict, token_ids: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

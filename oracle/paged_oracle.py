@@ -23,6 +23,14 @@ README "transformers", the fixtures were made with 5.5.0), at the reference's ca
 nanoPD/engine/model_runner.py:97-115.  It is pinned bit for bit against those functions by
 ``tests/golden/make_golden_rope.py`` and the fixture ``tests/golden/qk_norm_rope_cases.npz``.
 
+``top_k_candidates`` / ``top_k_sample`` restate ``top_k_sample`` of nanoPD/engine/model_runner.py:279-284
+(nan_to_num, ``torch.topk``, softmax over the k values in the logits' dtype, one multinomial draw).
+The k values, their ids and the probabilities are pinned bit for bit against those torch calls by
+``tests/golden/make_golden_sampling.py`` (fixture ``tests/golden/top_k_sample_cases.npz``), and the
+``top_k = 1`` result against the reference function itself.  The draw cannot be pinned: the
+reference takes it from torch's global generator.  Here it is the inverse CDF of a uniform number
+the caller supplies, over the same probabilities.
+
 Every function cites the reference file:line it follows.
 """
 from __future__ import annotations
@@ -32,6 +40,41 @@ from typing import Sequence
 
 import torch
 import torch.nn.functional as F
+
+
+# ---------------------------------------------------------------------------
+# Sampling
+# ---------------------------------------------------------------------------
+def top_k_candidates(logits, top_k):
+    """The k candidates of every row and their probabilities (nanoPD/engine/model_runner.py:280-282).
+
+    logits [T, V] (fp16 / bf16 / fp32).  Returns (values [T, k] in the logits' dtype, ids int64 [T, k],
+    probabilities [T, k] in the logits' dtype).  Candidates are ordered by value, largest first, equal
+    values by the lower id first (``torch.topk`` leaves that order unspecified)."""
+    x = torch.nan_to_num(logits, nan=0.0, posinf=1e4, neginf=-1e4)
+    order = torch.sort(x.float(), dim=-1, descending=True, stable=True).indices[:, :top_k]
+    vals = torch.gather(x, 1, order)
+    probs = torch.softmax(vals, dim=-1)
+    return vals, order, probs
+
+
+def top_k_sample(logits, top_k, uniforms=None):
+    """One draw per row from the top-k distribution (nanoPD/engine/model_runner.py:279-284).
+
+    The draw is the inverse CDF of ``uniforms[t]`` in [0, 1): the first candidate whose running fp32 sum
+    of probabilities exceeds ``uniforms[t]`` times the total.  ``top_k == 1`` needs no uniform number and
+    returns the arg-max, which is what the reference's default returns."""
+    import numpy as np
+    _, ids, probs = top_k_candidates(logits, top_k)
+    T = logits.size(0)
+    out = torch.empty(T, dtype=torch.int64)
+    u = torch.zeros(T) if uniforms is None else uniforms.float().cpu()
+    for t in range(T):
+        c = np.cumsum(probs[t].float().numpy(), dtype=np.float32)
+        target = np.float32(u[t].item()) * c[-1]
+        j = int(np.searchsorted(c, target, side="right"))
+        out[t] = ids[t, min(j, top_k - 1)]
+    return out
 
 
 # ---------------------------------------------------------------------------

@@ -73,6 +73,27 @@ def load_rope_cases():
     return cases
 
 
+def load_sampling_cases():
+    """The torch.topk / softmax / reference top-1 cases of tests/golden/top_k_sample_cases.npz."""
+    z = np.load(GOLDEN / "top_k_sample_cases.npz")
+    dtypes = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+    cases = []
+    for name in z["names"].tolist():
+        dtype = dtypes[str(z[f"{name}/dtype"])]
+
+        def tensor(key):
+            a = z[f"{name}/{key}"]
+            return torch.from_numpy(a.copy()) if dtype == torch.float32 else torch.from_numpy(a.copy()).view(dtype)
+
+        cases.append(dict(name=name, dtype=dtype, top_k=int(z[f"{name}/top_k"]), logits=tensor("logits"),
+                          values=tensor("values"), probabilities=tensor("probabilities"),
+                          ids=torch.from_numpy(z[f"{name}/ids"]),
+                          untied_rows=torch.from_numpy(z[f"{name}/untied_rows"]),
+                          reference_top_1=torch.from_numpy(z[f"{name}/reference_top_1"]),
+                          top_1_unique=torch.from_numpy(z[f"{name}/top_1_unique"])))
+    return cases
+
+
 @pytest.fixture(scope="session")
 def decode_cases():
     return load_decode_cases()

@@ -76,6 +76,8 @@ def test_one_step_matches_cpu_restatement(kernels, dtype):
     # layer 0's new K/V rows come straight from the embedding: same slots, values within the dtype's rounding
     assert (kc_d[0].float().cpu() - kc[0].float()).abs().max().item() < 0.05
     assert torch.equal(model.positions.cpu(), ctx + 1) and torch.equal(model.seq_lens.cpu(), ctx + 2)
+    # the sampled tokens: the reference's default top_k = 1 (nanoPD/engine/model_runner.py:279-284) over the step's logits
+    assert torch.equal(model.token_ids.cpu(), paged_oracle.top_k_sample(model.logits.cpu(), 1))
     assert paged_kernels.check_status(DEV, raise_on_error=False) == 0
 
 
@@ -98,7 +100,26 @@ def test_graph_replays_equal_eager_steps(kernels):
         assert torch.equal(model.token_ids, eager_tokens[i]), f"replay {i}"
     assert torch.equal(model.k_cache, kc_eager)
     assert torch.equal(model.positions.cpu(), ctx + 3)
-    assert model.launches_per_step() == 2 * SHAPE.num_layers
+    assert model.launches_per_step() == 2 * SHAPE.num_layers + 1
+
+
+def test_top_k_10_steps_in_a_graph_draw_fresh_numbers(kernels):
+    """With top_k = 10 (what the reference's workers pass, nanoPD/workers/decode_worker.py:110) the captured step
+    refreshes its uniform numbers inside the graph: every replayed token is one of the ten candidates of that
+    step's logits, and two replays do not reuse the numbers."""
+    dtype = torch.bfloat16
+    model = decoder_step.SyntheticDecoder(DEV, SHAPE, dtype, seed=6, max_position=256, top_k=10)
+    kc, vc, tables, ctx, tokens = make_batch(dtype, seed=7)
+    model.attach_batch(kc.to(DEV), vc.to(DEV), tables.to(DEV), ctx.to(DEV), tokens.to(DEV))
+    model.capture()
+    seen = []
+    for _ in range(3):
+        model.replay()
+        torch.cuda.synchronize()
+        _, ids, _ = paged_oracle.top_k_candidates(model.logits.cpu(), 10)
+        assert all(int(t) in ids[i].tolist() for i, t in enumerate(model.token_ids.cpu()))
+        seen.append(model.uniforms.clone())
+    assert not torch.equal(seen[0], seen[1]) and not torch.equal(seen[1], seen[2])
 
 
 def test_mixed_step_decode_rows_equal_the_decode_only_step(kernels):

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN, load_decode_cases, load_rope_cases
+from conftest import GOLDEN, load_decode_cases, load_rope_cases, load_sampling_cases
 from nanopd_b200 import workloads
 from oracle import paged_oracle
 
@@ -177,3 +177,28 @@ def test_qk_norm_rope_store_oracle_puts_rows_in_their_slots():
         blk, off = int(table[pos // B]), pos % B
         assert torch.equal(kc[blk, :, off], case["k_ref"][t]) and torch.equal(vc[blk, :, off], v[t])
     assert int((kc != 0).any(-1).sum()) == T * Hkv
+
+
+@pytest.mark.parametrize("case", load_sampling_cases(), ids=lambda c: c["name"])
+def test_sampling_oracle_matches_torch_topk_softmax_and_the_reference_top_1(case):
+    """Fixture made by tests/golden/make_golden_sampling.py from torch.nan_to_num / topk / softmax and the
+    reference's top_k_sample (nanoPD/engine/model_runner.py:279-284): values and probabilities bit for bit,
+    ids on the rows whose k-th value is not tied, the top-1 token wherever the maximum is unique."""
+    vals, ids, probs = paged_oracle.top_k_candidates(case["logits"], case["top_k"])
+    assert torch.equal(vals, case["values"])
+    assert torch.equal(probs, case["probabilities"])
+    rows = case["untied_rows"]
+    assert torch.equal(ids[rows], case["ids"][rows])
+    greedy = paged_oracle.top_k_sample(case["logits"], 1)
+    assert torch.equal(greedy[case["top_1_unique"]], case["reference_top_1"][case["top_1_unique"]])
+
+
+def test_sampling_oracle_draw_is_the_inverse_cdf():
+    logits = torch.tensor([[0.0, 1.0, 3.0, 2.0, -1.0]])
+    p = torch.softmax(torch.tensor([3.0, 2.0, 1.0]), 0)
+    for u, want in ((0.0, 2), (float(p[0]) - 1e-3, 2), (float(p[0]) + 1e-3, 3), (float(p[0] + p[1]) + 1e-3, 1),
+                    (0.9999, 1)):
+        assert int(paged_oracle.top_k_sample(logits, 3, torch.tensor([u]))[0]) == want
+    assert int(paged_oracle.top_k_sample(logits, 1)[0]) == 2
+    ties = torch.zeros(1, 6)
+    assert paged_oracle.top_k_candidates(ties, 3)[1].tolist() == [[0, 1, 2]]       # equal values: the lower id first
