@@ -220,7 +220,9 @@ int npd_qk_norm_rope_store(void *q_out, const void *q, const void *k, const void
  * ceil(vocab / 16384) * top_k <= 4096; rows must start on 16-byte boundaries.
  * `workspace`: device memory of at least npd_top_k_sample_workspace_bytes(...), zeroed once
  * by the caller and then reusable by any later call on the same stream (the kernel leaves
- * its arrival counters at zero).                                                          */
+ * its arrival counters at zero).  Its first int32 collects NPD_STATUS_* bits: the only one
+ * this kernel raises is NPD_STATUS_WAIT_TIMEOUT (a bounded wait for a bulk copy ran out;
+ * the tokens of that launch are then undefined — zero the workspace before reusing it).   */
 #define NPD_SAMPLE_MAX_TOP_K 64
 int64_t npd_top_k_sample_workspace_bytes(int64_t num_rows, int64_t vocab, int top_k);
 int npd_top_k_sample(int64_t *out_ids, const void *logits, const float *uniforms, int64_t num_rows,

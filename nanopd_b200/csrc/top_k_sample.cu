@@ -6,8 +6,10 @@
 // logits' dtype, one draw.  Here one launch serves every row of the step and leaves the tokens on the device.
 //
 // The work is a single pass over T x V logits, so HBM bounds it.  A CTA walks a run of slices of one row (a whole
-// row when there are enough rows to fill the GPU); a slice is 8 x 16 bytes per thread, held in registers, and the
-// next slice's loads are in flight while the current one is examined.  The k best are found without sorting:
+// row when there are enough rows to fill the GPU); a slice is 32 KiB, brought into a ring of three shared-memory
+// stages by one bulk asynchronous copy each (cp.async.bulk on an mbarrier, no multicast), so that two slices per
+// CTA — four per SM — are on their way while one is examined and no register holds data in flight.  The k best
+// are found without sorting:
 //   * first slice: every group of 2 or 4 threads reduces the maximum of its logits; the k-th largest of the group
 //     maxima is a lower bound of the slice's k-th largest logit (k groups hold a logit at least that large).  The
 //     logits not below it (about -G ln(1 - k/G) on unordered data, G groups) are gathered into shared memory and
@@ -30,14 +32,18 @@
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kLoads = 8;                       // 16-byte loads per thread and slice: 64 (16-bit) or 32 (fp32) logits
+constexpr int kLoads = 8;                       // 16-byte pieces per thread and slice: 64 (16-bit) or 32 (fp32) logits
+constexpr int kSliceBytes = kThreads * kLoads * 16;
+constexpr int kStages = 3;                      // ring of slices in shared memory; two CTAs of 96 KiB fit an SM
+constexpr long long kWaitLimit = 400000000LL;   // SM clocks a thread waits for a slice before it gives up (~0.2 s)
 constexpr int kMaxGroups = 128;
 constexpr int kMaxTopK = NPD_SAMPLE_MAX_TOP_K;
 constexpr int kSliceCandidates = 1024;          // more logits than this past the bound in one slice: arg-max rounds
 constexpr int kPool = 4096;                     // candidates of one row at the merge: chunks x k
 constexpr int kSmallestSlice = kThreads * kLoads * 4;
-constexpr int64_t kTicketBytes = 65536;         // head of the workspace: one arrival counter per row of a launch
-constexpr int64_t kRowsPerLaunch = kTicketBytes / 4;
+constexpr int64_t kTicketBytes = 65536;         // head of the workspace: a status word, then one arrival counter per row
+constexpr int64_t kTicketOffset = 256;
+constexpr int64_t kRowsPerLaunch = (kTicketBytes - kTicketOffset) / 4;
 
 struct SampleParams {
     const void *logits;
@@ -46,6 +52,7 @@ struct SampleParams {
     float *cand_value;      // [rows of a launch, chunks, k]
     int32_t *cand_id;
     uint32_t *tickets;
+    int32_t *status;
     int64_t row_stride;
     int64_t first_row;
     int vocab;
@@ -56,14 +63,6 @@ struct SampleParams {
 
 __device__ __forceinline__ bool before(float va, int ia, float vb, int ib) {
     return va > vb || (va == vb && ia < ib);
-}
-
-__device__ __forceinline__ uint4 load_streaming(const void *p) {
-    uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(p));
-    return r;
 }
 
 // nan_to_num(nan = 0, posinf = 1e4, neginf = -1e4), the replacement already rounded to the logits' dtype
@@ -158,32 +157,33 @@ template <> struct Logit<__nv_bfloat16> {
     }
 };
 
-// One slice of a row into registers: kLoads 16-byte pieces per thread, piece j of thread t at logits
-// base + (j * kThreads + t) * kVec.  Past the end of the row the most negative finite value is filled in.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Piece j of thread t of the slice in `stage`: the 16 bytes at logits base + (j * kThreads + t) * kVec.  The bulk
+// copy stops at the last whole 16 bytes of the row; a piece that reaches past the row's end is put together from
+// global memory, the most negative finite value standing in for what is not there.
 template <typename T>
-__device__ __forceinline__ void load_slice(const T *logits, int vocab, int base, int tid, uint4 (&raw)[kLoads]) {
+__device__ __forceinline__ uint4 piece_of(const uint8_t *stage, const T *logits, int vocab, int base, int j, int tid) {
     constexpr int kVec = 16 / sizeof(T);
+    const int e0 = base + (j * kThreads + tid) * kVec;
+    if (e0 + kVec <= vocab) return *reinterpret_cast<const uint4 *>(stage + (j * kThreads + tid) * 16);
+    uint32_t w[4];
 #pragma unroll
-    for (int j = 0; j < kLoads; ++j) {
-        const int e0 = base + (j * kThreads + tid) * kVec;
-        if (e0 + kVec <= vocab) {
-            raw[j] = load_streaming(logits + e0);
+    for (int i = 0; i < 4; ++i) {
+        if (sizeof(T) == 4) {
+            w[i] = e0 + i < vocab ? reinterpret_cast<const uint32_t *>(logits)[e0 + i] : Logit<T>::kLowestBits;
         } else {
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (sizeof(T) == 4) {
-                    w[i] = e0 + i < vocab ? reinterpret_cast<const uint32_t *>(logits)[e0 + i] : Logit<T>::kLowestBits;
-                } else {
-                    const uint16_t *h = reinterpret_cast<const uint16_t *>(logits);
-                    const uint32_t lo = e0 + 2 * i < vocab ? h[e0 + 2 * i] : Logit<T>::kLowestBits;
-                    const uint32_t hi = e0 + 2 * i + 1 < vocab ? h[e0 + 2 * i + 1] : Logit<T>::kLowestBits;
-                    w[i] = lo | (hi << 16);
-                }
-            }
-            raw[j] = make_uint4(w[0], w[1], w[2], w[3]);
+            const uint16_t *h = reinterpret_cast<const uint16_t *>(logits);
+            const uint32_t lo = e0 + 2 * i < vocab ? h[e0 + 2 * i] : Logit<T>::kLowestBits;
+            const uint32_t hi = e0 + 2 * i + 1 < vocab ? h[e0 + 2 * i + 1] : Logit<T>::kLowestBits;
+            w[i] = lo | (hi << 16);
         }
     }
+    return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 template <typename T>
@@ -191,8 +191,10 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     using L = Logit<T>;
     constexpr int kVec = 16 / sizeof(T);
     constexpr int kSlice = kThreads * kLoads * kVec;
-    __shared__ float pool_value[kPool];
-    __shared__ int pool_id[kPool];
+    extern __shared__ __align__(128) uint8_t ring[];        // kStages slices; reused for the merge of the chunks' lists
+    __shared__ uint64_t full[kStages];
+    __shared__ float pool_value[kSliceCandidates];
+    __shared__ int pool_id[kSliceCandidates];
     __shared__ float group_max[kMaxGroups];
     __shared__ float warp_value[kThreads / 32];
     __shared__ int warp_id[kThreads / 32];
@@ -220,8 +222,8 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     int n_top = 0, side = 0, bank = 0, pooled = 0;
     float tau = -INFINITY;
 
-    // One slice, already in registers.
-    auto examine = [&](const uint4 (&cur)[kLoads], const int s) {
+    // One slice, already in shared memory.
+    auto examine = [&](const uint8_t *stage, const int s) {
         const int base = s * kSlice;
         const bool first = s == s_begin;
 
@@ -233,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
             // can only lower a group's maximum below the one nan_to_num would give, which keeps the bound valid.
             float m = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < kLoads; ++j) m = L::max_of(cur[j], m);
+            for (int j = 0; j < kLoads; ++j) m = L::max_of(piece_of<T>(stage, logits, p.vocab, base, j, tid), m);
             if (m != m) m = 0.f;                            // unreachable with fmaxf; kept for a max that returns NaN
             else if (fabsf(m) > FLT_MAX) m = copysignf(replacement, m);
             const int group_threads = k <= 16 ? 4 : 2;
@@ -261,9 +263,10 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         const bool careful = limit < -replacement || (first && limit == -replacement);
 #pragma unroll
         for (int j = 0; j < kLoads; ++j) {
-            if (careful || L::any_past(cur[j], limit, first)) {
+            const uint4 raw = piece_of<T>(stage, logits, p.vocab, base, j, tid);
+            if (careful || L::any_past(raw, limit, first)) {
                 float f[kVec];
-                L::widen(cur[j], f);
+                L::widen(raw, f);
                 const int e0 = base + (j * kThreads + tid) * kVec;
 #pragma unroll
                 for (int i = 0; i < kVec; ++i) {
@@ -283,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
 
         if (count > kSliceCandidates) {
             // ---- data that defeats the limit (long runs of equal or rising values): the slice's own k best by
-            // k rounds of a block-wide arg-max over the registers, placed behind what earlier slices pooled ------
+            // k rounds of a block-wide arg-max over the slice, placed behind what earlier slices pooled ------
             uint64_t taken = 0;
             count = pooled;
             for (int r = 0; r < k; ++r) {
@@ -292,11 +295,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
 #pragma unroll
                 for (int j = 0; j < kLoads; ++j) {
                     float f[kVec];
-                    uint4 w = cur[j];
-                    // opaque to the compiler, so that the conversions stay inside the round instead of being
-                    // hoisted into registers that every path of the kernel would then pay for
-                    asm volatile("" : "+r"(w.x), "+r"(w.y), "+r"(w.z), "+r"(w.w));
-                    L::widen(w, f);
+                    L::widen(piece_of<T>(stage, logits, p.vocab, base, j, tid), f);
                     const int e0 = base + (j * kThreads + tid) * kVec;
 #pragma unroll
                     for (int i = 0; i < kVec; ++i) {
@@ -370,19 +369,48 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         }
     };
 
-    // Two register buffers take turns: while one slice is examined the next is in flight, and the buffer just
-    // examined is refilled at once with the slice after that — up to 2 x 8 x 16 bytes per thread on their way.
-    uint4 buf_a[kLoads], buf_b[kLoads];
-    load_slice<T>(logits, p.vocab, s_begin * kSlice, tid, buf_a);
-    if (s_begin + 1 < s_end) load_slice<T>(logits, p.vocab, (s_begin + 1) * kSlice, tid, buf_b);
-    for (int s = s_begin; s < s_end; s += 2) {
-        examine(buf_a, s);
-        if (s + 2 < s_end) load_slice<T>(logits, p.vocab, (s + 2) * kSlice, tid, buf_a);
-        if (s + 1 < s_end) {
-            examine(buf_b, s + 1);
-            if (s + 3 < s_end) load_slice<T>(logits, p.vocab, (s + 3) * kSlice, tid, buf_b);
+    // The ring: thread 0 starts the copy of slice t into stage t % kStages and, once the slice in a stage has been
+    // examined, of the slice kStages further on.  Every wait is bounded: a thread that gives up stops waiting,
+    // examines whatever the stage holds (all accesses stay inside the ring and the row) and the launch reports
+    // NPD_STATUS_WAIT_TIMEOUT; thread 0 then gives the copies it started a last bounded chance to land.
+    const int n_slices = s_end - s_begin;
+    const int64_t row_bytes = static_cast<int64_t>(p.vocab) * sizeof(T);
+    auto start_copy = [&](int t) {
+        const int64_t byte0 = static_cast<int64_t>(s_begin + t) * kSliceBytes;
+        const int64_t left = row_bytes - byte0;
+        const uint32_t bytes = left >= kSliceBytes ? kSliceBytes : static_cast<uint32_t>(left & ~15ll);
+        const uint32_t bar = npd::smem_u32(&full[t % kStages]);
+        if (bytes) {
+            npd::mbar_expect_tx(bar, bytes);
+            bulk_g2s(npd::smem_u32(ring + (t % kStages) * kSliceBytes), reinterpret_cast<const uint8_t *>(logits) + byte0,
+                     bytes, bar);
+        } else {
+            npd::mbar_arrive(bar);                      // fewer than 16 bytes of the row left: read piecewise
+        }
+    };
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) npd::mbar_init(npd::smem_u32(&full[i]), 1);
+        npd::mbar_fence_init();
+        npd::fence_proxy_async_smem();
+        for (int t = 0; t < kStages && t < n_slices; ++t) start_copy(t);
+    }
+    __syncthreads();
+    bool lost = false;
+    for (int t = 0; t < n_slices; ++t) {
+        if (!lost && !npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit)) lost = true;
+        examine(ring + (t % kStages) * kSliceBytes, s_begin + t);   // ends behind a barrier that follows every read
+        if (tid == 0 && !lost && t + kStages < n_slices) {
+            npd::fence_proxy_async_smem();
+            start_copy(t + kStages);
         }
     }
+    if (lost) {
+        if (p.status) atomicOr(p.status, NPD_STATUS_WAIT_TIMEOUT);
+        if (tid == 0)
+            for (int t = 0; t < n_slices; ++t)
+                npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit);
+    }
+    __syncthreads();
 
     if (p.chunks > 1) {
         // ---- the last CTA of the row to arrive merges the chunks' lists ------------------------------------
@@ -398,20 +426,22 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         __syncthreads();
         if (!is_last) return;
         __threadfence();
-        const int total = p.chunks * k;
+        const int total = p.chunks * k;                     // at most kPool entries: 32 KiB of the ring, now idle
+        float *merge_value = reinterpret_cast<float *>(ring);
+        int *merge_id = reinterpret_cast<int *>(ring) + kPool;
         const float *row_value = p.cand_value + static_cast<int64_t>(row) * total;
         const int32_t *row_id = p.cand_id + static_cast<int64_t>(row) * total;
         for (int i = tid; i < total; i += kThreads) {
-            pool_value[i] = __ldcg(row_value + i);
-            pool_id[i] = __ldcg(row_id + i);
+            merge_value[i] = __ldcg(row_value + i);
+            merge_id[i] = __ldcg(row_id + i);
         }
         __syncthreads();
         for (int i = tid; i < total; i += kThreads) {
-            const int mi = pool_id[i];
+            const int mi = merge_id[i];
             if (mi < 0) continue;
-            const float mv = pool_value[i];
+            const float mv = merge_value[i];
             int rank = 0;
-            for (int j = 0; j < total; ++j) rank += before(pool_value[j], pool_id[j], mv, mi);   // an empty entry is -inf
+            for (int j = 0; j < total; ++j) rank += before(merge_value[j], merge_id[j], mv, mi);   // an empty entry is -inf
             if (rank < k) {
                 top_value[0][rank] = mv;
                 top_id[0][rank] = mi;
@@ -457,6 +487,20 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
 
 int slices_of(int64_t vocab, int slice) { return static_cast<int>((vocab + slice - 1) / slice); }
 
+template <typename T>
+cudaError_t launch(const SampleParams &p, unsigned grid, cudaStream_t stream) {
+    constexpr int kRingBytes = kStages * kSliceBytes;
+    static_assert(kRingBytes >= kPool * 8, "the merge reuses the ring");
+    // Set on every call: the attribute is per device and cheap; the maximum carve-out lets two CTAs share an SM.
+    cudaError_t e = cudaFuncSetAttribute(top_k_sample_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(top_k_sample_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    top_k_sample_kernel<T><<<grid, kThreads, kRingBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
 }  // namespace
 
 extern "C" int64_t npd_top_k_sample_workspace_bytes(int64_t num_rows, int64_t vocab, int top_k) {
@@ -498,7 +542,8 @@ extern "C" int npd_top_k_sample(int64_t *out_ids, const void *logits, const floa
     p.logits = logits;
     p.uniforms = uniforms;
     p.out = out_ids;
-    p.tickets = static_cast<uint32_t *>(workspace);
+    p.status = static_cast<int32_t *>(workspace);
+    p.tickets = reinterpret_cast<uint32_t *>(static_cast<char *>(workspace) + kTicketOffset);
     p.row_stride = row_stride;
     p.vocab = static_cast<int>(vocab);
     p.slices = slices_of(vocab, kThreads * kLoads * (16 / elem));
@@ -527,10 +572,9 @@ extern "C" int npd_top_k_sample(int64_t *out_ids, const void *logits, const floa
         p.cand_value = reinterpret_cast<float *>(static_cast<char *>(workspace) + kTicketBytes);
         p.cand_id = reinterpret_cast<int32_t *>(p.cand_value + rows * chunks * top_k);
         const unsigned grid = static_cast<unsigned>(rows * chunks);
-        if (dtype == NPD_DTYPE_F16) top_k_sample_kernel<__half><<<grid, kThreads, 0, s>>>(p);
-        else if (dtype == NPD_DTYPE_BF16) top_k_sample_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(p);
-        else top_k_sample_kernel<float><<<grid, kThreads, 0, s>>>(p);
-        NPD_CUDA_TRY(cudaGetLastError());
+        if (dtype == NPD_DTYPE_F16) NPD_CUDA_TRY(launch<__half>(p, grid, s));
+        else if (dtype == NPD_DTYPE_BF16) NPD_CUDA_TRY(launch<__nv_bfloat16>(p, grid, s));
+        else NPD_CUDA_TRY(launch<float>(p, grid, s));
     }
     return NPD_OK;
 }

@@ -39,6 +39,25 @@ def _workspace(device: torch.device, stream_handle: int, nbytes: int) -> torch.T
         return ws
 
 
+def check_status(device=None, raise_on_error: bool = True) -> int:
+    """Reads and clears the status words of the sampler's workspaces on ``device`` (synchronises).  The only bit
+    the sampler raises is the wait time-out (4); the workspace is zeroed again when it is seen."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    with _lock:
+        items = [w for (d, _), w in _workspaces.items() if d == idx]
+    bits = 0
+    for ws in items:
+        word = int(ws[:4].view(torch.int32).item())
+        if word:
+            bits |= word
+            ws.zero_()
+            torch.cuda.synchronize(idx)
+    if bits and raise_on_error:
+        raise RuntimeError(f"nanopd_b200 sampler device status: {bits}")
+    return bits
+
+
 def top_k_sample(logit: torch.Tensor, top_k: int = 1, uniforms: Optional[torch.Tensor] = None,
                  out: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None) -> torch.Tensor:
     """Token ids (int64) drawn from the ``top_k`` largest logits of every row.

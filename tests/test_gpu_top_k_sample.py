@@ -176,6 +176,11 @@ def test_workspace_is_reusable_across_shapes(sampling):
         check_draws(sampling, logits, k, torch.rand(rows))
 
 
+def test_status_word_stays_clear(sampling):
+    sampling.top_k_sample(torch.randn(4, 40000, device=DEV), 3, uniforms=torch.rand(4, device=DEV))
+    assert sampling.check_status(DEV, raise_on_error=False) == 0
+
+
 def test_argument_errors(sampling):
     logits = torch.randn(4, 1024, device=DEV)
     with pytest.raises(RuntimeError):
