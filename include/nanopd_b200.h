@@ -216,8 +216,8 @@ int npd_qk_norm_rope_store(void *q_out, const void *q, const void *k, const void
  *   the draw: the first candidate whose running fp32 sum of p exceeds uniforms[row] * sum(p)
  * `uniforms` (device float32 [num_rows], values in [0, 1)) supplies the randomness, so a
  * caller's generator decides the stream; it may be NULL when top_k == 1 (the arg-max,
- * the reference's default).  top_k in [1, NPD_SAMPLE_MAX_TOP_K], top_k <= vocab,
- * ceil(vocab / 16384) * top_k <= 4096; rows must start on 16-byte boundaries.
+ * the reference's default).  top_k in [1, NPD_SAMPLE_MAX_TOP_K], top_k <= vocab <= 2^30;
+ * rows must start on 16-byte boundaries.
  * `workspace`: device memory of at least npd_top_k_sample_workspace_bytes(...), zeroed once
  * by the caller and then reusable by any later call on the same stream (the kernel leaves
  * its arrival counters at zero).  Its first int32 collects NPD_STATUS_* bits: the only one

@@ -5,24 +5,25 @@
 // nanoPD/workers/decode_worker.py:110): nan_to_num, the k largest logits, a softmax over them in the
 // logits' dtype, one draw.  Here one launch serves every row of the step and leaves the tokens on the device.
 //
-// The work is a single pass over T x V logits, so HBM bounds it.  A CTA walks a run of slices of one row (a whole
-// row when there are enough rows to fill the GPU); a slice is 32 KiB, brought into a ring of three shared-memory
-// stages by one bulk asynchronous copy each (cp.async.bulk on an mbarrier, no multicast), so that two slices per
-// CTA — four per SM — are on their way while one is examined and no register holds data in flight.  The k best
-// are found without sorting:
+// The work is a single pass over T x V logits, so HBM bounds it.  A row is cut into slices of 32 KiB; all slices
+// of all rows are dealt, in order, in equal runs to two persistent CTAs per SM.  A CTA brings its slices into a
+// ring of three shared-memory stages by one bulk asynchronous copy each (cp.async.bulk on an mbarrier, no
+// multicast) — across the ends of rows, so two copies per CTA are on their way while a slice is examined and no
+// register holds data in flight.  The k best of a row (of the CTA's part of it) are found without sorting:
 //   * first slice: every group of 2 or 4 threads reduces the maximum of its logits; the k-th largest of the group
 //     maxima is a lower bound of the slice's k-th largest logit (k groups hold a logit at least that large).  The
 //     logits not below it (about -G ln(1 - k/G) on unordered data, G groups) are gathered into shared memory and
 //     ranked by counting; ranks below k are the k best so far and the k-th of them is the running threshold;
 //   * later slices: only logits ABOVE the threshold are gathered (their ids are larger than every id seen, so an
-//     equal value ranks behind) — k/(slices seen) of them on unordered data — and ranked together with the k
-//     best so far; the scan itself is one conversion and one comparison per logit.
+//     equal value ranks behind) — about k/(slices seen) of them on unordered data — and ranked together with
+//     the k best so far; the scan itself is a packed maximum of each 16 bytes compared with the threshold.
 // Data that defeats the threshold (more than 1024 logits past it in one slice: long runs of equal or rising
-// values) takes k rounds of a block-wide arg-max over that slice instead — slower, same result.  Where a row is
-// shared by several CTAs, each writes its k best to global memory and the last to arrive (a ticket per row, reset
-// by that CTA) merges them.  One warp then computes the probabilities and draws.
+// values) takes k rounds of a block-wide arg-max over that slice instead — slower, same result.  A row that one
+// CTA saw whole is drawn at once; where a run starts or ends inside a row, each CTA writes the k best of its part
+// to global memory and the last to arrive (a ticket per row, reset by that CTA) merges them.  One warp computes
+// the probabilities and draws.
 // Order everywhere: larger value first, equal values by the lower id — which makes the result independent of
-// how the row was cut.
+// how the rows were cut.
 #include <cfloat>
 #include <climits>
 #include <cstdlib>
@@ -39,8 +40,6 @@ constexpr long long kWaitLimit = 400000000LL;   // SM clocks a thread waits for 
 constexpr int kMaxGroups = 128;
 constexpr int kMaxTopK = NPD_SAMPLE_MAX_TOP_K;
 constexpr int kSliceCandidates = 1024;          // more logits than this past the bound in one slice: arg-max rounds
-constexpr int kPool = 4096;                     // candidates of one row at the merge: chunks x k
-constexpr int kSmallestSlice = kThreads * kLoads * 4;
 constexpr int64_t kTicketBytes = 65536;         // head of the workspace: a status word, then one arrival counter per row
 constexpr int64_t kTicketOffset = 256;
 constexpr int64_t kRowsPerLaunch = (kTicketBytes - kTicketOffset) / 4;
@@ -49,7 +48,7 @@ struct SampleParams {
     const void *logits;
     const float *uniforms;
     int64_t *out;
-    float *cand_value;      // [rows of a launch, chunks, k]
+    float *cand_value;      // [rows of a launch, parts_cap, k]
     int32_t *cand_id;
     uint32_t *tickets;
     int32_t *status;
@@ -57,8 +56,9 @@ struct SampleParams {
     int64_t first_row;
     int vocab;
     int slices;             // per row
-    int chunks;             // CTAs per row, each over a run of slices
+    int parts_cap;          // list slots per row in cand_*: the most CTAs one row is spread over
     int top_k;
+    int64_t items;          // rows of this launch x slices, dealt to the CTAs in equal consecutive runs
 };
 
 __device__ __forceinline__ bool before(float va, int ia, float vb, int ib) {
@@ -112,16 +112,13 @@ template <> struct Logit<__half> {
         const float2 f = __half22float2(__hmax2(a, b));
         return fmaxf(m, fmaxf(f.x, f.y));
     }
+    // The NaN-propagating packed maximum of the eight logits decides: past the limit, or a NaN, or neither.
     static __device__ __forceinline__ bool any_past(const uint4 &raw, float limit, bool inclusive) {
-        const __half2 l2 = __float2half2_rn(limit);         // exact: the limit is one of the logits
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        unsigned any = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __half2 x = *reinterpret_cast<const __half2 *>(&w[i]);
-            any |= inclusive ? __hgeu2_mask(x, l2) : __hgtu2_mask(x, l2);
-        }
-        return any != 0;
+        const __half2 a = __hmax2_nan(*reinterpret_cast<const __half2 *>(&w[0]), *reinterpret_cast<const __half2 *>(&w[1]));
+        const __half2 b = __hmax2_nan(*reinterpret_cast<const __half2 *>(&w[2]), *reinterpret_cast<const __half2 *>(&w[3]));
+        const float2 f = __half22float2(__hmax2_nan(a, b));
+        return inclusive ? (!(f.x < limit) || !(f.y < limit)) : (!(f.x <= limit) || !(f.y <= limit));
     }
 };
 template <> struct Logit<__nv_bfloat16> {
@@ -145,15 +142,15 @@ template <> struct Logit<__nv_bfloat16> {
         return fmaxf(m, fmaxf(f.x, f.y));
     }
     static __device__ __forceinline__ bool any_past(const uint4 &raw, float limit, bool inclusive) {
-        const __nv_bfloat162 l2 = __float2bfloat162_rn(limit);
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        unsigned any = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162 *>(&w[i]);
-            any |= inclusive ? __hgeu2_mask(x, l2) : __hgtu2_mask(x, l2);
-        }
-        return any != 0;
+        const __nv_bfloat162 a = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]),
+                                             *reinterpret_cast<const __nv_bfloat162 *>(&w[1]));
+        const __nv_bfloat162 b = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162 *>(&w[2]),
+                                             *reinterpret_cast<const __nv_bfloat162 *>(&w[3]));
+        const __nv_bfloat162 m = __hmax2_nan(a, b);
+        const uint32_t bits = *reinterpret_cast<const uint32_t *>(&m);
+        const float x = __uint_as_float(bits << 16), y = __uint_as_float(bits & 0xffff0000u);
+        return inclusive ? (!(x < limit) || !(y < limit)) : (!(x <= limit) || !(y <= limit));
     }
 };
 
@@ -191,7 +188,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     using L = Logit<T>;
     constexpr int kVec = 16 / sizeof(T);
     constexpr int kSlice = kThreads * kLoads * kVec;
-    extern __shared__ __align__(128) uint8_t ring[];        // kStages slices; reused for the merge of the chunks' lists
+    extern __shared__ __align__(128) uint8_t ring[];        // kStages slices
     __shared__ uint64_t full[kStages];
     __shared__ float pool_value[kSliceCandidates];
     __shared__ int pool_id[kSliceCandidates];
@@ -205,27 +202,26 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     __shared__ int is_last;
 
     const int tid = threadIdx.x;
-    const int row = blockIdx.x / p.chunks;                  // within this launch
-    const int chunk = blockIdx.x - row * p.chunks;
     const int k = p.top_k;
-    const int s_begin = static_cast<int>(static_cast<int64_t>(chunk) * p.slices / p.chunks);
-    const int s_end = static_cast<int>(static_cast<int64_t>(chunk + 1) * p.slices / p.chunks);
-    const T *logits = static_cast<const T *>(p.logits) + (p.first_row + row) * p.row_stride;
+    const int64_t grid = gridDim.x;
+    const int64_t item_begin = blockIdx.x * p.items / grid;
+    const int n_items = static_cast<int>((blockIdx.x + 1) * p.items / grid - item_begin);
+    const T *const all_logits = static_cast<const T *>(p.logits) + p.first_row * p.row_stride;
     const float replacement = L::round(1e4f);
     if (tid < 2) gathered[tid] = 0;
 
-    // The chunk's k best so far live in top_value[side] / top_id[side], best first; n_top of them, and `tau` is
-    // the k-th.  A later slice only has to look at logits ABOVE tau: its ids are all larger than the ids seen, so
-    // an equal value ranks behind.  What it finds collects in the pool (counter gathered[bank]) and is ranked
-    // together with the k best so far once there are k of them (enough to move tau), or at the chunk's end — an
-    // older, lower tau only lets a few more logits through.
+    // This CTA's run of slices may start and end inside a row; a stretch of one row is a "part".  The part's k best
+    // so far live in top_value[side] / top_id[side], best first; n_top of them, and `tau` is the k-th.  A later
+    // slice of the part only has to look at logits ABOVE tau: its ids are all larger than the ids seen, so an equal
+    // value ranks behind.  What it finds collects in the pool (counter gathered[bank]) and is ranked together with
+    // the k best so far once there are k of them (enough to move tau), or at the part's end — an older, lower tau
+    // only lets a few more logits through.
     int n_top = 0, side = 0, bank = 0, pooled = 0;
     float tau = -INFINITY;
 
     // One slice, already in shared memory.
-    auto examine = [&](const uint8_t *stage, const int s) {
+    auto examine = [&](const uint8_t *stage, const T *logits, const int s, const bool first, const bool last) {
         const int base = s * kSlice;
-        const bool first = s == s_begin;
 
         float limit = tau;
         if (first) {
@@ -345,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         }
         pooled = count;
 
-        if (count > 0 && (first || count >= k || s + 1 == s_end)) {
+        if (count > 0 && (first || count >= k || last)) {
             // ---- rank the pooled logits together with the k best so far; ranks below k are the new best ---------
             const int all = count + n_top;
             for (int i = tid; i < all; i += kThreads) {
@@ -369,128 +365,191 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         }
     };
 
-    // The ring: thread 0 starts the copy of slice t into stage t % kStages and, once the slice in a stage has been
-    // examined, of the slice kStages further on.  Every wait is bounded: a thread that gives up stops waiting,
-    // examines whatever the stage holds (all accesses stay inside the ring and the row) and the launch reports
-    // NPD_STATUS_WAIT_TIMEOUT; thread 0 then gives the copies it started a last bounded chance to land.
-    const int n_slices = s_end - s_begin;
+    // The ring: thread 0 starts the copy of this CTA's t-th slice into stage t % kStages and, once the slice in a
+    // stage has been examined, of the slice kStages further on — across the ends of rows, so the copies never stop
+    // while the CTA has work.  Every wait is bounded: a thread that gives up stops waiting, examines whatever the
+    // stage holds (all accesses stay inside the ring and the rows) and the launch reports NPD_STATUS_WAIT_TIMEOUT;
+    // thread 0 then gives the copies it started a last bounded chance to land.
     const int64_t row_bytes = static_cast<int64_t>(p.vocab) * sizeof(T);
     auto start_copy = [&](int t) {
-        const int64_t byte0 = static_cast<int64_t>(s_begin + t) * kSliceBytes;
+        const int64_t item = item_begin + t;
+        const int64_t row = item / p.slices;
+        const int64_t byte0 = (item - row * p.slices) * kSliceBytes;
         const int64_t left = row_bytes - byte0;
         const uint32_t bytes = left >= kSliceBytes ? kSliceBytes : static_cast<uint32_t>(left & ~15ll);
         const uint32_t bar = npd::smem_u32(&full[t % kStages]);
         if (bytes) {
             npd::mbar_expect_tx(bar, bytes);
-            bulk_g2s(npd::smem_u32(ring + (t % kStages) * kSliceBytes), reinterpret_cast<const uint8_t *>(logits) + byte0,
-                     bytes, bar);
+            bulk_g2s(npd::smem_u32(ring + (t % kStages) * kSliceBytes),
+                     reinterpret_cast<const uint8_t *>(all_logits + row * p.row_stride) + byte0, bytes, bar);
         } else {
             npd::mbar_arrive(bar);                      // fewer than 16 bytes of the row left: read piecewise
         }
     };
+
+    // The k best of a whole row are in top_*[side]: probabilities and the draw, by one warp.
+    auto draw = [&](const int row) {
+        if (tid < 32) {
+            // softmax over the k values, rounded to the logits' dtype as torch.softmax returns it
+            const float mx = top_value[side][0];
+            const float e0 = tid < k ? expf(top_value[side][tid] - mx) : 0.f;
+            const float e1 = tid + 32 < k ? expf(top_value[side][tid + 32] - mx) : 0.f;
+            float sum = e0 + e1;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (tid < k) top_prob[tid] = L::round(__fdiv_rn(e0, sum));
+            if (tid + 32 < k) top_prob[tid + 32] = L::round(__fdiv_rn(e1, sum));
+            __syncwarp();
+            if (tid == 0) {
+                int pick = 0;
+                if (k > 1) {
+                    // inverse CDF: the first candidate whose running sum exceeds uniform x total
+                    float all = 0.f;
+                    for (int j = 0; j < k; ++j) all += top_prob[j];
+                    const float target = p.uniforms[p.first_row + row] * all;
+                    float run = 0.f;
+                    pick = k - 1;
+                    for (int j = 0; j < k; ++j) {
+                        run += top_prob[j];
+                        if (run > target) {
+                            pick = j;
+                            break;
+                        }
+                    }
+                }
+                p.out[p.first_row + row] = top_id[side][pick];
+            }
+            __syncwarp();
+        }
+    };
+
+    // The CTA that owns global slice number i: the g with g * items / grid <= i < (g + 1) * items / grid.
+    auto owner_of = [&](int64_t i) { return ((i + 1) * grid - 1) / p.items; };
+
+    // End of this CTA's part of `row`.  A row that one CTA saw whole is drawn at once; otherwise the part's k best go
+    // to the row's list in global memory and the last part to arrive (a ticket per row, reset by it) merges them.
+    auto finish_part = [&](const int row) {
+        const int64_t first_owner = owner_of(static_cast<int64_t>(row) * p.slices);
+        const int parts = static_cast<int>(owner_of(static_cast<int64_t>(row + 1) * p.slices - 1) - first_owner) + 1;
+        if (parts > 1) {
+            const int slot = static_cast<int>(blockIdx.x - first_owner);
+            float *list_value = p.cand_value + (static_cast<int64_t>(row) * p.parts_cap + slot) * k;
+            int32_t *list_id = p.cand_id + (static_cast<int64_t>(row) * p.parts_cap + slot) * k;
+            for (int r = tid; r < k; r += kThreads) {
+                list_value[r] = r < n_top ? top_value[side][r] : -INFINITY;
+                list_id[r] = r < n_top ? top_id[side][r] : -1;
+            }
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) is_last = atomicAdd(&p.tickets[row], 1u) == static_cast<uint32_t>(parts - 1);
+            __syncthreads();
+            if (!is_last) return;
+            __threadfence();
+            const int total = parts * k;                    // at most kSliceCandidates: the pool is idle here
+            const float *row_value = p.cand_value + static_cast<int64_t>(row) * p.parts_cap * k;
+            const int32_t *row_id = p.cand_id + static_cast<int64_t>(row) * p.parts_cap * k;
+            for (int i = tid; i < total; i += kThreads) {
+                pool_value[i] = __ldcg(row_value + i);
+                pool_id[i] = __ldcg(row_id + i);
+            }
+            if (tid == 0) p.tickets[row] = 0;               // every part has arrived: ready for the next launch
+            __syncthreads();
+            for (int i = tid; i < total; i += kThreads) {
+                const int mi = pool_id[i];
+                if (mi < 0) continue;
+                const float mv = pool_value[i];
+                int rank = 0;
+                for (int j = 0; j < total; ++j) rank += before(pool_value[j], pool_id[j], mv, mi);   // an empty entry is -inf
+                if (rank < k) {
+                    top_value[side ^ 1][rank] = mv;
+                    top_id[side ^ 1][rank] = mi;
+                }
+            }
+            side ^= 1;
+            __syncthreads();
+        }
+        draw(row);
+    };
+
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) npd::mbar_init(npd::smem_u32(&full[i]), 1);
         npd::mbar_fence_init();
         npd::fence_proxy_async_smem();
-        for (int t = 0; t < kStages && t < n_slices; ++t) start_copy(t);
+        for (int t = 0; t < kStages && t < n_items; ++t) start_copy(t);
     }
     __syncthreads();
     bool lost = false;
-    for (int t = 0; t < n_slices; ++t) {
+    for (int t = 0; t < n_items; ++t) {
+        const int64_t item = item_begin + t;
+        const int row = static_cast<int>(item / p.slices);
+        const int s = static_cast<int>(item - static_cast<int64_t>(row) * p.slices);
+        const bool first = t == 0 || s == 0;
+        const bool last = t == n_items - 1 || s == p.slices - 1;
+        if (first) {
+            n_top = 0;
+            pooled = 0;
+            tau = -INFINITY;
+        }
         if (!lost && !npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit)) lost = true;
-        examine(ring + (t % kStages) * kSliceBytes, s_begin + t);   // ends behind a barrier that follows every read
-        if (tid == 0 && !lost && t + kStages < n_slices) {
+        examine(ring + (t % kStages) * kSliceBytes, all_logits + row * p.row_stride, s, first, last);
+        // examine() ends behind a barrier that follows every read of the stage
+        if (tid == 0 && !lost && t + kStages < n_items) {
             npd::fence_proxy_async_smem();
             start_copy(t + kStages);
         }
+        if (last) finish_part(row);
     }
     if (lost) {
         if (p.status) atomicOr(p.status, NPD_STATUS_WAIT_TIMEOUT);
         if (tid == 0)
-            for (int t = 0; t < n_slices; ++t)
+            for (int t = 0; t < n_items; ++t)
                 npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit);
-    }
-    __syncthreads();
-
-    if (p.chunks > 1) {
-        // ---- the last CTA of the row to arrive merges the chunks' lists ------------------------------------
-        float *list_value = p.cand_value + (static_cast<int64_t>(row) * p.chunks + chunk) * k;
-        int32_t *list_id = p.cand_id + (static_cast<int64_t>(row) * p.chunks + chunk) * k;
-        for (int r = tid; r < k; r += kThreads) {
-            list_value[r] = r < n_top ? top_value[side][r] : -INFINITY;
-            list_id[r] = r < n_top ? top_id[side][r] : -1;
-        }
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) is_last = atomicAdd(&p.tickets[row], 1u) == static_cast<uint32_t>(p.chunks - 1);
-        __syncthreads();
-        if (!is_last) return;
-        __threadfence();
-        const int total = p.chunks * k;                     // at most kPool entries: 32 KiB of the ring, now idle
-        float *merge_value = reinterpret_cast<float *>(ring);
-        int *merge_id = reinterpret_cast<int *>(ring) + kPool;
-        const float *row_value = p.cand_value + static_cast<int64_t>(row) * total;
-        const int32_t *row_id = p.cand_id + static_cast<int64_t>(row) * total;
-        for (int i = tid; i < total; i += kThreads) {
-            merge_value[i] = __ldcg(row_value + i);
-            merge_id[i] = __ldcg(row_id + i);
-        }
-        __syncthreads();
-        for (int i = tid; i < total; i += kThreads) {
-            const int mi = merge_id[i];
-            if (mi < 0) continue;
-            const float mv = merge_value[i];
-            int rank = 0;
-            for (int j = 0; j < total; ++j) rank += before(merge_value[j], merge_id[j], mv, mi);   // an empty entry is -inf
-            if (rank < k) {
-                top_value[0][rank] = mv;
-                top_id[0][rank] = mi;
-            }
-        }
-        side = 0;
-        __syncthreads();
-    }
-
-    if (tid < 32) {
-        // softmax over the k values, rounded to the logits' dtype as torch.softmax returns it
-        const float mx = top_value[side][0];
-        const float e0 = tid < k ? expf(top_value[side][tid] - mx) : 0.f;
-        const float e1 = tid + 32 < k ? expf(top_value[side][tid + 32] - mx) : 0.f;
-        float sum = e0 + e1;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-        if (tid < k) top_prob[tid] = L::round(__fdiv_rn(e0, sum));
-        if (tid + 32 < k) top_prob[tid + 32] = L::round(__fdiv_rn(e1, sum));
-        __syncwarp();
-        if (tid == 0) {
-            int pick = 0;
-            if (k > 1) {
-                // inverse CDF: the first candidate whose running sum exceeds uniform x total
-                float all = 0.f;
-                for (int j = 0; j < k; ++j) all += top_prob[j];
-                const float target = p.uniforms[p.first_row + row] * all;
-                float run = 0.f;
-                pick = k - 1;
-                for (int j = 0; j < k; ++j) {
-                    run += top_prob[j];
-                    if (run > target) {
-                        pick = j;
-                        break;
-                    }
-                }
-            }
-            p.out[p.first_row + row] = top_id[side][pick];
-            if (p.chunks > 1) p.tickets[row] = 0;       // every CTA of the row has arrived: ready for the next launch
-        }
     }
 }
 
 int slices_of(int64_t vocab, int slice) { return static_cast<int>((vocab + slice - 1) / slice); }
 
+// How one launch is dealt out: rows x slices items in equal consecutive runs over at most two CTAs per SM, fewer
+// where a row would otherwise be spread over more parts than the merge has room for.
+struct Plan {
+    int slices;
+    int64_t items;
+    int grid;
+    int parts_cap;
+};
+
+Plan plan_for(int64_t rows, int64_t vocab, int elem, int top_k, int sms) {
+    Plan plan;
+    plan.slices = slices_of(vocab, kThreads * kLoads * (16 / elem));
+    plan.items = rows * plan.slices;
+    int64_t grid = plan.items < 2 * sms ? plan.items : 2 * sms;
+    if (const char *forced = getenv("NPD_SAMPLE_CTAS")) {                   // for experiments
+        const int64_t g = atoll(forced);
+        if (g >= 1 && g <= plan.items) grid = g;
+    }
+    const int max_parts = kSliceCandidates / top_k;
+    int parts = 1;
+    for (;; --grid) {
+        const int64_t shortest = plan.items / grid;                         // a run is at least this long
+        parts = static_cast<int>((plan.slices + shortest - 1) / shortest) + 1;
+        if (parts > plan.slices) parts = plan.slices;
+        if (parts <= max_parts || grid == 1) break;
+    }
+    plan.grid = static_cast<int>(grid);
+    plan.parts_cap = parts;
+    return plan;
+}
+
+int sms_of_current_device() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 148;
+    const int sms = npd::sm_count(device);
+    return sms > 0 ? sms : 148;
+}
+
 template <typename T>
 cudaError_t launch(const SampleParams &p, unsigned grid, cudaStream_t stream) {
     constexpr int kRingBytes = kStages * kSliceBytes;
-    static_assert(kRingBytes >= kPool * 8, "the merge reuses the ring");
     // Set on every call: the attribute is per device and cheap; the maximum carve-out lets two CTAs share an SM.
     cudaError_t e = cudaFuncSetAttribute(top_k_sample_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
     if (e != cudaSuccess) return e;
@@ -504,11 +563,11 @@ cudaError_t launch(const SampleParams &p, unsigned grid, cudaStream_t stream) {
 }  // namespace
 
 extern "C" int64_t npd_top_k_sample_workspace_bytes(int64_t num_rows, int64_t vocab, int top_k) {
-    if (num_rows <= 0 || vocab <= 0 || top_k <= 0) return kTicketBytes;
+    if (num_rows <= 0 || vocab <= 0 || top_k <= 0 || top_k > kMaxTopK) return kTicketBytes;
     const int64_t rows = num_rows < kRowsPerLaunch ? num_rows : kRowsPerLaunch;
-    int64_t chunks = slices_of(vocab, kSmallestSlice);
-    if (chunks * top_k > kPool) chunks = kPool / top_k;
-    return kTicketBytes + rows * chunks * top_k * 8;
+    const int sms = sms_of_current_device();
+    const int a = plan_for(rows, vocab, 2, top_k, sms).parts_cap, b = plan_for(rows, vocab, 4, top_k, sms).parts_cap;
+    return kTicketBytes + rows * (a > b ? a : b) * top_k * 8;               // whichever dtype the logits have
 }
 
 extern "C" int npd_top_k_sample(int64_t *out_ids, const void *logits, const float *uniforms, int64_t num_rows,
@@ -534,9 +593,7 @@ extern "C" int npd_top_k_sample(int64_t *out_ids, const void *logits, const floa
     NPD_REQUIRE(workspace_bytes >= npd_top_k_sample_workspace_bytes(num_rows, vocab, top_k), NPD_ERR_WORKSPACE,
                 "npd_top_k_sample: workspace of %lld bytes, %lld needed", (long long)workspace_bytes,
                 (long long)npd_top_k_sample_workspace_bytes(num_rows, vocab, top_k));
-    int device = 0;
-    NPD_CUDA_TRY(cudaGetDevice(&device));
-    const int sms = npd::sm_count(device);
+    const int sms = sms_of_current_device();
 
     SampleParams p;
     p.logits = logits;
@@ -546,32 +603,21 @@ extern "C" int npd_top_k_sample(int64_t *out_ids, const void *logits, const floa
     p.tickets = reinterpret_cast<uint32_t *>(static_cast<char *>(workspace) + kTicketOffset);
     p.row_stride = row_stride;
     p.vocab = static_cast<int>(vocab);
-    p.slices = slices_of(vocab, kThreads * kLoads * (16 / elem));
     p.top_k = top_k;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     for (int64_t first = 0; first < num_rows; first += kRowsPerLaunch) {
         const int64_t rows = num_rows - first < kRowsPerLaunch ? num_rows - first : kRowsPerLaunch;
-        // CTAs per row: the split that needs the fewest slice-times, counting a wave of CTAs as its slices plus one
-        // for the first bound and the hand-over, and a little per extra list to merge.
-        int64_t chunks = 1;
-        double best = 0;
-        for (int64_t c = 1; c <= p.slices && c * top_k <= kPool; ++c) {
-            const int64_t waves = (rows * c + 2 * sms - 1) / (2 * sms);          // two CTAs fit an SM
-            const double cost = static_cast<double>(waves) * ((p.slices + c - 1) / c + 1.0) + 0.05 * c;
-            if (c == 1 || cost < best) {
-                best = cost;
-                chunks = c;
-            }
-        }
-        if (const char *forced = getenv("NPD_SAMPLE_CHUNKS")) {                  // for experiments
-            const int64_t c = atoll(forced);
-            if (c >= 1 && c <= p.slices && c * top_k <= kPool) chunks = c;
-        }
-        p.chunks = static_cast<int>(chunks);
+        const Plan plan = plan_for(rows, vocab, elem, top_k, sms);
+        NPD_REQUIRE(plan.parts_cap * top_k <= kSliceCandidates, NPD_ERR_UNSUPPORTED,
+                    "npd_top_k_sample: vocabulary %lld x top_k %d needs more than %d candidates per row",
+                    (long long)vocab, top_k, kSliceCandidates);
+        p.slices = plan.slices;
+        p.items = plan.items;
+        p.parts_cap = plan.parts_cap;
         p.first_row = first;
         p.cand_value = reinterpret_cast<float *>(static_cast<char *>(workspace) + kTicketBytes);
-        p.cand_id = reinterpret_cast<int32_t *>(p.cand_value + rows * chunks * top_k);
-        const unsigned grid = static_cast<unsigned>(rows * chunks);
+        p.cand_id = reinterpret_cast<int32_t *>(p.cand_value + rows * plan.parts_cap * top_k);
+        const unsigned grid = static_cast<unsigned>(plan.grid);
         if (dtype == NPD_DTYPE_F16) NPD_CUDA_TRY(launch<__half>(p, grid, s));
         else if (dtype == NPD_DTYPE_BF16) NPD_CUDA_TRY(launch<__nv_bfloat16>(p, grid, s));
         else NPD_CUDA_TRY(launch<float>(p, grid, s));
