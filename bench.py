@@ -742,6 +742,38 @@ def run_gpu_arm(args):
         except Exception as exc:  # noqa: BLE001
             extras["fused_norm_rope_store_error"] = str(exc)[:200]
         try:
+            # batched top-k sampling over the step's logits: the batch's rows x the Qwen3 vocabulary, bf16; five
+            # buffers (389 MB, larger than L2) taken in turn inside one CUDA graph, so neither L2 nor the host's
+            # launch rate enters the figure.  The library kernels torch would run stand beside it.
+            from nanopd_b200 import sampling
+            V_s, nbuf = 151936, 5
+            logit_bufs = [(2.5 * torch.randn(S, V_s, device=dev)).to(torch.bfloat16) for _ in range(nbuf)]
+            uni = torch.rand(S, device=dev)
+            tok = torch.empty(S, dtype=torch.int64, device=dev)
+            bytes_s = S * V_s * 2 + S * 12
+            entry = {"rows": S, "vocab": V_s, "dtype": "bf16", "algorithmic_bytes": bytes_s}
+            side_s = torch.cuda.Stream(device=dev)
+            for k_s in (1, 10):
+                with torch.cuda.stream(side_s):
+                    sampling.top_k_sample(logit_bufs[0], k_s, uniforms=uni, out=tok)
+                    side_s.synchronize()
+                    graph_s = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph_s, stream=side_s):
+                        for lb in logit_bufs:
+                            sampling.top_k_sample(lb, k_s, uniforms=uni, out=tok)
+                graph_s.replay()
+                ms_s = timed(graph_s.replay, 10) / nbuf
+                entry[f"top_{k_s}"] = {"us": round(ms_s * 1e3, 2), "gbs": round(bytes_s / (ms_s * 1e-3) / 1e9, 1),
+                                       "frac_of_hbm_peak": round(bytes_s / (ms_s * 1e-3) / 1e9 / measured_peak_gbs()[0], 3)}
+            it = iter(range(10 ** 9))
+            entry["torch_argmax_us"] = round(timed(lambda: torch.argmax(logit_bufs[next(it) % nbuf], dim=-1), 20) * 1e3, 2)
+            entry["torch_topk_10_us"] = round(timed(lambda: torch.topk(logit_bufs[next(it) % nbuf], 10), 20) * 1e3, 2)
+            entry["status"] = sampling.check_status(dev, raise_on_error=False)
+            extras["top_k_sample"] = entry
+            del logit_bufs
+        except Exception as exc:  # noqa: BLE001
+            extras["top_k_sample_error"] = str(exc)[:200]
+        try:
             # the same launch on the interleaved cache layouts of the reference's split-K op
             k_il = b.k_cache.view(b.k_cache.size(0), Hkv, B, D // 8, 8).permute(0, 1, 3, 2, 4).contiguous()
             v_il = b.v_cache.permute(0, 1, 3, 2).contiguous()

@@ -61,8 +61,10 @@ struct SampleParams {
     int64_t items;          // rows of this launch x slices, dealt to the CTAs in equal consecutive runs
 };
 
+// (value, id) order: larger value first, equal values by the lower id.  Bitwise on purpose: no branches in the
+// counting loops.
 __device__ __forceinline__ bool before(float va, int ia, float vb, int ib) {
-    return va > vb || (va == vb && ia < ib);
+    return (va > vb) | ((va == vb) & (ia < ib));
 }
 
 // nan_to_num(nan = 0, posinf = 1e4, neginf = -1e4), the replacement already rounded to the logits' dtype
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     __shared__ uint64_t full[kStages];
     __shared__ float pool_value[kSliceCandidates];
     __shared__ int pool_id[kSliceCandidates];
-    __shared__ float group_max[kMaxGroups];
+    __shared__ __align__(16) float group_max[kMaxGroups];
     __shared__ float warp_value[kThreads / 32];
     __shared__ int warp_id[kThreads / 32];
     __shared__ float top_value[2][kMaxTopK], top_prob[kMaxTopK];
@@ -234,19 +236,20 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
             for (int j = 0; j < kLoads; ++j) m = L::max_of(piece_of<T>(stage, logits, p.vocab, base, j, tid), m);
             if (m != m) m = 0.f;                            // unreachable with fmaxf; kept for a max that returns NaN
             else if (fabsf(m) > FLT_MAX) m = copysignf(replacement, m);
-            const int group_threads = k <= 16 ? 4 : 2;
-            const int groups = kThreads / group_threads;
+            const int group_shift = k <= 16 ? 2 : 1;        // threads per group: 4 or 2
+            const int groups = kThreads >> group_shift;
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            if (group_threads == 4) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-            if (tid % group_threads == 0) group_max[tid / group_threads] = m;
+            if (group_shift == 2) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            if ((tid & ((1 << group_shift) - 1)) == 0) group_max[tid >> group_shift] = m;
             __syncthreads();
             if (tid < groups) {
                 const float mine = group_max[tid];
                 int rank = 0;
-#pragma unroll 8
-                for (int j = 0; j < groups; ++j) {
-                    const float other = group_max[j];
-                    rank += (other > mine) || (other == mine && j < tid);
+#pragma unroll 4
+                for (int j = 0; j < groups; j += 4) {
+                    const float4 other = *reinterpret_cast<const float4 *>(&group_max[j]);
+                    rank += before(other.x, j, mine, tid) + before(other.y, j + 1, mine, tid) +
+                            before(other.z, j + 2, mine, tid) + before(other.w, j + 3, mine, tid);
                 }
                 if (rank == k - 1) bound = mine;
             }
@@ -257,22 +260,35 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         // ---- gather the logits past the limit (not below it in the first slice, above it later) ---------------
         // -inf only matters when its replacement, -1e4, would pass the limit.
         const bool careful = limit < -replacement || (first && limit == -replacement);
+        // First one bit per 16-byte piece, all eight pieces independent of each other; then the few pieces that
+        // hold something.
+        unsigned hits = 0;
+        if (base + kSlice <= p.vocab) {
 #pragma unroll
-        for (int j = 0; j < kLoads; ++j) {
-            const uint4 raw = piece_of<T>(stage, logits, p.vocab, base, j, tid);
-            if (careful || L::any_past(raw, limit, first)) {
-                float f[kVec];
-                L::widen(raw, f);
-                const int e0 = base + (j * kThreads + tid) * kVec;
+            for (int j = 0; j < kLoads; ++j) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(stage + (j * kThreads + tid) * 16);
+                hits |= static_cast<unsigned>(L::any_past(raw, limit, first)) << j;
+            }
+        } else {
 #pragma unroll
-                for (int i = 0; i < kVec; ++i) {
-                    const float x = replace_special(f[i], replacement);
-                    if ((first ? x >= limit : x > limit) && e0 + i < p.vocab) {
-                        const int pos = atomicAdd(&gathered[bank], 1);
-                        if (pos < kSliceCandidates) {
-                            pool_value[pos] = x;
-                            pool_id[pos] = e0 + i;
-                        }
+            for (int j = 0; j < kLoads; ++j)
+                hits |= static_cast<unsigned>(L::any_past(piece_of<T>(stage, logits, p.vocab, base, j, tid), limit, first)) << j;
+        }
+        if (careful) hits = (1u << kLoads) - 1;
+        while (hits) {
+            const int j = __ffs(hits) - 1;
+            hits &= hits - 1;
+            float f[kVec];
+            L::widen(piece_of<T>(stage, logits, p.vocab, base, j, tid), f);
+            const int e0 = base + (j * kThreads + tid) * kVec;
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) {
+                const float x = replace_special(f[i], replacement);
+                if ((first ? x >= limit : x > limit) && e0 + i < p.vocab) {
+                    const int pos = atomicAdd(&gathered[bank], 1);
+                    if (pos < kSliceCandidates) {
+                        pool_value[pos] = x;
+                        pool_id[pos] = e0 + i;
                     }
                 }
             }
@@ -348,7 +364,9 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
                 const float mv = i < count ? pool_value[i] : top_value[side][i - count];
                 const int mi = i < count ? pool_id[i] : top_id[side][i - count];
                 int rank = 0;
+#pragma unroll 4
                 for (int j = 0; j < count; ++j) rank += before(pool_value[j], pool_id[j], mv, mi);
+#pragma unroll 4
                 for (int j = 0; j < n_top; ++j) rank += before(top_value[side][j], top_id[side][j], mv, mi);
                 if (rank < k) {
                     top_value[side ^ 1][rank] = mv;
@@ -371,19 +389,23 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     // stage holds (all accesses stay inside the ring and the rows) and the launch reports NPD_STATUS_WAIT_TIMEOUT;
     // thread 0 then gives the copies it started a last bounded chance to land.
     const int64_t row_bytes = static_cast<int64_t>(p.vocab) * sizeof(T);
-    auto start_copy = [&](int t) {
-        const int64_t item = item_begin + t;
-        const int64_t row = item / p.slices;
-        const int64_t byte0 = (item - row * p.slices) * kSliceBytes;
+    int64_t copy_row = item_begin / p.slices;           // thread 0: the slice the next copy brings in
+    int copy_slice = static_cast<int>(item_begin - copy_row * p.slices);
+    auto start_copy = [&](int t) {                      // called for t = 0, 1, 2, ... in order
+        const int64_t byte0 = static_cast<int64_t>(copy_slice) * kSliceBytes;
         const int64_t left = row_bytes - byte0;
         const uint32_t bytes = left >= kSliceBytes ? kSliceBytes : static_cast<uint32_t>(left & ~15ll);
         const uint32_t bar = npd::smem_u32(&full[t % kStages]);
         if (bytes) {
             npd::mbar_expect_tx(bar, bytes);
             bulk_g2s(npd::smem_u32(ring + (t % kStages) * kSliceBytes),
-                     reinterpret_cast<const uint8_t *>(all_logits + row * p.row_stride) + byte0, bytes, bar);
+                     reinterpret_cast<const uint8_t *>(all_logits + copy_row * p.row_stride) + byte0, bytes, bar);
         } else {
             npd::mbar_arrive(bar);                      // fewer than 16 bytes of the row left: read piecewise
+        }
+        if (++copy_slice == p.slices) {
+            copy_slice = 0;
+            ++copy_row;
         }
     };
 
@@ -459,6 +481,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
                 if (mi < 0) continue;
                 const float mv = pool_value[i];
                 int rank = 0;
+#pragma unroll 4
                 for (int j = 0; j < total; ++j) rank += before(pool_value[j], pool_id[j], mv, mi);   // an empty entry is -inf
                 if (rank < k) {
                     top_value[side ^ 1][rank] = mv;
@@ -479,10 +502,13 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     }
     __syncthreads();
     bool lost = false;
-    for (int t = 0; t < n_items; ++t) {
-        const int64_t item = item_begin + t;
-        const int row = static_cast<int>(item / p.slices);
-        const int s = static_cast<int>(item - static_cast<int64_t>(row) * p.slices);
+    int row = static_cast<int>(item_begin / p.slices);
+    int s = static_cast<int>(item_begin - static_cast<int64_t>(row) * p.slices);
+    for (int t = 0; t < n_items; ++t, ++s) {
+        if (s == p.slices) {
+            s = 0;
+            ++row;
+        }
         const bool first = t == 0 || s == 0;
         const bool last = t == n_items - 1 || s == p.slices - 1;
         if (first) {
