@@ -478,7 +478,7 @@ def run_model_workload(args, dev, timed, batch, seed):
            "tok_s": round(S / (ms_graph * 1e-3), 1), "tok_s_eager": round(S / (ms_eager * 1e-3), 1),
            "kv_bytes_per_step": kv_bytes_step, "weight_bytes_per_step": 2 * (shape.param_count - shape.vocab * shape.hidden),
            "library_launches_per_step": model.launches_per_step(),
-           "sampling": "greedy argmax on the device", "device_status": status,
+           "sampling": "top_k_sample, top_k = 1, one launch per step, tokens stay on the device", "device_status": status,
            "steps_timed": n_graph, "tokens_advance_in_place": True}
     del model, k_cache, v_cache
     torch.cuda.empty_cache()
@@ -488,6 +488,41 @@ def run_model_workload(args, dev, timed, batch, seed):
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
+def run_sampler_workload(dev, timed, rows, vocab=151936):
+    """Batched top-k sampling over one step's logits (``rows`` x the Qwen3 vocabulary, bf16).  Five buffers (389 MB
+    at 256 rows, larger than L2) are taken in turn inside one CUDA graph, so neither L2 nor the host's launch rate
+    enters the figure.  The library kernels torch would run for the same job stand beside it."""
+    from nanopd_b200 import sampling
+    nbuf = 5
+    logit_bufs = [(2.5 * torch.randn(rows, vocab, device=dev)).to(torch.bfloat16) for _ in range(nbuf)]
+    uni = torch.rand(rows, device=dev)
+    tok = torch.empty(rows, dtype=torch.int64, device=dev)
+    bytes_s = rows * vocab * 2 + rows * 12
+    peak = measured_peak_gbs()[0]
+    entry = {"rows": rows, "vocab": vocab, "dtype": "bf16", "algorithmic_bytes": bytes_s}
+    side = torch.cuda.Stream(device=dev)
+    for k in (1, 10):
+        with torch.cuda.stream(side):
+            sampling.top_k_sample(logit_bufs[0], k, uniforms=uni, out=tok)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for lb in logit_bufs:
+                    sampling.top_k_sample(lb, k, uniforms=uni, out=tok)
+        graph.replay()
+        ms = timed(graph.replay, 10) / nbuf
+        entry[f"top_{k}"] = {"us": round(ms * 1e3, 2), "gbs": round(bytes_s / (ms * 1e-3) / 1e9, 1),
+                             "frac_of_hbm_peak": round(bytes_s / (ms * 1e-3) / 1e9 / peak, 3)}
+    turn = iter(range(10 ** 9))
+    for name, fn in (("torch_argmax_us", lambda: torch.argmax(logit_bufs[next(turn) % nbuf], dim=-1)),
+                     ("torch_topk_10_us", lambda: torch.topk(logit_bufs[next(turn) % nbuf], 10))):
+        for _ in range(3):
+            fn()
+        entry[name] = round(timed(fn, 20) * 1e3, 2)
+    entry["status"] = sampling.check_status(dev, raise_on_error=False)
+    return entry
+
+
 def run_gpu_arm(args):
     import paged_kernels                      # raises if the CUDA library is missing: no fallback
     from nanopd_b200 import kv_transfer
@@ -543,6 +578,15 @@ def run_gpu_arm(args):
                 res["n_gpus"] = world
                 res["tok_s_all_gpus"] = round(toks / (ms * 1e-3), 1)
             print(json.dumps({"workload": "decode tokens/s at model level (secondary, not the headline metric)", **res}), flush=True)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return 0
+
+    if args.workload == "sampler":
+        res = run_sampler_workload(dev, timed, args.batch)
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"workload": "batched top-k sampling of one step (secondary, not the headline metric)", **res}), flush=True)
         if world > 1:
             torch.distributed.destroy_process_group()
         return 0
@@ -742,35 +786,7 @@ def run_gpu_arm(args):
         except Exception as exc:  # noqa: BLE001
             extras["fused_norm_rope_store_error"] = str(exc)[:200]
         try:
-            # batched top-k sampling over the step's logits: the batch's rows x the Qwen3 vocabulary, bf16; five
-            # buffers (389 MB, larger than L2) taken in turn inside one CUDA graph, so neither L2 nor the host's
-            # launch rate enters the figure.  The library kernels torch would run stand beside it.
-            from nanopd_b200 import sampling
-            V_s, nbuf = 151936, 5
-            logit_bufs = [(2.5 * torch.randn(S, V_s, device=dev)).to(torch.bfloat16) for _ in range(nbuf)]
-            uni = torch.rand(S, device=dev)
-            tok = torch.empty(S, dtype=torch.int64, device=dev)
-            bytes_s = S * V_s * 2 + S * 12
-            entry = {"rows": S, "vocab": V_s, "dtype": "bf16", "algorithmic_bytes": bytes_s}
-            side_s = torch.cuda.Stream(device=dev)
-            for k_s in (1, 10):
-                with torch.cuda.stream(side_s):
-                    sampling.top_k_sample(logit_bufs[0], k_s, uniforms=uni, out=tok)
-                    side_s.synchronize()
-                    graph_s = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph_s, stream=side_s):
-                        for lb in logit_bufs:
-                            sampling.top_k_sample(lb, k_s, uniforms=uni, out=tok)
-                graph_s.replay()
-                ms_s = timed(graph_s.replay, 10) / nbuf
-                entry[f"top_{k_s}"] = {"us": round(ms_s * 1e3, 2), "gbs": round(bytes_s / (ms_s * 1e-3) / 1e9, 1),
-                                       "frac_of_hbm_peak": round(bytes_s / (ms_s * 1e-3) / 1e9 / measured_peak_gbs()[0], 3)}
-            it = iter(range(10 ** 9))
-            entry["torch_argmax_us"] = round(timed(lambda: torch.argmax(logit_bufs[next(it) % nbuf], dim=-1), 20) * 1e3, 2)
-            entry["torch_topk_10_us"] = round(timed(lambda: torch.topk(logit_bufs[next(it) % nbuf], 10), 20) * 1e3, 2)
-            entry["status"] = sampling.check_status(dev, raise_on_error=False)
-            extras["top_k_sample"] = entry
-            del logit_bufs
+            extras["top_k_sample"] = run_sampler_workload(dev, timed, S)
         except Exception as exc:  # noqa: BLE001
             extras["top_k_sample_error"] = str(exc)[:200]
         try:
@@ -856,7 +872,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--workload", choices=["decode", "prefill", "model", "model-tables", "reference-grid"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "model", "model-tables", "reference-grid", "sampler"], default="decode",
                     help="decode = the headline configuration 2 (default); prefill = configuration 3's chunked prefill")
     ap.add_argument("--profile", action="store_true",
                     help="only warm up and run the timed step loop (for short ncu captures); prints no bench line")

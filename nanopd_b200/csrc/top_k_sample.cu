@@ -185,6 +185,211 @@ __device__ __forceinline__ uint4 piece_of(const uint8_t *stage, const T *logits,
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Shared memory beside the ring.
+struct Scratch {
+    float pool_value[kSliceCandidates];     // logits gathered since the last ranking; the chunks' lists at a merge
+    int pool_id[kSliceCandidates];
+    alignas(16) float group_max[kMaxGroups];
+    float warp_value[kThreads / 32];
+    int warp_id[kThreads / 32];
+    float top_value[2][kMaxTopK];           // the k best so far, best first; two sides, written in turn
+    int top_id[2][kMaxTopK];
+    float top_prob[kMaxTopK];
+    float bound;
+    int gathered[2];
+    int is_last;
+};
+
+// The paths below run once per row, or a few times, or never; they are kept out of line so that the loop over
+// the slices stays a few hundred instructions that the instruction cache holds.
+
+// A lower bound of the slice's k-th largest logit: the k-th largest of the maxima of G groups of threads (k groups
+// hold a logit at least that large).  G = 64 for k <= 16, else 128.  The maximum is taken over the logits as they
+// are, NaNs passed over, and repaired afterwards: that can only lower a group's maximum below the one nan_to_num
+// would give, which keeps the bound valid.
+template <typename T>
+__device__ __noinline__ float first_bound(Scratch &sh, const uint8_t *stage, const T *logits, int vocab, int base, int k,
+                                          float replacement) {
+    using L = Logit<T>;
+    const int tid = threadIdx.x;
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kLoads; ++j) m = L::max_of(piece_of<T>(stage, logits, vocab, base, j, tid), m);
+    if (m != m) m = 0.f;                            // unreachable with fmaxf; kept for a max that returns NaN
+    else if (fabsf(m) > FLT_MAX) m = copysignf(replacement, m);
+    const int group_shift = k <= 16 ? 2 : 1;        // threads per group: 4 or 2
+    const int groups = kThreads >> group_shift;
+    for (int o = 1; o < (1 << group_shift); o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((tid & ((1 << group_shift) - 1)) == 0) sh.group_max[tid >> group_shift] = m;
+    __syncthreads();
+    if (tid < groups) {
+        const float mine = sh.group_max[tid];
+        int rank = 0;
+#pragma unroll 4
+        for (int j = 0; j < groups; j += 4) {
+            const float4 other = *reinterpret_cast<const float4 *>(&sh.group_max[j]);
+            rank += before(other.x, j, mine, tid) + before(other.y, j + 1, mine, tid) +
+                    before(other.z, j + 2, mine, tid) + before(other.w, j + 3, mine, tid);
+        }
+        if (rank == k - 1) sh.bound = mine;
+    }
+    __syncthreads();
+    return sh.bound;
+}
+
+// Data that defeats the limit (long runs of equal or rising values): the slice's own k best by k rounds of a
+// block-wide arg-max over the slice, placed in the pool behind the `pooled` entries earlier slices left there.
+// Returns the pool's new count.
+template <typename T>
+__device__ __noinline__ int arg_max_rounds(Scratch &sh, const uint8_t *stage, const T *logits, int vocab, int base, int k,
+                                           int pooled, float replacement) {
+    using L = Logit<T>;
+    constexpr int kVec = 16 / sizeof(T);
+    const int tid = threadIdx.x;
+    uint64_t taken = 0;
+    int count = pooled;
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = INT_MAX, be = 0;
+#pragma unroll
+        for (int j = 0; j < kLoads; ++j) {
+            float f[kVec];
+            L::widen(piece_of<T>(stage, logits, vocab, base, j, tid), f);
+            const int e0 = base + (j * kThreads + tid) * kVec;
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) {
+                const float x = replace_special(f[i], replacement);
+                if (!((taken >> (j * kVec + i)) & 1ull) && e0 + i < vocab && before(x, e0 + i, bv, bi)) {
+                    bv = x;
+                    bi = e0 + i;
+                    be = j * kVec + i;
+                }
+            }
+        }
+        float wv = bv;
+        int wi = bi;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, wv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, wi, off);
+            if (before(ov, oi, wv, wi)) {
+                wv = ov;
+                wi = oi;
+            }
+        }
+        if ((tid & 31) == 0) {
+            sh.warp_value[tid >> 5] = wv;
+            sh.warp_id[tid >> 5] = wi;
+        }
+        __syncthreads();
+        wv = sh.warp_value[0];
+        wi = sh.warp_id[0];
+#pragma unroll
+        for (int w = 1; w < kThreads / 32; ++w) {
+            if (before(sh.warp_value[w], sh.warp_id[w], wv, wi)) {
+                wv = sh.warp_value[w];
+                wi = sh.warp_id[w];
+            }
+        }
+        if (wi != INT_MAX) {
+            if (wi == bi) taken |= 1ull << be;
+            if (tid == 0) {
+                sh.pool_value[count] = wv;
+                sh.pool_id[count] = wi;
+            }
+            ++count;
+        }
+        __syncthreads();
+    }
+    return count;
+}
+
+// Ranks the `count` pooled logits together with the `n_top` best so far (side `side`) by counting; ranks below k
+// go to the other side.  Entries with a negative id (empty slots of a list) are passed over.  Ends in a barrier.
+__device__ __noinline__ void rank_pool(Scratch &sh, int count, int n_top, int side, int k) {
+    const int all = count + n_top;
+    for (int i = threadIdx.x; i < all; i += kThreads) {
+        const float mv = i < count ? sh.pool_value[i] : sh.top_value[side][i - count];
+        const int mi = i < count ? sh.pool_id[i] : sh.top_id[side][i - count];
+        if (mi < 0) continue;
+        int rank = 0;
+#pragma unroll 4
+        for (int j = 0; j < count; ++j) rank += before(sh.pool_value[j], sh.pool_id[j], mv, mi);     // an empty slot is -inf
+#pragma unroll 4
+        for (int j = 0; j < n_top; ++j) rank += before(sh.top_value[side][j], sh.top_id[side][j], mv, mi);
+        if (rank < k) {
+            sh.top_value[side ^ 1][rank] = mv;
+            sh.top_id[side ^ 1][rank] = mi;
+        }
+    }
+    __syncthreads();
+}
+
+// The k best of a whole row are in side `side`: probabilities (softmax over the k values, rounded to the logits'
+// dtype as torch.softmax returns it) and the draw (inverse CDF: the first candidate whose running sum exceeds
+// uniform x total), by one warp.
+template <typename T>
+__device__ __noinline__ void draw_row(Scratch &sh, int side, int k, const float *uniform, int64_t *out) {
+    using L = Logit<T>;
+    const int tid = threadIdx.x;
+    if (tid >= 32) return;
+    const float mx = sh.top_value[side][0];
+    const float e0 = tid < k ? expf(sh.top_value[side][tid] - mx) : 0.f;
+    const float e1 = tid + 32 < k ? expf(sh.top_value[side][tid + 32] - mx) : 0.f;
+    float sum = e0 + e1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (tid < k) sh.top_prob[tid] = L::round(__fdiv_rn(e0, sum));
+    if (tid + 32 < k) sh.top_prob[tid + 32] = L::round(__fdiv_rn(e1, sum));
+    __syncwarp();
+    if (tid == 0) {
+        int pick = 0;
+        if (k > 1) {
+            float all = 0.f;
+            for (int j = 0; j < k; ++j) all += sh.top_prob[j];
+            const float target = *uniform * all;
+            float run = 0.f;
+            pick = k - 1;
+            for (int j = 0; j < k; ++j) {
+                run += sh.top_prob[j];
+                if (run > target) {
+                    pick = j;
+                    break;
+                }
+            }
+        }
+        *out = sh.top_id[side][pick];
+    }
+    __syncwarp();
+}
+
+// End of a CTA's part of a row that several CTAs share: the part's k best (side `side`, n_top of them) go to slot
+// `slot` of the row's list in global memory; the last of the `parts` to arrive (a ticket per row, reset by it)
+// ranks all lists into the other side and returns true.
+__device__ __noinline__ bool hand_over_part(Scratch &sh, float *row_value, int32_t *row_id, uint32_t *ticket, int slot,
+                                            int parts, int n_top, int side, int k) {
+    const int tid = threadIdx.x;
+    for (int r = tid; r < k; r += kThreads) {
+        row_value[slot * k + r] = r < n_top ? sh.top_value[side][r] : -INFINITY;
+        row_id[slot * k + r] = r < n_top ? sh.top_id[side][r] : -1;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) sh.is_last = atomicAdd(ticket, 1u) == static_cast<uint32_t>(parts - 1);
+    __syncthreads();
+    if (!sh.is_last) return false;
+    __threadfence();
+    const int total = parts * k;                    // at most kSliceCandidates: the pool is idle here
+    for (int i = tid; i < total; i += kThreads) {
+        sh.pool_value[i] = __ldcg(row_value + i);
+        sh.pool_id[i] = __ldcg(row_id + i);
+    }
+    if (tid == 0) *ticket = 0;                      // every part has arrived: ready for the next launch
+    __syncthreads();
+    rank_pool(sh, total, 0, side, k);
+    return true;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleParams p) {
     using L = Logit<T>;
@@ -192,16 +397,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     constexpr int kSlice = kThreads * kLoads * kVec;
     extern __shared__ __align__(128) uint8_t ring[];        // kStages slices
     __shared__ uint64_t full[kStages];
-    __shared__ float pool_value[kSliceCandidates];
-    __shared__ int pool_id[kSliceCandidates];
-    __shared__ __align__(16) float group_max[kMaxGroups];
-    __shared__ float warp_value[kThreads / 32];
-    __shared__ int warp_id[kThreads / 32];
-    __shared__ float top_value[2][kMaxTopK], top_prob[kMaxTopK];
-    __shared__ int top_id[2][kMaxTopK];
-    __shared__ float bound;
-    __shared__ int gathered[2];
-    __shared__ int is_last;
+    __shared__ Scratch sh;
 
     const int tid = threadIdx.x;
     const int k = p.top_k;
@@ -210,178 +406,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     const int n_items = static_cast<int>((blockIdx.x + 1) * p.items / grid - item_begin);
     const T *const all_logits = static_cast<const T *>(p.logits) + p.first_row * p.row_stride;
     const float replacement = L::round(1e4f);
-    if (tid < 2) gathered[tid] = 0;
-
-    // This CTA's run of slices may start and end inside a row; a stretch of one row is a "part".  The part's k best
-    // so far live in top_value[side] / top_id[side], best first; n_top of them, and `tau` is the k-th.  A later
-    // slice of the part only has to look at logits ABOVE tau: its ids are all larger than the ids seen, so an equal
-    // value ranks behind.  What it finds collects in the pool (counter gathered[bank]) and is ranked together with
-    // the k best so far once there are k of them (enough to move tau), or at the part's end — an older, lower tau
-    // only lets a few more logits through.
-    int n_top = 0, side = 0, bank = 0, pooled = 0;
-    float tau = -INFINITY;
-
-    // One slice, already in shared memory.
-    auto examine = [&](const uint8_t *stage, const T *logits, const int s, const bool first, const bool last) {
-        const int base = s * kSlice;
-
-        float limit = tau;
-        if (first) {
-            // A lower bound of the slice's k-th largest logit: the k-th largest of the maxima of G groups of
-            // threads (k groups hold a logit at least that large).  G = 64 for k <= 16, else 128.
-            // The maximum is taken over the logits as they are, NaNs passed over, and repaired afterwards: that
-            // can only lower a group's maximum below the one nan_to_num would give, which keeps the bound valid.
-            float m = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < kLoads; ++j) m = L::max_of(piece_of<T>(stage, logits, p.vocab, base, j, tid), m);
-            if (m != m) m = 0.f;                            // unreachable with fmaxf; kept for a max that returns NaN
-            else if (fabsf(m) > FLT_MAX) m = copysignf(replacement, m);
-            const int group_shift = k <= 16 ? 2 : 1;        // threads per group: 4 or 2
-            const int groups = kThreads >> group_shift;
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            if (group_shift == 2) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-            if ((tid & ((1 << group_shift) - 1)) == 0) group_max[tid >> group_shift] = m;
-            __syncthreads();
-            if (tid < groups) {
-                const float mine = group_max[tid];
-                int rank = 0;
-#pragma unroll 4
-                for (int j = 0; j < groups; j += 4) {
-                    const float4 other = *reinterpret_cast<const float4 *>(&group_max[j]);
-                    rank += before(other.x, j, mine, tid) + before(other.y, j + 1, mine, tid) +
-                            before(other.z, j + 2, mine, tid) + before(other.w, j + 3, mine, tid);
-                }
-                if (rank == k - 1) bound = mine;
-            }
-            __syncthreads();
-            limit = bound;
-        }
-
-        // ---- gather the logits past the limit (not below it in the first slice, above it later) ---------------
-        // -inf only matters when its replacement, -1e4, would pass the limit.
-        const bool careful = limit < -replacement || (first && limit == -replacement);
-        // First one bit per 16-byte piece, all eight pieces independent of each other; then the few pieces that
-        // hold something.
-        unsigned hits = 0;
-        if (base + kSlice <= p.vocab) {
-#pragma unroll
-            for (int j = 0; j < kLoads; ++j) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(stage + (j * kThreads + tid) * 16);
-                hits |= static_cast<unsigned>(L::any_past(raw, limit, first)) << j;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < kLoads; ++j)
-                hits |= static_cast<unsigned>(L::any_past(piece_of<T>(stage, logits, p.vocab, base, j, tid), limit, first)) << j;
-        }
-        if (careful) hits = (1u << kLoads) - 1;
-        while (hits) {
-            const int j = __ffs(hits) - 1;
-            hits &= hits - 1;
-            float f[kVec];
-            L::widen(piece_of<T>(stage, logits, p.vocab, base, j, tid), f);
-            const int e0 = base + (j * kThreads + tid) * kVec;
-#pragma unroll
-            for (int i = 0; i < kVec; ++i) {
-                const float x = replace_special(f[i], replacement);
-                if ((first ? x >= limit : x > limit) && e0 + i < p.vocab) {
-                    const int pos = atomicAdd(&gathered[bank], 1);
-                    if (pos < kSliceCandidates) {
-                        pool_value[pos] = x;
-                        pool_id[pos] = e0 + i;
-                    }
-                }
-            }
-        }
-        __syncthreads();
-        int count = gathered[bank];
-
-        if (count > kSliceCandidates) {
-            // ---- data that defeats the limit (long runs of equal or rising values): the slice's own k best by
-            // k rounds of a block-wide arg-max over the slice, placed behind what earlier slices pooled ------
-            uint64_t taken = 0;
-            count = pooled;
-            for (int r = 0; r < k; ++r) {
-                float bv = -INFINITY;
-                int bi = INT_MAX, be = 0;
-#pragma unroll
-                for (int j = 0; j < kLoads; ++j) {
-                    float f[kVec];
-                    L::widen(piece_of<T>(stage, logits, p.vocab, base, j, tid), f);
-                    const int e0 = base + (j * kThreads + tid) * kVec;
-#pragma unroll
-                    for (int i = 0; i < kVec; ++i) {
-                        const float x = replace_special(f[i], replacement);
-                        if (!((taken >> (j * kVec + i)) & 1ull) && e0 + i < p.vocab && before(x, e0 + i, bv, bi)) {
-                            bv = x;
-                            bi = e0 + i;
-                            be = j * kVec + i;
-                        }
-                    }
-                }
-                float wv = bv;
-                int wi = bi;
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) {
-                    const float ov = __shfl_xor_sync(0xffffffffu, wv, off);
-                    const int oi = __shfl_xor_sync(0xffffffffu, wi, off);
-                    if (before(ov, oi, wv, wi)) {
-                        wv = ov;
-                        wi = oi;
-                    }
-                }
-                if ((tid & 31) == 0) {
-                    warp_value[tid >> 5] = wv;
-                    warp_id[tid >> 5] = wi;
-                }
-                __syncthreads();
-                wv = warp_value[0];
-                wi = warp_id[0];
-#pragma unroll
-                for (int w = 1; w < kThreads / 32; ++w) {
-                    if (before(warp_value[w], warp_id[w], wv, wi)) {
-                        wv = warp_value[w];
-                        wi = warp_id[w];
-                    }
-                }
-                if (wi != INT_MAX) {
-                    if (wi == bi) taken |= 1ull << be;
-                    if (tid == 0) {
-                        pool_value[count] = wv;
-                        pool_id[count] = wi;
-                    }
-                    ++count;
-                }
-                __syncthreads();
-            }
-        }
-        pooled = count;
-
-        if (count > 0 && (first || count >= k || last)) {
-            // ---- rank the pooled logits together with the k best so far; ranks below k are the new best ---------
-            const int all = count + n_top;
-            for (int i = tid; i < all; i += kThreads) {
-                const float mv = i < count ? pool_value[i] : top_value[side][i - count];
-                const int mi = i < count ? pool_id[i] : top_id[side][i - count];
-                int rank = 0;
-#pragma unroll 4
-                for (int j = 0; j < count; ++j) rank += before(pool_value[j], pool_id[j], mv, mi);
-#pragma unroll 4
-                for (int j = 0; j < n_top; ++j) rank += before(top_value[side][j], top_id[side][j], mv, mi);
-                if (rank < k) {
-                    top_value[side ^ 1][rank] = mv;
-                    top_id[side ^ 1][rank] = mi;
-                }
-            }
-            if (tid == 0) gathered[bank ^ 1] = 0;       // last read before the previous ranking's closing barrier
-            n_top = all < k ? all : k;
-            side ^= 1;
-            bank ^= 1;
-            pooled = 0;
-            __syncthreads();
-            if (n_top == k) tau = top_value[side][k - 1];
-        }
-    };
+    if (tid < 2) sh.gathered[tid] = 0;
 
     // The ring: thread 0 starts the copy of this CTA's t-th slice into stage t % kStages and, once the slice in a
     // stage has been examined, of the slice kStages further on — across the ends of rows, so the copies never stop
@@ -408,91 +433,8 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
             ++copy_row;
         }
     };
-
-    // The k best of a whole row are in top_*[side]: probabilities and the draw, by one warp.
-    auto draw = [&](const int row) {
-        if (tid < 32) {
-            // softmax over the k values, rounded to the logits' dtype as torch.softmax returns it
-            const float mx = top_value[side][0];
-            const float e0 = tid < k ? expf(top_value[side][tid] - mx) : 0.f;
-            const float e1 = tid + 32 < k ? expf(top_value[side][tid + 32] - mx) : 0.f;
-            float sum = e0 + e1;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-            if (tid < k) top_prob[tid] = L::round(__fdiv_rn(e0, sum));
-            if (tid + 32 < k) top_prob[tid + 32] = L::round(__fdiv_rn(e1, sum));
-            __syncwarp();
-            if (tid == 0) {
-                int pick = 0;
-                if (k > 1) {
-                    // inverse CDF: the first candidate whose running sum exceeds uniform x total
-                    float all = 0.f;
-                    for (int j = 0; j < k; ++j) all += top_prob[j];
-                    const float target = p.uniforms[p.first_row + row] * all;
-                    float run = 0.f;
-                    pick = k - 1;
-                    for (int j = 0; j < k; ++j) {
-                        run += top_prob[j];
-                        if (run > target) {
-                            pick = j;
-                            break;
-                        }
-                    }
-                }
-                p.out[p.first_row + row] = top_id[side][pick];
-            }
-            __syncwarp();
-        }
-    };
-
     // The CTA that owns global slice number i: the g with g * items / grid <= i < (g + 1) * items / grid.
     auto owner_of = [&](int64_t i) { return ((i + 1) * grid - 1) / p.items; };
-
-    // End of this CTA's part of `row`.  A row that one CTA saw whole is drawn at once; otherwise the part's k best go
-    // to the row's list in global memory and the last part to arrive (a ticket per row, reset by it) merges them.
-    auto finish_part = [&](const int row) {
-        const int64_t first_owner = owner_of(static_cast<int64_t>(row) * p.slices);
-        const int parts = static_cast<int>(owner_of(static_cast<int64_t>(row + 1) * p.slices - 1) - first_owner) + 1;
-        if (parts > 1) {
-            const int slot = static_cast<int>(blockIdx.x - first_owner);
-            float *list_value = p.cand_value + (static_cast<int64_t>(row) * p.parts_cap + slot) * k;
-            int32_t *list_id = p.cand_id + (static_cast<int64_t>(row) * p.parts_cap + slot) * k;
-            for (int r = tid; r < k; r += kThreads) {
-                list_value[r] = r < n_top ? top_value[side][r] : -INFINITY;
-                list_id[r] = r < n_top ? top_id[side][r] : -1;
-            }
-            __threadfence();
-            __syncthreads();
-            if (tid == 0) is_last = atomicAdd(&p.tickets[row], 1u) == static_cast<uint32_t>(parts - 1);
-            __syncthreads();
-            if (!is_last) return;
-            __threadfence();
-            const int total = parts * k;                    // at most kSliceCandidates: the pool is idle here
-            const float *row_value = p.cand_value + static_cast<int64_t>(row) * p.parts_cap * k;
-            const int32_t *row_id = p.cand_id + static_cast<int64_t>(row) * p.parts_cap * k;
-            for (int i = tid; i < total; i += kThreads) {
-                pool_value[i] = __ldcg(row_value + i);
-                pool_id[i] = __ldcg(row_id + i);
-            }
-            if (tid == 0) p.tickets[row] = 0;               // every part has arrived: ready for the next launch
-            __syncthreads();
-            for (int i = tid; i < total; i += kThreads) {
-                const int mi = pool_id[i];
-                if (mi < 0) continue;
-                const float mv = pool_value[i];
-                int rank = 0;
-#pragma unroll 4
-                for (int j = 0; j < total; ++j) rank += before(pool_value[j], pool_id[j], mv, mi);   // an empty entry is -inf
-                if (rank < k) {
-                    top_value[side ^ 1][rank] = mv;
-                    top_id[side ^ 1][rank] = mi;
-                }
-            }
-            side ^= 1;
-            __syncthreads();
-        }
-        draw(row);
-    };
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) npd::mbar_init(npd::smem_u32(&full[i]), 1);
@@ -501,6 +443,15 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         for (int t = 0; t < kStages && t < n_items; ++t) start_copy(t);
     }
     __syncthreads();
+
+    // This CTA's run of slices may start and end inside a row; a stretch of one row is a "part".  The part's k best
+    // so far live in side `side` of the scratch, best first; n_top of them, and `tau` is the k-th.  A later slice of
+    // the part only has to look at logits ABOVE tau: its ids are all larger than the ids seen, so an equal value
+    // ranks behind.  What it finds collects in the pool (counter gathered[bank]) and is ranked together with the k
+    // best so far once there are max(k, 8) of them (enough to move tau), or at the part's end — an older, lower tau
+    // only lets a few more logits through.
+    int n_top = 0, side = 0, bank = 0, pooled = 0;
+    float tau = -INFINITY;
     bool lost = false;
     int row = static_cast<int>(item_begin / p.slices);
     int s = static_cast<int>(item_begin - static_cast<int64_t>(row) * p.slices);
@@ -511,19 +462,88 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         }
         const bool first = t == 0 || s == 0;
         const bool last = t == n_items - 1 || s == p.slices - 1;
+        const uint8_t *stage = ring + (t % kStages) * kSliceBytes;
+        const T *logits = all_logits + row * p.row_stride;
+        const int base = s * kSlice;
+        if (!lost && !npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit)) lost = true;
+
+        float limit = tau;
         if (first) {
             n_top = 0;
             pooled = 0;
             tau = -INFINITY;
+            limit = first_bound<T>(sh, stage, logits, p.vocab, base, k, replacement);
         }
-        if (!lost && !npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit)) lost = true;
-        examine(ring + (t % kStages) * kSliceBytes, all_logits + row * p.row_stride, s, first, last);
-        // examine() ends behind a barrier that follows every read of the stage
+
+        // ---- gather the logits past the limit (not below it in the first slice, above it later) ---------------
+        // -inf only matters when its replacement, -1e4, would pass the limit.  First one bit per 16-byte piece, all
+        // eight pieces independent of each other; then the few pieces that hold something.
+        const bool careful = limit < -replacement || (first && limit == -replacement);
+        unsigned hits = 0;
+        if (base + kSlice <= p.vocab) {
+#pragma unroll
+            for (int j = 0; j < kLoads; ++j) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(stage + (j * kThreads + tid) * 16);
+                hits |= static_cast<unsigned>(L::any_past(raw, limit, first)) << j;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < kLoads; ++j)
+                hits |= static_cast<unsigned>(L::any_past(piece_of<T>(stage, logits, p.vocab, base, j, tid), limit, first)) << j;
+        }
+        if (careful) hits = (1u << kLoads) - 1;
+        while (hits) {
+            const int j = __ffs(hits) - 1;
+            hits &= hits - 1;
+            float f[kVec];
+            L::widen(piece_of<T>(stage, logits, p.vocab, base, j, tid), f);
+            const int e0 = base + (j * kThreads + tid) * kVec;
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) {
+                const float x = replace_special(f[i], replacement);
+                if ((first ? x >= limit : x > limit) && e0 + i < p.vocab) {
+                    const int pos = atomicAdd(&sh.gathered[bank], 1);
+                    if (pos < kSliceCandidates) {
+                        sh.pool_value[pos] = x;
+                        sh.pool_id[pos] = e0 + i;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        int count = sh.gathered[bank];
+        if (count > kSliceCandidates)
+            count = arg_max_rounds<T>(sh, stage, logits, p.vocab, base, k, pooled, replacement);
+        pooled = count;
+        // Every read of the stage lies before a barrier all threads have passed: the stage can be refilled.
         if (tid == 0 && !lost && t + kStages < n_items) {
             npd::fence_proxy_async_smem();
             start_copy(t + kStages);
         }
-        if (last) finish_part(row);
+
+        if (count > 0 && (first || count >= (k > 8 ? k : 8) || last)) {
+            if (tid == 0) sh.gathered[bank ^ 1] = 0;    // last read before the previous ranking's closing barrier
+            rank_pool(sh, count, n_top, side, k);
+            n_top = count + n_top < k ? count + n_top : k;
+            side ^= 1;
+            bank ^= 1;
+            pooled = 0;
+            if (n_top == k) tau = sh.top_value[side][k - 1];
+        }
+
+        if (last) {
+            // A row that one CTA saw whole is drawn at once; otherwise the last part to arrive merges and draws.
+            const int64_t first_owner = owner_of(static_cast<int64_t>(row) * p.slices);
+            const int parts = static_cast<int>(owner_of(static_cast<int64_t>(row + 1) * p.slices - 1) - first_owner) + 1;
+            bool whole = true;
+            if (parts > 1) {
+                whole = hand_over_part(sh, p.cand_value + static_cast<int64_t>(row) * p.parts_cap * k,
+                                       p.cand_id + static_cast<int64_t>(row) * p.parts_cap * k, p.tickets + row,
+                                       static_cast<int>(blockIdx.x - first_owner), parts, n_top, side, k);
+                if (whole) side ^= 1;
+            }
+            if (whole) draw_row<T>(sh, side, k, p.uniforms ? p.uniforms + p.first_row + row : nullptr, p.out + p.first_row + row);
+        }
     }
     if (lost) {
         if (p.status) atomicOr(p.status, NPD_STATUS_WAIT_TIMEOUT);
