@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own CPU path.
 
-Run in a container that has the reference checkout (default /root/reference; override with
-NANOPD_REFERENCE):  python tests/golden/make_golden.py
+Run where the reference checkout is at hand, its path in NANOPD_REFERENCE:
+    NANOPD_REFERENCE=<checkout> python tests/golden/make_golden.py
 
 It imports ``ref_paged_attention`` and the input builder ``make_attn_inputs`` from
 nanoPD/paged_attention/tests/test_paged_kernels.py (the module imports without the CUDA
@@ -23,7 +23,9 @@ sys.path.insert(0, str(ROOT))
 from oracle import paged_oracle  # noqa: E402
 from nanopd_b200 import workloads  # noqa: E402
 
-REF = Path(os.environ.get("NANOPD_REFERENCE", "/root/reference"))
+if "NANOPD_REFERENCE" not in os.environ:
+    sys.exit("set NANOPD_REFERENCE to the reference checkout")
+REF = Path(os.environ["NANOPD_REFERENCE"])
 OUT = Path(__file__).resolve().parent
 
 

@@ -4,7 +4,7 @@ CPU, and the reference's own ``top_k_sample`` (imported from the reference tree)
 ``top_k = 1``, whose result does not depend on the random generator.  The oracle must reproduce the k
 values and the probabilities BIT FOR BIT, the ids wherever the k-th value is not tied, and the
 ``top_k = 1`` token (checked here and again by tests/test_oracle.py on the committed fixture).
-Run:  python tests/golden/make_golden_sampling.py [path to the reference checkout]
+Run:  python tests/golden/make_golden_sampling.py <path to the reference checkout>
 """
 import sys
 from pathlib import Path
@@ -17,7 +17,9 @@ sys.path.insert(0, str(ROOT))
 from oracle import paged_oracle  # noqa: E402
 
 OUT = Path(__file__).resolve().parent
-REFERENCE = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden_sampling.py <path to the reference checkout>")
+REFERENCE = Path(sys.argv[1])
 
 
 def bits(t):
