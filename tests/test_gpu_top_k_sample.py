@@ -121,6 +121,31 @@ def test_special_values_and_ties(sampling):
         assert torch.equal(sampling.top_k_sample(logits.to(DEV)).cpu(), ids[:, 0])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_scattered_ties_at_the_top_go_to_the_lowest_id(sampling, dtype):
+    """The largest value several times in a row, far apart: whichever CTA, warp or slice meets which copy first,
+    top_k = 1 returns the lowest id and top_k = 4 the four lowest, in order."""
+    torch.manual_seed(12)
+    V, rows = 151936, 24
+    logits = torch.randn(rows, V).to(dtype)
+    want = []
+    for r in range(rows):
+        ids = torch.randperm(V)[:6].sort().values
+        logits[r, ids] = 30.0
+        logits[r, ids[2]] = -0.0 if r % 5 == 0 else 30.0          # a zero of either sign is no tie-breaker
+        want.append(ids.tolist())
+    zero_row = torch.full((V,), -1.0).to(dtype)
+    zero_row[[140000, 17, 90000]] = torch.tensor([0.0, -0.0, 0.0]).to(dtype)
+    logits[0] = zero_row
+    dev_logits = logits.to(DEV)
+    got = sampling.top_k_sample(dev_logits).cpu()
+    _, ids, _ = paged_oracle.top_k_candidates(logits, 4)
+    assert torch.equal(got, ids[:, 0])
+    assert got[0] == 17 and all(int(got[r]) == want[r][0] for r in range(1, rows))
+    u = torch.full((rows,), 0.999)
+    assert torch.equal(sampling.top_k_sample(dev_logits, 4, uniforms=u.to(DEV)).cpu(), paged_oracle.top_k_sample(logits, 4, u))
+
+
 @pytest.mark.parametrize("vocab", [5, 64, 1000, 16384, 16392, 32768 + 24, 49160])
 def test_ragged_vocabularies(sampling, vocab):
     torch.manual_seed(vocab)
