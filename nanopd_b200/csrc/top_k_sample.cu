@@ -6,7 +6,8 @@
 // logits' dtype, one draw.  Here one launch serves every row of the step and leaves the tokens on the device.
 //
 // The work is a single pass over T x V logits, so HBM bounds it.  A row is cut into slices of 32 KiB; all slices
-// of all rows are dealt, in order, in equal runs to two persistent CTAs per SM.  A CTA brings its slices into a
+// of all rows are dealt, in order, in equal runs to at most two persistent CTAs per SM (a whole number of CTAs per
+// row while the rows fit, so that no run crosses a row's end).  A CTA brings its slices into a
 // ring of three shared-memory stages by one bulk asynchronous copy each (cp.async.bulk on an mbarrier, no
 // multicast) — across the ends of rows, so two copies per CTA are on their way while a slice is examined and no
 // register holds data in flight.  The k best of a row (of the CTA's part of it) are found without sorting:
