@@ -692,6 +692,7 @@ def run_gpu_arm(args):
             e2e_graph_step()
         if torch.equal(out_host, out.cpu()):
             ms_e2e_graph = timed(e2e_graph_step, steps)
+        del graph_e                                     # it holds the staging buffers' addresses; they are freed below
     except Exception as exc:  # noqa: BLE001
         print(f"e2e graph variant skipped: {exc}", file=sys.stderr)
         ms_e2e_graph = None
