@@ -61,6 +61,50 @@ def transfer_kv(src_k, src_v, dst_k, dst_v, block_table: Sequence[int], stream=N
     return "p2p"
 
 
+class KVReceiver:
+    """The receiving half of the hand-over, as ``DecodeWorker`` keeps it (``receive_kv_async`` and
+    ``_promote_ready``, nanoPD/workers/decode_worker.py:36-68): transfers are issued on a stream of their own on
+    the destination GPU, each followed by an event; ``promote_ready`` returns, without blocking, the requests
+    whose pages have arrived, in the order they were issued.  Scheduling stays with the caller."""
+
+    def __init__(self, dst_k: torch.Tensor, dst_v: torch.Tensor, max_ctas: int = 0):
+        self.dst_k, self.dst_v = dst_k, dst_v
+        self.device = dst_k.device
+        self.transfer_stream = torch.cuda.Stream(device=self.device)
+        self.max_ctas = max_ctas
+        self._pending: List[tuple] = []
+
+    def receive_kv_async(self, group, block_table: Sequence[int], buf=None, src_k: torch.Tensor = None,
+                         src_v: torch.Tensor = None, dst_block_table: Optional[Sequence[int]] = None) -> str:
+        """Starts pulling ``block_table`` of ``src_k`` / ``src_v`` into this replica's pools and returns the path
+        taken (always ``"p2p"``).  The source pages must already be complete on the stream that is current on the
+        destination device (the transfer stream waits for it), as after the prefill worker's synchronise."""
+        self.transfer_stream.wait_stream(torch.cuda.current_stream(self.device))
+        path = transfer_kv(src_k, src_v, self.dst_k, self.dst_v, block_table, stream=self.transfer_stream, buf=buf,
+                           dst_block_table=dst_block_table, max_ctas=self.max_ctas)
+        event = torch.cuda.Event()
+        self.transfer_stream.record_event(event)
+        self._pending.append((group, event))
+        return path
+
+    def promote_ready(self) -> list:
+        """Requests whose transfer has completed since the last call (``event.query()``, no host wait).  The compute
+        stream is made to wait for each completed event, so kernels launched afterwards see the pages."""
+        ready, still = [], []
+        for group, event in self._pending:
+            if event.query():
+                torch.cuda.current_stream(self.device).wait_event(event)
+                ready.append(group)
+            else:
+                still.append((group, event))
+        self._pending = still
+        return ready
+
+    @property
+    def num_pending(self) -> int:
+        return len(self._pending)
+
+
 def migration_bytes(num_blocks: int, pool: torch.Tensor) -> int:
     """Algorithmic bytes of one request's migration: blocks x layers x 2 (K, V) x block bytes."""
     L = pool.size(0)

@@ -201,3 +201,31 @@ def test_prefill_here_decode_there(kernels, two_gpus):
         assert torch.equal(dk_cache[li, dst_ids[0]].cpu(), pk_cache[li, src_ids[0]].cpu())
     for d in {p_dev, d_dev}:
         assert paged_kernels.check_status(d, raise_on_error=False) == 0
+
+
+def test_receiver_promotes_requests_as_their_pages_arrive(kernels):
+    """The receiving half as DecodeWorker keeps it (nanoPD/workers/decode_worker.py:36-68): three requests issued
+    on the transfer stream, promoted without a host wait once their events have completed, pages exact and placed
+    at the destination allocator's ids."""
+    torch.manual_seed(21)
+    L, nb, Hkv, B, D = 4, 64, 2, 16, 128
+    src_k = torch.randn(L, nb, Hkv, B, D, device="cuda:0").to(torch.float16)
+    src_v = torch.randn(L, nb, Hkv, B, D, device="cuda:0").to(torch.float16)
+    dst_k, dst_v = torch.zeros_like(src_k), torch.zeros_like(src_v)
+    rx = kv_transfer.KVReceiver(dst_k, dst_v)
+    requests = {"a": ([3, 9, 27], [0, 1, 2]), "b": ([5, 6], [10, 11]), "c": (list(range(30, 50)), list(range(40, 60)))}
+    for name, (src_ids, dst_ids) in requests.items():
+        assert rx.receive_kv_async(name, src_ids, src_k=src_k, src_v=src_v, dst_block_table=dst_ids) == "p2p"
+    assert rx.num_pending == 3
+    promoted = []
+    for _ in range(10000):
+        promoted += rx.promote_ready()
+        if rx.num_pending == 0:
+            break
+    assert promoted == ["a", "b", "c"] and rx.num_pending == 0
+    # the compute stream waited for the events: a kernel launched now sees the pages
+    for src_ids, dst_ids in requests.values():
+        assert torch.equal(dst_k[:, dst_ids], src_k[:, src_ids]) and torch.equal(dst_v[:, dst_ids], src_v[:, src_ids])
+    untouched = [i for i in range(nb) if i not in sum((d for _, d in requests.values()), [])]
+    assert not dst_k[:, untouched].any()
+    assert kernels.check_status("cuda:0", raise_on_error=False) == 0
