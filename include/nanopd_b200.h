@@ -170,7 +170,7 @@ int npd_paged_prefill_attention(void *out, const void *q, const void *k_cache,
  * the kernel itself (bulk asynchronous copies through shared memory, no multicast), so no
  * copy engine or NCCL call is involved.
  * `max_ctas` > 0 sets the grid (one warp and 64 KiB of shared memory per CTA, small enough to
- * share an SM with a decode-attention CTA of the compute stream; 0 = 48 CTAs, which fill an
+ * share an SM with a decode-attention CTA of the compute stream; 0 = 64 CTAs, which fill an
  * NVLink); `max_ctas` < 0 selects the plain load/store variant with -max_ctas CTAs of 256 threads. */
 int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
                    const int32_t *src_blocks, const int32_t *dst_blocks, int64_t num_pairs,

@@ -225,7 +225,8 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
     p.dst_num_blocks = static_cast<int>(dst_num_blocks);
     // Ring of the bulk path: 4 stages of 16 KiB.  64 KiB of shared memory and one warp fit beside a decode-attention
     // CTA on the same SM (132 KiB, 8 warps x 224 registers), so a migration on a side stream does not take SMs away
-    // from the compute stream; 48 such CTAs keep ~2.3 MB in flight, enough for an NVLink.
+    // from the compute stream; 64 such CTAs keep ~3 MB in flight, enough for an NVLink on every box seen (with 48 the
+    // same build reached 771 GB/s on one box and 708 GB/s on another; with 64, 762-772 GB/s).
     // A copy between two pools of ONE GPU has three times an NVLink's bandwidth to fill and nothing to gain from
     // being small: it takes the larger ring (6 x 32 KiB).
     cudaPointerAttributes src_attr{}, dst_attr{};
@@ -249,7 +250,7 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
     // max_ctas < 0 selects the load/store path with -max_ctas CTAs (kept for comparison and as a fallback).
     if (max_ctas >= 0) {
         const long long pieces = units * p.pieces_per_unit;
-        long long grid = max_ctas > 0 ? max_ctas : 48;
+        long long grid = max_ctas > 0 ? max_ctas : 64;
         if (grid > npd::sm_count(dev)) grid = npd::sm_count(dev);
         if (grid > pieces) grid = pieces;
         const size_t smem = (size_t)p.stages * p.piece_bytes;

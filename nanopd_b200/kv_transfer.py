@@ -49,8 +49,8 @@ def transfer_kv(src_k, src_v, dst_k, dst_v, block_table: Sequence[int], stream=N
     if src_device != dst_device and not _check_p2p(src_device, dst_device):
         raise RuntimeError(f"no peer access from {dst_device} to {src_device}: page migration needs NVLink/P2P")
     if max_ctas == 0:
-        # 48 single-warp CTAs fill an NVLink; a pool-to-pool copy inside one GPU has 3x the bandwidth to fill
-        max_ctas = 48 if src_device != dst_device else 96
+        # 64 single-warp CTAs fill an NVLink; a pool-to-pool copy inside one GPU has 3x the bandwidth to fill
+        max_ctas = 64 if src_device != dst_device else 96
     ctx = torch.cuda.stream(stream) if stream is not None else nullcontext()
     with torch.cuda.device(dst_device), ctx:
         if src_device != dst_device:
