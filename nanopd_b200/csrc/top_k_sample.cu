@@ -334,6 +334,10 @@ __device__ __noinline__ void draw_row(Scratch &sh, int side, int k, const float 
     using L = Logit<T>;
     const int tid = threadIdx.x;
     if (tid >= 32) return;
+    if (k == 1) {                                   // the arg-max: nothing to draw
+        if (tid == 0) *out = sh.top_id[side][0];
+        return;
+    }
     const float mx = sh.top_value[side][0];
     const float e0 = tid < k ? expf(sh.top_value[side][tid] - mx) : 0.f;
     const float e1 = tid + 32 < k ? expf(sh.top_value[side][tid + 32] - mx) : 0.f;
