@@ -45,7 +45,6 @@ extern "C" {
  * decode batch of the same scheduler step — can run side by side on two streams, each on its share of the SMs. */
 #define NPD_FLAG_MAX_CTAS(n)      (((n) & 0xffff) << 8)
 
-#define NPD_DECODE_SKIP_MERGE     1   /* diagnostic: sequences split across workers stay unmerged (wrong rows for those) */
 #define NPD_DECODE_KV_INTERLEAVED 2   /* caches in the layouts of the reference's split-K op and of its kernel tests
                                        * (csrc/paged_attention_optimized/index.h:14-31,60-75; tests/test_paged_kernels.py:39-56):
                                        * K [num_blocks, num_kv_heads, head_dim/8, block_size, 8],

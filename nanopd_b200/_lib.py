@@ -11,7 +11,6 @@ NPD_OK = 0
 NPD_ERR_INVALID_ARG, NPD_ERR_UNSUPPORTED, NPD_ERR_CUDA, NPD_ERR_WORKSPACE = 1, 2, 3, 4
 NPD_DTYPE_F16, NPD_DTYPE_BF16, NPD_DTYPE_F32 = 0, 1, 2
 NPD_STATUS_BAD_BLOCK_ID, NPD_STATUS_BAD_POSITION, NPD_STATUS_WAIT_TIMEOUT = 1, 2, 4
-NPD_DECODE_SKIP_MERGE = 1
 NPD_DECODE_KV_INTERLEAVED = 2
 
 # name -> (restype, argtypes); the order mirrors include/nanopd_b200.h
@@ -38,6 +37,9 @@ SIGNATURES = {
     "npd_kv_migrate": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_int, c_void_p, c_void_p]),
+    "npd_testing_kv_migrate_withheld": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                                c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                                c_int64, c_int, c_void_p, c_void_p, c_int64, c_int64]),
     "npd_qk_norm_rope_store": (c_int, [c_void_p] * 8 + [c_float] + [c_void_p] * 4 + [c_int64] * 14 +
                                [c_int, c_void_p, c_void_p]),
     "npd_top_k_sample_workspace_bytes": (c_int64, [c_int64, c_int64, c_int]),

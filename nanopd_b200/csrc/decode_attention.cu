@@ -680,16 +680,19 @@ LaunchShape launch_shape(int head_dim, int block_size, int cta_cap, long long nu
     LaunchShape ls;
     const int stage_bytes = 2 * kTile * head_dim * 2;
     const int sms = npd::sm_count(device);
-    ls.grid = env_int("NPD_DECODE_CTAS", sms);
+    // tuning knobs from the environment, read once per process
+    static const int knob_ctas = env_int("NPD_DECODE_CTAS", 0), knob_warps = env_int("NPD_DECODE_WARPS", 0),
+                     knob_stages = env_int("NPD_DECODE_STAGES", 0);
+    ls.grid = knob_ctas > 0 ? knob_ctas : sms;
     if (cta_cap > 0 && cta_cap < ls.grid) ls.grid = cta_cap;
     int warps = 8, stages = 2;
     if (head_dim == 256) stages = 1;
     // a handful of long sequences: every worker has few tiles and the launch is latency-bound, a deeper ring helps
     if (head_dim == 128 && num_seq_heads < 64) stages = 3;
     if (head_dim == 64 || (head_dim == 128 && (block_size < 16 || ls.grid * 100 < sms * 85))) warps = 12;
-    ls.nwarps = env_int("NPD_DECODE_WARPS", warps);
+    ls.nwarps = knob_warps > 0 ? knob_warps : warps;
     if (ls.nwarps > NPD_DECODE_MAX_WARPS) ls.nwarps = NPD_DECODE_MAX_WARPS;   // the kernel's launch bound
-    int nst = env_int("NPD_DECODE_STAGES", stages);
+    int nst = knob_stages > 0 ? knob_stages : stages;
     while (nst > 1 && (long long)ls.nwarps * nst * stage_bytes > 192 * 1024) --nst;
     ls.nstages = nst;
     return ls;
@@ -939,7 +942,15 @@ extern "C" int npd_paged_decode_attention_static(void *out, const void *q, const
     // The array keeps whatever the previous call left.  The status word must start at zero, and so must the
     // arrival tickets: the kernel leaves them at zero itself, except when an earlier launch gave up on a bounded
     // wait — and this caller has no pointer to clean up with.  The partial records are written before they are read.
-    NPD_CUDA_TRY(cudaMemsetAsync(scratch, 0, kStatusBytes + (size_t)kTicketCapacity * sizeof(int32_t), st));
+    // Only the tickets one launch can touch are cleared: one per (sequence of a sub-batch, virtual kv head).
+    const LaunchShape ls = launch_shape(static_cast<int>(head_dim), static_cast<int>(block_size), (flags >> 8) & 0xffff,
+                                        (long long)num_seqs * num_kv_heads, dev);
+    const WorkspacePlan wp = plan_workspace(num_seqs, num_q_heads, num_kv_heads, head_dim, ls);
+    const int64_t vheads = num_kv_heads * wp.kv_rep;
+    int64_t batch_cap = vheads > 0 ? kTicketCapacity / vheads : 0;
+    if (batch_cap > kMaxSeqsPerLaunch) batch_cap = kMaxSeqsPerLaunch;
+    const int64_t tickets = (num_seqs < batch_cap ? num_seqs : batch_cap) * vheads;
+    NPD_CUDA_TRY(cudaMemsetAsync(scratch, 0, kStatusBytes + (size_t)tickets * sizeof(int32_t), st));
     const int rc = npd_paged_decode_attention(out, q, k_cache, v_cache, block_tables, seq_lens, scale, num_seqs,
                                               num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
                                               num_blocks, cache_block_stride, bt_row_stride, dtype, scratch,

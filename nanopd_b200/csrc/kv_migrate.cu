@@ -12,11 +12,14 @@
 //     bulk groups): copies in flight without occupying registers or issue slots, in a CTA small
 //     enough (one warp, 64 KiB) to sit beside a decode-attention CTA on the same SM.  No multicast.
 //   * ld/st: 256 threads per CTA, 16-byte loads and stores, eight loads in flight per thread —
-//     used when a unit is not a multiple of 16 bytes wide enough for the bulk path.
+//     taken when one side is pinned host memory (the relay buffer of extract_kv_to_pinned /
+//     load_kv_from_pinned, nanoPD/workers/kv_transfer.py:44-66, reached over PCIe through the
+//     unified address space), or on request.
 // Link- or HBM-bound: blocks * layers * 2 * block_bytes, one direction.
 #include <cstdlib>
 
 #include "npd_common.cuh"
+#include "../../include/nanopd_b200_testing.h"
 
 namespace {
 
@@ -42,6 +45,8 @@ struct MigrateParams {
     int pieces_per_unit;      // bulk path: a unit is moved in pieces of at most piece_bytes
     int piece_bytes;          // bulk path: bytes per ring stage (a multiple of 16)
     int stages;               // bulk path: ring depth (<= kMaxBulkStages)
+    long long wait_limit;     // bulk path: clocks a wait for a load may take before the kernel gives up
+    long long withhold_piece; // testing only: this piece's load is announced but never issued (-1 = none)
 };
 
 constexpr int kThreads = 256;
@@ -139,7 +144,7 @@ __global__ void __launch_bounds__(32) kv_migrate_bulk_kernel(const MigrateParams
         return true;
     };
 
-    bool dead = false;
+    long long dead_at = -1;
     long long issued = 0;
     auto issue_load = [&](long long i) {
         const int st = static_cast<int>(i % kBulkStages);
@@ -149,18 +154,19 @@ __global__ void __launch_bounds__(32) kv_migrate_bulk_kernel(const MigrateParams
         const uint32_t bar = smem_u32(&bars[st]);
         if (piece_ptrs(i, src, dst, bytes)) {
             mbar_expect_tx(bar, bytes);
-            bulk_g2s(smem_u32(smem + (size_t)st * kPieceBytes), src, bytes, bar);
+            if (blockIdx.x + i * gridDim.x != p.withhold_piece)
+                bulk_g2s(smem_u32(smem + (size_t)st * kPieceBytes), src, bytes, bar);
         } else {
             mbar_arrive(bar);          // skipped piece: keep the ring's phases in step
         }
     };
     for (; issued < my_count && issued < kBulkStages - 1; ++issued) issue_load(issued);
 
-    for (long long i = 0; i < my_count && !dead; ++i) {
+    for (long long i = 0; i < my_count; ++i) {
         const int st = static_cast<int>(i % kBulkStages);
-        if (!mbar_wait_bounded(smem_u32(&bars[st]), static_cast<uint32_t>((i / kBulkStages) & 1))) {
+        if (!mbar_wait_bounded(smem_u32(&bars[st]), static_cast<uint32_t>((i / kBulkStages) & 1), p.wait_limit)) {
             if (p.status) atomicOr(p.status, NPD_STATUS_WAIT_TIMEOUT);
-            dead = true;
+            dead_at = i;
             break;
         }
         const uint8_t *src;
@@ -176,17 +182,26 @@ __global__ void __launch_bounds__(32) kv_migrate_bulk_kernel(const MigrateParams
             ++issued;
         }
     }
+    if (dead_at >= 0) {
+        // Loads issued behind the one that never arrived may still be writing this CTA's shared memory: give each a
+        // bounded chance to land before the CTA ends and the SM hands the memory to another CTA.
+        for (long long j = dead_at + 1; j < issued; ++j)
+            (void)mbar_wait_bounded(smem_u32(&bars[j % kBulkStages]), static_cast<uint32_t>((j / kBulkStages) & 1),
+                                    200000000LL);
+    }
     bulk_wait_all();     // all stores have landed before the kernel (and its stream position) completes
 }
 
 }  // namespace
 
-extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
-                              const int32_t *src_blocks, const int32_t *dst_blocks, int64_t num_pairs,
-                              int64_t num_layers, int64_t block_elems, int elem_bytes,
-                              int64_t src_layer_stride, int64_t src_block_stride, int64_t src_num_blocks,
-                              int64_t dst_layer_stride, int64_t dst_block_stride, int64_t dst_num_blocks,
-                              int max_ctas, int32_t *status, void *stream) {
+namespace {
+
+int kv_migrate_impl(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
+                    const int32_t *src_blocks, const int32_t *dst_blocks, int64_t num_pairs,
+                    int64_t num_layers, int64_t block_elems, int elem_bytes,
+                    int64_t src_layer_stride, int64_t src_block_stride, int64_t src_num_blocks,
+                    int64_t dst_layer_stride, int64_t dst_block_stride, int64_t dst_num_blocks,
+                    int max_ctas, int32_t *status, void *stream, long long withhold_piece, long long wait_limit) {
     NPD_REQUIRE(num_pairs >= 0 && num_layers > 0 && block_elems > 0 && elem_bytes > 0, NPD_ERR_INVALID_ARG,
                 "npd_kv_migrate: non-positive dimension");
     if (num_pairs == 0) return NPD_OK;
@@ -223,6 +238,8 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
     p.dst_block_stride = dst_block_stride * elem_bytes;
     p.src_num_blocks = static_cast<int>(src_num_blocks);
     p.dst_num_blocks = static_cast<int>(dst_num_blocks);
+    p.withhold_piece = withhold_piece;
+    p.wait_limit = wait_limit > 0 ? wait_limit : 4000000000LL;
     // Ring of the bulk path: 4 stages of 16 KiB.  64 KiB of shared memory and one warp fit beside a decode-attention
     // CTA on the same SM (132 KiB, 8 warps x 224 registers), so a migration on a side stream does not take SMs away
     // from the compute stream; 64 such CTAs keep ~3 MB in flight, enough for an NVLink on every box seen (with 48 the
@@ -230,13 +247,21 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
     // A copy between two pools of ONE GPU has three times an NVLink's bandwidth to fill and nothing to gain from
     // being small: it takes the larger ring (6 x 32 KiB).
     cudaPointerAttributes src_attr{}, dst_attr{};
-    const bool same_gpu = cudaPointerGetAttributes(&src_attr, src_k) == cudaSuccess &&
-                          cudaPointerGetAttributes(&dst_attr, dst_k) == cudaSuccess &&
-                          src_attr.type == cudaMemoryTypeDevice && dst_attr.type == cudaMemoryTypeDevice &&
-                          src_attr.device == dst_attr.device;
+    const bool known = cudaPointerGetAttributes(&src_attr, src_k) == cudaSuccess &&
+                       cudaPointerGetAttributes(&dst_attr, dst_k) == cudaSuccess;
     (void)cudaGetLastError();
-    p.piece_bytes = env_int("NPD_MIGRATE_PIECE_KB", same_gpu ? 32 : 16) * 1024;
-    p.stages = env_int("NPD_MIGRATE_STAGES", same_gpu ? 6 : 4);
+    const bool same_gpu = known && src_attr.type == cudaMemoryTypeDevice && dst_attr.type == cudaMemoryTypeDevice &&
+                          src_attr.device == dst_attr.device;
+    // One side in pinned host memory (the relay buffer): plain loads and stores over PCIe, a small grid.
+    const bool host_side = known && (src_attr.type == cudaMemoryTypeHost || dst_attr.type == cudaMemoryTypeHost);
+    if (known)
+        NPD_REQUIRE(src_attr.type != cudaMemoryTypeUnregistered && dst_attr.type != cudaMemoryTypeUnregistered,
+                    NPD_ERR_INVALID_ARG, "npd_kv_migrate: a pool lies in pageable host memory (pin it first)");
+    if (host_side && max_ctas >= 0) max_ctas = max_ctas > 0 ? -max_ctas : -32;
+    // tuning knobs from the environment, read once per process
+    static const int knob_piece_kb = env_int("NPD_MIGRATE_PIECE_KB", 0), knob_stages = env_int("NPD_MIGRATE_STAGES", 0);
+    p.piece_bytes = (knob_piece_kb > 0 ? knob_piece_kb : (same_gpu ? 32 : 16)) * 1024;
+    p.stages = knob_stages > 0 ? knob_stages : (same_gpu ? 6 : 4);
     if (p.stages > kMaxBulkStages) p.stages = kMaxBulkStages;
     if (p.stages < 2) p.stages = 2;
     while ((long long)p.piece_bytes * p.stages > 200 * 1024 && p.piece_bytes > 4096) p.piece_bytes /= 2;
@@ -270,4 +295,34 @@ extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k,
     }
     NPD_CUDA_TRY(cudaGetLastError());
     return NPD_OK;
+}
+
+}  // namespace
+
+extern "C" int npd_kv_migrate(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
+                              const int32_t *src_blocks, const int32_t *dst_blocks, int64_t num_pairs,
+                              int64_t num_layers, int64_t block_elems, int elem_bytes,
+                              int64_t src_layer_stride, int64_t src_block_stride, int64_t src_num_blocks,
+                              int64_t dst_layer_stride, int64_t dst_block_stride, int64_t dst_num_blocks,
+                              int max_ctas, int32_t *status, void *stream) {
+    return kv_migrate_impl(src_k, src_v, dst_k, dst_v, src_blocks, dst_blocks, num_pairs, num_layers, block_elems,
+                           elem_bytes, src_layer_stride, src_block_stride, src_num_blocks, dst_layer_stride,
+                           dst_block_stride, dst_num_blocks, max_ctas, status, stream, -1, 0);
+}
+
+extern "C" int npd_testing_kv_migrate_withheld(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
+                                               const int32_t *src_blocks, const int32_t *dst_blocks, int64_t num_pairs,
+                                               int64_t num_layers, int64_t block_elems, int elem_bytes,
+                                               int64_t src_layer_stride, int64_t src_block_stride,
+                                               int64_t src_num_blocks, int64_t dst_layer_stride,
+                                               int64_t dst_block_stride, int64_t dst_num_blocks, int max_ctas,
+                                               int32_t *status, void *stream, int64_t withhold_piece,
+                                               int64_t wait_limit_clocks) {
+    NPD_REQUIRE(max_ctas > 0, NPD_ERR_INVALID_ARG, "npd_testing_kv_migrate_withheld: the bulk path only (max_ctas > 0)");
+    NPD_REQUIRE(wait_limit_clocks > 0 && wait_limit_clocks <= 2000000000LL, NPD_ERR_INVALID_ARG,
+                "npd_testing_kv_migrate_withheld: wait limit must be in (0, 2e9] clocks");
+    return kv_migrate_impl(src_k, src_v, dst_k, dst_v, src_blocks, dst_blocks, num_pairs, num_layers, block_elems,
+                           elem_bytes, src_layer_stride, src_block_stride, src_num_blocks, dst_layer_stride,
+                           dst_block_stride, dst_num_blocks, max_ctas, status, stream, withhold_piece,
+                           wait_limit_clocks);
 }

@@ -13,6 +13,10 @@
 
 #include "../../include/nanopd_b200.h"
 
+// Internal diagnostic flag of the decode launcher (bit 0 of `flags`): sequences split across workers stay
+// unmerged, which leaves wrong rows for those.  Not part of the public ABI.
+#define NPD_DECODE_SKIP_MERGE 1
+
 // ---------------------------------------------------------------------------
 // Host-side error plumbing: every entry point returns a code and leaves a message.
 // ---------------------------------------------------------------------------

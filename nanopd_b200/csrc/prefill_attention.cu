@@ -1,22 +1,26 @@
 // Kernel 3: chunked-prefill causal attention over paged K/V on the 5th-generation tensor cores.
 //
-// One CTA computes a 128-row query tile for one kv head: the rows are TQ = 128/G consecutive
-// query tokens of a chunk times the G q heads that share the kv head (token-major), so every
-// K/V tile read from the pages serves the whole group.  Keys are walked in tiles of 128
-// (8 pages of 16 tokens) from position 0 up to the tile's last query position — earlier chunks
-// are read from the pages like any other key, which the reference's prefill branch does not do
+// A work item is a PAIR of 128-row query tiles of one chunk and one kv head: the rows of a tile are
+// TQ = 128/G consecutive query tokens times the G q heads that share the kv head (token-major), so every
+// K/V tile read from the pages serves the whole group and both tiles.  Keys are walked in tiles of 128
+// (8 pages of 16 tokens) from position 0 up to the tile's last query position — earlier chunks are read
+// from the pages like any other key, which the reference's prefill branch does not do
 // (nanoPD/engine/model_runner.py:125-127,152-168 attends to the current chunk only).
 //
-// Warp roles (192 threads):
-//   warps 0-3  softmax + accumulate: thread i owns row i == TMEM lane i (no shuffles needed)
-//   warp  4    TMA producer: Q tile once, then K/V tiles into a 2-stage shared-memory ring
-//              (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA operand layout)
-//   warp  5    TMEM allocation and the single thread that issues tcgen05.mma
-// Per key tile:  S = Q.K^T  (tcgen05.mma, fp32 accumulator in TMEM columns 0-127)
-//                P = exp2(S*scale - m) rounded to the input type, written to shared memory in the
-//                    K-major swizzled layout (masking only on tiles that touch the diagonal)
-//                PV = P.V   (tcgen05.mma with V as the MN-major B operand, TMEM columns 128-255)
-//                O  = O*alpha + PV  in fp32 registers of the row's thread.
+// Persistent grid, one CTA of 384 threads per SM; items are handed out heaviest first through an atomic
+// counter.  Warp roles:
+//   warps 0-3 / 4-7  softmax of query tile A / B: thread i owns row i == TMEM lane i (no shuffles)
+//   warp  8          TMA producer: query tiles, then K and V tiles into two 2-stage shared-memory rings
+//                    (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA operand layout); it also
+//                    draws the next work item and publishes it to the other roles
+//   warps 9 / 10     issue the tcgen05.mma instructions of tile A / B (one elected lane)
+//   warp  11         idle (completes the third warpgroup for setmaxnreg)
+// TMEM (512 columns): S_A | S_B | O_A | O_B, 128 columns each.  Per key tile and query tile:
+//   S = Q.K^T        tcgen05.mma, both operands in shared memory, fp32 scores in TMEM
+//   P = exp2(S*scale - m), rounded to the input type and written back to TMEM over the first 64 score
+//       columns (masking only on tiles that touch the diagonal)
+//   O += P.V         tcgen05.mma with P as the TMEM A operand and V as the MN-major B operand; O stays in
+//       TMEM and is rescaled only when a row maximum grows by more than 2^8, then read once in the epilogue.
 // Completion of MMAs is tracked with tcgen05.commit on mbarriers; every wait is bounded and an
 // abort flag lets all roles leave together, after which TMEM is released.
 //

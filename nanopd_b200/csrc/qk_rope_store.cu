@@ -116,7 +116,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStore
             const T *src = kd == 0 ? static_cast<const T *>(p.q) + t * p.q_token_stride
                          : kd == 1 ? static_cast<const T *>(p.k) + t * p.k_token_stride
                                    : static_cast<const T *>(p.v) + t * p.v_token_stride;
-            raw[u] = __ldg(reinterpret_cast<const uint4 *>(src + (long long)h * D + sub * 8));
+            // a plain (coherent) load: q_out may alias q, and a non-coherent load of memory the same kernel writes
+            // is undefined
+            raw[u] = *reinterpret_cast<const uint4 *>(src + (long long)h * D + sub * 8);
             if (kd != 2) {
                 craw[u] = __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.cos) + t * p.cs_row_stride + sub * 8));
                 sraw[u] = __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.sin) + t * p.cs_row_stride + sub * 8));

@@ -577,8 +577,10 @@ Plan plan_for(int64_t rows, int64_t vocab, int elem, int top_k, int sms) {
     plan.slices = slices_of(vocab, kThreads * kLoads * (16 / elem));
     plan.items = rows * plan.slices;
     const int max_parts = kSliceCandidates / top_k;
-    int64_t forced = 0;
-    if (const char *env = getenv("NPD_SAMPLE_CTAS")) forced = atoll(env);      // for experiments
+    static const int64_t forced = [] {                                         // for experiments; read once per process
+        const char *env = getenv("NPD_SAMPLE_CTAS");
+        return env ? atoll(env) : 0LL;
+    }();
     if (rows <= 2 * sms && (forced < 1 || forced > plan.items)) {
         int64_t per_row = 2 * sms / rows;
         if (per_row > plan.slices) per_row = plan.slices;

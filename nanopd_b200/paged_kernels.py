@@ -44,17 +44,29 @@ _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
 def _workspace(device: torch.device, stream_handle: int, nbytes: int) -> torch.Tensor:
     key = (device.index, stream_handle)
+    ws = _workspaces.get(key)                 # dict reads are atomic under the GIL: the common case takes no lock
+    if ws is not None and ws.numel() >= nbytes:
+        return ws
     with _ws_lock:
         ws = _workspaces.get(key)
         if ws is None or ws.numel() < nbytes:
-            carry = 0
+            grown = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
             if ws is not None:
-                carry = int(ws[:4].view(torch.int32).item())
-            ws = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
-            if carry:
-                ws[:4].view(torch.int32).fill_(carry)
-            _workspaces[key] = ws
+                grown[:4].copy_(ws[:4])       # carry the status word over, on the device (no host wait)
+            _workspaces[key] = ws = grown
         return ws
+
+
+def release_workspaces(device=None) -> None:
+    """Drops the cached per-stream workspaces of ``device`` (default: all devices), e.g. after destroying the
+    streams they belonged to.  Synchronises the devices concerned first; the next call on a stream makes a new one."""
+    with _ws_lock:
+        idx = None if device is None else torch.device(device).index
+        keys = [k for k in _workspaces if idx is None or k[0] == idx]
+        for d in {k[0] for k in keys}:
+            torch.cuda.synchronize(d)
+        for k in keys:
+            del _workspaces[k]
 
 
 def check_status(device=None, raise_on_error: bool = True) -> int:
@@ -365,15 +377,29 @@ def _pool_geometry(pool: torch.Tensor, name: str):
     return L, nb, block_elems, pool.stride(0), pool.stride(1)
 
 
+def _block_list(ids, dev: torch.device) -> torch.Tensor:
+    """A block list as an int32 tensor on ``dev``.  A Python list goes through pinned host memory and a
+    non-blocking copy on the current stream, so the calling thread never waits behind work already queued on
+    that stream (a pageable source would make the copy synchronous with the stream's earlier work)."""
+    if torch.is_tensor(ids):
+        return ids
+    host = torch.tensor(list(ids), dtype=torch.int32)
+    if host.numel() == 0:
+        return host.to(dev)
+    return host.pin_memory().to(dev, non_blocking=True)
+
+
 def paged_kv_migrate(src_k, src_v, dst_k, dst_v, src_blocks, dst_blocks=None, max_ctas: int = 0) -> None:
     """Copy blocks ``src_blocks[i] -> dst_blocks[i]`` of every layer between two 5-D pools.
 
     One kernel on the current stream of the CURRENT device, which must be able to address
-    both pools (same device, or peer access enabled — see ``kv_transfer.transfer_kv``).
-    ``src_blocks``/``dst_blocks``: int32 tensors on the current device (or Python lists,
-    which are copied there).  ``max_ctas`` > 0 caps the grid of the bulk-copy kernel (one warp
-    per CTA; 0 = 32 CTAs) so a side-stream migration leaves the SMs to compute; a negative value
-    selects the plain load/store kernel with that many CTAs.
+    both pools (same device, or peer access enabled — see ``kv_transfer.transfer_kv``).  One of the
+    two pools may be a PINNED host buffer (``kv_transfer.PinnedKVBuffer``): the kernel then reads or writes
+    it over PCIe through the unified address space with plain loads and stores.
+    ``src_blocks``/``dst_blocks``: int32 tensors on the current device, or Python lists, which are staged in
+    pinned memory and copied there without blocking the host.  ``max_ctas`` > 0 caps the grid of the
+    bulk-copy kernel (one warp per CTA; 0 = 64 CTAs) so a side-stream migration leaves the SMs to compute; a
+    negative value selects the plain load/store kernel with that many CTAs.
     """
     dev = torch.device("cuda", torch.cuda.current_device())
     L, snb, belems, sls, sbs = _pool_geometry(src_k, "src_k")
@@ -382,12 +408,11 @@ def paged_kv_migrate(src_k, src_v, dst_k, dst_v, src_blocks, dst_blocks=None, ma
     _require(_pool_geometry(dst_v, "dst_v") == (L2, dnb, belems2, dls, dbs), "dst_k and dst_v layouts differ")
     _require(L == L2 and belems == belems2 and src_k.dtype == dst_k.dtype == src_v.dtype == dst_v.dtype,
              "source and destination pools differ in layers, block shape or dtype")
-    if not torch.is_tensor(src_blocks):
-        src_blocks = torch.tensor(list(src_blocks), dtype=torch.int32, device=dev)
-    if dst_blocks is None:
-        dst_blocks = src_blocks
-    elif not torch.is_tensor(dst_blocks):
-        dst_blocks = torch.tensor(list(dst_blocks), dtype=torch.int32, device=dev)
+    for name, pool in (("src_k", src_k), ("src_v", src_v), ("dst_k", dst_k), ("dst_v", dst_v)):
+        _require(pool.is_cuda or pool.is_pinned(), f"{name} must be a CUDA tensor or a pinned host tensor")
+    _require(src_k.is_cuda or dst_k.is_cuda, "one of the two pools must be on a GPU")
+    src_blocks = _block_list(src_blocks, dev)
+    dst_blocks = src_blocks if dst_blocks is None else _block_list(dst_blocks, dev)
     _require(src_blocks.dtype == torch.int32 and dst_blocks.dtype == torch.int32, "block lists must be int32")
     _require(src_blocks.device == dev and dst_blocks.device == dev, "block lists must live on the current device")
     _require(src_blocks.numel() == dst_blocks.numel() and src_blocks.is_contiguous() and dst_blocks.is_contiguous(),

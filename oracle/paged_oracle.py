@@ -257,6 +257,22 @@ def kv_migrate(src_k, src_v, dst_k, dst_v, src_blocks, dst_blocks=None):
         dst_v[:, int(db)].copy_(src_v[:, int(sb)])
 
 
+def extract_kv_to_buffer(k_cache, v_cache, block_table, buf_k, buf_v):
+    """The sending half of the pinned relay (nanoPD/workers/kv_transfer.py:44-52):
+    ``buf[:, i] = cache[:, block_table[i]]`` on ``[L, blocks, Hkv, B, D]`` tensors."""
+    for i, bid in enumerate(block_table):
+        buf_k[:, i].copy_(k_cache[:, int(bid)])
+        buf_v[:, i].copy_(v_cache[:, int(bid)])
+
+
+def load_kv_from_buffer(k_cache, v_cache, block_table, buf_k, buf_v):
+    """The receiving half of the pinned relay (nanoPD/workers/kv_transfer.py:55-66):
+    ``cache[:, block_table[i]] = buf[:, i]``."""
+    for i, bid in enumerate(block_table):
+        k_cache[:, int(bid)].copy_(buf_k[:, i])
+        v_cache[:, int(bid)].copy_(buf_v[:, i])
+
+
 # ---------------------------------------------------------------------------
 # Algorithmic work (the figures the benchmark's roofline uses)
 # ---------------------------------------------------------------------------

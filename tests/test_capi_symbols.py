@@ -8,12 +8,15 @@ import pytest
 
 from nanopd_b200 import _lib
 
-HEADER = Path(__file__).resolve().parents[1] / "include" / "nanopd_b200.h"
+HEADERS = sorted((Path(__file__).resolve().parents[1] / "include").glob("*.h"))
 
 
 def declared_symbols():
-    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return sorted(set(re.findall(r"\b(npd_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in HEADERS:
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        names.update(re.findall(r"\b(npd_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_declares_the_four_kernels():

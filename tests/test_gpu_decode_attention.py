@@ -2,6 +2,7 @@
 
 Tolerance (max-abs against the fp32-accumulated oracle): 2e-3 for fp16, 1e-2 for bf16."""
 import math
+import os
 
 import numpy as np
 import pytest
@@ -170,13 +171,11 @@ def test_config2_quarter_batch_vs_oracle(kernels):
     assert (out - want).abs().max().item() <= TOL[torch.bfloat16]
 
 
-def test_config2_full_size_properties(kernels):
-    """Configuration 2 at full size (batch 256, ~1.5 GB of K/V).
-
-    Size-independent properties: (i) a sequence's row does not depend on what else is in the
-    batch (different work partition, same answer); (ii) rows are convex combinations of V
-    rows, so every output lies inside the value range of its sequence; (iii) a sample of
-    sequences agrees with the oracle."""
+def test_config2_full_size_vs_oracle(kernels):
+    """Configuration 2 at full size (batch 256, ~1.5 GB of K/V): every sequence against the oracle, plus two
+    size-independent properties: (i) a sequence's row does not depend on what else is in the batch (different
+    work partition, same answer); (ii) rows are convex combinations of V rows, so every output lies inside the
+    value range."""
     b = workloads.make_config2(device=DEV, seed=0, batch=256)
     out = run_kernel(kernels, b.query, b.k_cache, b.v_cache, b.block_tables, b.ctx_lens, b.scale)
     assert torch.isfinite(out).all()
@@ -186,9 +185,10 @@ def test_config2_full_size_properties(kernels):
                        b.block_tables[idx].contiguous(), b.ctx_lens[idx].contiguous(), b.scale)
     assert (alone.float() - out[idx].float()).abs().max().item() <= 4e-3
     assert out.float().abs().max().item() <= b.v_cache.float().abs().max().item() * 1.01
-    want = paged_oracle.paged_decode_attention(b.query[idx].cpu(), b.k_cache.cpu(), b.v_cache.cpu(),
-                                               b.block_tables[idx].cpu(), b.ctx_lens[idx].cpu(), b.scale)
-    assert (out[idx].float().cpu() - want).abs().max().item() <= TOL[torch.bfloat16]
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    want = paged_oracle.paged_decode_attention(b.query.cpu(), b.k_cache.cpu(), b.v_cache.cpu(),
+                                               b.block_tables.cpu(), b.ctx_lens.cpu(), b.scale)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL[torch.bfloat16]
 
 
 def test_skip_merge_flag_only_affects_split_sequences(kernels):

@@ -74,3 +74,18 @@ def test_ops_reject_cpu_tensors_with_runtime_error():
     with pytest.raises(RuntimeError):
         paged_kernels.paged_kv_store(kc, kc, torch.zeros(4, 1, 128, dtype=torch.float16),
                                      torch.zeros(4, 1, 128, dtype=torch.float16), bt, sl)
+
+
+def test_kv_transfer_exports_the_reference_module_names():
+    """The reference's workers import these at module load (nanoPD/workers/prefill_worker.py:10,
+    nanoPD/workers/decode_worker.py:11)."""
+    from nanopd_b200.kv_transfer import (PinnedKVBuffer, _check_p2p, extract_kv_to_pinned,  # noqa: F401
+                                         load_kv_from_pinned, transfer_kv)
+    import inspect
+    assert list(inspect.signature(transfer_kv).parameters)[:7] == ["src_k", "src_v", "dst_k", "dst_v", "block_table",
+                                                                   "stream", "buf"]
+    assert list(inspect.signature(extract_kv_to_pinned).parameters)[:4] == ["k_cache", "v_cache", "block_table", "buf"]
+    assert list(inspect.signature(load_kv_from_pinned).parameters)[:5] == ["k_cache", "v_cache", "block_table", "buf",
+                                                                          "stream"]
+    assert list(inspect.signature(PinnedKVBuffer.__init__).parameters)[1:] == ["num_layers", "num_block", "num_kv_heads",
+                                                                               "block_size", "head_dim", "dtype"]
