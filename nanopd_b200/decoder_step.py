@@ -89,10 +89,16 @@ class SyntheticDecoder:
 
     # ---- batch state -------------------------------------------------------------------------------------
     def attach_batch(self, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
-                     ctx_lens: torch.Tensor, token_ids: torch.Tensor) -> None:
+                     ctx_lens: torch.Tensor, token_ids: torch.Tensor, active: Optional[torch.Tensor] = None) -> None:
         """``k_cache``/``v_cache`` ``[L, blocks, Hkv, B, D]`` (the reference's pool layout, model_runner.py:24-31),
         ``block_tables`` int32 ``[S, max_blk]`` with room for the tokens to come, ``ctx_lens`` int32 ``[S]`` tokens
-        already in the pool, ``token_ids`` int64 ``[S]`` the tokens to feed first."""
+        already in the pool, ``token_ids`` int64 ``[S]`` the tokens to feed first.
+
+        ``active`` (int32 ``[S]`` of 0/1, optional) turns the batch into a table of SLOTS for continuous batching:
+        a step advances only the rows whose entry is 1.  An idle slot keeps ``seq_lens == 0`` (its attention row is
+        zero) and position 0 of whatever block its table row names, so give idle rows a block nobody reads.  The
+        four state tensors (``block_tables``, ``positions``, ``seq_lens``, ``active``) and ``token_ids`` may be
+        rewritten in place between steps — also between replays of a captured step."""
         s = self.shape
         if k_cache.dim() != 5 or k_cache.size(0) != s.num_layers or k_cache.size(2) != s.num_kv_heads or k_cache.size(4) != s.head_dim:
             raise RuntimeError("k_cache must be [num_layers, blocks, Hkv, B, D] for this decoder's shape")
@@ -100,13 +106,22 @@ class SyntheticDecoder:
         self.block_size = k_cache.size(3)
         self.block_tables = block_tables
         self.positions = ctx_lens.clone()                       # slot of the token being fed
-        self.seq_lens = ctx_lens + 1
+        self.active = active
+        self.seq_lens = ctx_lens + 1 if active is None else (ctx_lens + 1) * active
         self.token_ids = token_ids.clone()
         S = token_ids.numel()
         self.q_rot = torch.empty(S, s.num_q_heads, s.head_dim, dtype=self.dtype, device=self.device)
         self.attn_out = torch.empty_like(self.q_rot)
         self.uniforms = torch.zeros(S, dtype=torch.float32, device=self.device)
         self._graph = None
+
+    def detach_batch(self) -> None:
+        """Drops the batch state, the pools and the captured step (and with it the memory the capture holds)."""
+        self._graph = None
+        for name in ("k_cache", "v_cache", "block_tables", "positions", "seq_lens", "active", "token_ids", "q_rot",
+                     "attn_out", "uniforms", "logits"):
+            if hasattr(self, name):
+                delattr(self, name)
 
     # ---- one decode step -----------------------------------------------------------------------------------
     def _forward(self) -> None:
@@ -138,8 +153,12 @@ class SyntheticDecoder:
             self.uniforms.uniform_()
         sampling.top_k_sample(logits, self.top_k, uniforms=self.uniforms if self.top_k > 1 else None,
                               out=self.token_ids)
-        self.positions.add_(1)
-        self.seq_lens.add_(1)
+        if self.active is None:
+            self.positions.add_(1)
+            self.seq_lens.add_(1)
+        else:
+            self.positions.add_(self.active)
+            self.seq_lens.add_(self.active)
 
     def step(self) -> None:
         """One token for every sequence, eagerly (one launch per op)."""
@@ -153,8 +172,8 @@ class SyntheticDecoder:
         keep = self.token_ids.clone()
         with torch.cuda.stream(side):
             self._forward()
-            self.positions.sub_(1)
-            self.seq_lens.sub_(1)
+            self.positions.sub_(1 if self.active is None else self.active)
+            self.seq_lens.sub_(1 if self.active is None else self.active)
             self.token_ids.copy_(keep)
         side.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -175,14 +194,17 @@ class SyntheticDecoder:
 
     # ---- one scheduler step with prompt chunks and decode sequences -----------------------------------------
     def mixed_step(self, ctx: dict, token_ids: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                   overlap: bool = True) -> torch.Tensor:
+                   overlap: bool = True, after_layer=None) -> torch.Tensor:
         """Runs the scheduler's step ``ctx`` (the reference's context dict, nanoPD/engine/engine.py:68-90) through
         all layers: ``token_ids`` int64 ``[num_prefill_tokens + num_decode_tokens]`` are the packed prompt-chunk
         tokens followed by one token per decode sequence, ``k_cache``/``v_cache`` the ``[L, blocks, Hkv, B, D]``
         pools.  Tables and positions go to the device once (``build_step_context``); every layer then runs the
         fused norm/rotary/store launches and the two attention kernels (side by side in a mixed step).  Returns
         the logits of the last token of every prompt chunk followed by those of the decode sequences, as the
-        reference samples them (nanoPD/engine/engine.py:96-108).  Eager: the chunk lists are host data."""
+        reference samples them (nanoPD/engine/engine.py:96-108).  Eager: the chunk lists are host data.
+        ``after_layer(layer_index)`` is called once the launches of a layer's store and attention have been
+        issued — the hook a prefill worker uses to start moving that layer's pages to the decode GPU while the
+        remaining layers still compute."""
         from . import paged_forward
         s = self.shape
         sc = paged_forward.build_step_context(ctx, self.device, block_size=k_cache.size(3))
@@ -203,11 +225,13 @@ class SyntheticDecoder:
             v = qkv[:, hq_d + hkv_d:].view(total, s.num_kv_heads, s.head_dim)
             attn = paged_forward.paged_attention_step_fused(sc, q, k, v, cos, sin, k_cache[li], v_cache[li], self.scale,
                                                             L["q_norm"], L["k_norm"], s.eps, overlap=overlap)
+            if after_layer is not None:
+                after_layer(li)
             x = x + F.linear(attn.view(total, hq_d), L["w_o"])
             h = F.rms_norm(x, (s.hidden,), L["post_norm"], s.eps)
             gu = F.linear(h, L["w_gate_up"])
             x = x + F.linear(F.silu(gu[:, :s.ffn]) * gu[:, s.ffn:], L["w_down"])
         last_rows = [off + n - 1 for off, n in zip(sc.prefill_offsets, sc.prefill_tokens)]
         last_rows += list(range(sc.num_prefill_tokens, total))
-        rows = torch.tensor(last_rows, dtype=torch.int64, device=self.device)
+        rows = torch.tensor(last_rows, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
         return F.linear(F.rms_norm(x.index_select(0, rows), (s.hidden,), self.final_norm, s.eps), self.lm_head)

@@ -37,6 +37,22 @@ def barrier():
         dist.barrier()
 
 
+_host_group = None
+
+
+def host_barrier(timeout_s: float = 1800.0):
+    """A barrier that waits on the HOST (a gloo group over the same ranks).  For phases in which one rank drives
+    several GPUs for a long time while the others wait: an NCCL barrier would park a spinning kernel on every
+    waiting rank's GPU, next to the kernels the working rank launches there."""
+    global _host_group
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return
+    if _host_group is None:
+        import datetime
+        _host_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
+    dist.barrier(group=_host_group)
+
+
 def max_over_ranks(value: float, device="cpu") -> float:
     if not (dist.is_available() and dist.is_initialized()):
         return float(value)

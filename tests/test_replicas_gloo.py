@@ -24,6 +24,7 @@ def _worker(rank, world, port, out_dir):
     q, bt, sl = replicas.shard_batch_rows([b.query, b.block_tables, b.ctx_lens], rank, world)
     local = paged_oracle.paged_decode_attention(q, b.k_cache, b.v_cache, bt, sl, b.scale)
     replicas.barrier()
+    replicas.host_barrier()          # the host-side barrier the benchmark uses around its one-rank phases
     full = replicas.gather_rows(local, world)
     # plumbing used by the benchmark: max of per-rank time, sum of per-rank work
     assert replicas.max_over_ranks(float(rank + 1)) == float(world)
