@@ -748,7 +748,7 @@ def run_poisson_workload(args, dev, rates=(2, 4, 8, 16, 32), horizon_s: float = 
     model = serving.build_models([idx], seed=args.seed)[idx]
     out = {"workload": "cfg4: Poisson arrivals, prompts lognormal(512, 0.8) in [16,4096], outputs geometric(256) <= 1024, "
                        "Qwen3-8B shape random init bf16, collocated continuous batching on one GPU",
-           "arrival_window_s": horizon_s, "slots": 256, "prefill_token_budget_per_step": 4096, "rates": {}}
+           "arrival_window_s": horizon_s, "slots": 256, "prefill_token_budget_per_step": 2048, "rates": {}}
     worker = None
     fig, worker = serving.run_poisson(model, 8.0, 1.0, args.seed + 99, worker=worker)      # warm-up (cuBLAS, workspaces)
     for lam in rates:

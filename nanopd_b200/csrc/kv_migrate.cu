@@ -258,6 +258,24 @@ int kv_migrate_impl(const void *src_k, const void *src_v, void *dst_k, void *dst
         NPD_REQUIRE(src_attr.type != cudaMemoryTypeUnregistered && dst_attr.type != cudaMemoryTypeUnregistered,
                     NPD_ERR_INVALID_ARG, "npd_kv_migrate: a pool lies in pageable host memory (pin it first)");
     if (host_side && max_ctas >= 0) max_ctas = max_ctas > 0 ? -max_ctas : -32;
+    if (host_side) {
+        // the kernel needs the DEVICE alias of a pinned host pointer (the same number under unified addressing,
+        // but asked for rather than assumed)
+        const void *ptrs[4] = {p.src_k, p.src_v, p.dst_k, p.dst_v};
+        for (int i = 0; i < 4; ++i) {
+            cudaPointerAttributes a{};
+            NPD_CUDA_TRY(cudaPointerGetAttributes(&a, ptrs[i]));
+            if (a.type == cudaMemoryTypeHost) {
+                NPD_REQUIRE(a.devicePointer != nullptr, NPD_ERR_INVALID_ARG,
+                            "npd_kv_migrate: a pinned host pool is not mapped into the device's address space");
+                ptrs[i] = a.devicePointer;
+            }
+        }
+        p.src_k = static_cast<const uint8_t *>(ptrs[0]);
+        p.src_v = static_cast<const uint8_t *>(ptrs[1]);
+        p.dst_k = static_cast<uint8_t *>(const_cast<void *>(ptrs[2]));
+        p.dst_v = static_cast<uint8_t *>(const_cast<void *>(ptrs[3]));
+    }
     // tuning knobs from the environment, read once per process
     static const int knob_piece_kb = env_int("NPD_MIGRATE_PIECE_KB", 0), knob_stages = env_int("NPD_MIGRATE_STAGES", 0);
     p.piece_bytes = (knob_piece_kb > 0 ? knob_piece_kb : (same_gpu ? 32 : 16)) * 1024;

@@ -145,7 +145,14 @@ def paged_kv_store(k_cache, v_cache, k_src, v_src, block_tables, positions) -> N
     nb, chkv, bs, cd, cstride = _cache_geometry(k_cache, "k_cache")
     _require(_cache_geometry(v_cache, "v_cache") == (nb, chkv, bs, cd, cstride), "k_cache and v_cache layouts differ")
     _require(chkv == hkv and cd == d, "source heads / head_dim do not match the cache")
-    _require(k_src.stride(2) == 1 and v_src.stride() == k_src.stride(), "sources need a contiguous last dim and equal strides")
+    _require(k_src.stride(2) == 1 and v_src.stride(2) == 1, "sources need a contiguous last dim")
+    # The stride of a size-1 dimension means nothing (torch leaves whatever the producing view had, e.g. on the
+    # decode branch's [Hkv, 1, D] slices, nanoPD/engine/model_runner.py:190-193): only real strides must agree.
+    def _strides(t):
+        return (t.stride(0) if hkv > 1 else T * d, t.stride(1) if T > 1 else d)
+    if _strides(k_src) != _strides(v_src):
+        k_src, v_src = k_src.contiguous(), v_src.contiguous()
+    src_head_stride, src_token_stride = _strides(k_src)
     if block_tables.stride(1) != 1 and block_tables.size(1) > 1:
         block_tables = block_tables.contiguous()
     if positions.stride(0) != 1:
@@ -159,7 +166,7 @@ def paged_kv_store(k_cache, v_cache, k_src, v_src, block_tables, positions) -> N
             k_cache.data_ptr(), v_cache.data_ptr(), k_src.data_ptr(), v_src.data_ptr(),
             block_tables.data_ptr(), positions.data_ptr(),
             T, hkv, d, bs, nb, block_tables.size(1),
-            cstride, k_src.stride(0), k_src.stride(1), block_tables.stride(0),
+            cstride, src_head_stride, src_token_stride, block_tables.stride(0),
             _DTYPE_CODE[k_cache.dtype], ws.data_ptr(), handle))
 
 

@@ -246,7 +246,7 @@ def poisson_requests(rate: float, horizon_s: float, vocab: int, seed: int, media
 
 
 def run_poisson(model, rate: float, horizon_s: float, seed: int, num_blocks: int = 20480, capacity: int = 256,
-                token_budget: int = 4096, max_chunk: int = 2048, worker: Optional[workers.CollocatedWorker] = None):
+                token_budget: int = 2048, max_chunk: int = 2048, worker: Optional[workers.CollocatedWorker] = None):
     """One arrival rate on one GPU: returns throughput and latency figures (and the worker, for reuse)."""
     if worker is None:
         worker = workers.CollocatedWorker(model, num_blocks, capacity=capacity, max_context=4096 + 1024,

@@ -465,9 +465,9 @@ class DecodeWorker:
         finished with it."""
         with torch.cuda.device(self.device), torch.cuda.stream(self.compute_stream):
             self._promote_ready()
+            self.slots.flush()              # also when the last request has just left: the slots go back to parked
             if self.slots.table.num_active == 0:
                 return []
-            self.slots.flush()
             if self.record_steps:
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(self.compute_stream)
@@ -489,6 +489,11 @@ class DecodeWorker:
             # Pace the host: at most a few steps queued ahead, so that admissions take effect promptly
             self._pace()
             return done
+
+    def park(self) -> None:
+        """Uploads pending slot changes (after the last request has left, this parks every slot again)."""
+        with torch.cuda.device(self.device), torch.cuda.stream(self.compute_stream):
+            self.slots.flush()
 
     def _pace(self, ahead: int = 2) -> None:
         ev = torch.cuda.Event()
@@ -602,6 +607,9 @@ class DisaggregatedScheduler:
         stop.set()
         for t in threads:
             t.join(timeout=30)
+        for d in self.decode_workers:
+            if hasattr(d, "park"):
+                d.park()
         for w in list(self.prefill_workers) + list(self.decode_workers):
             torch.cuda.synchronize(w.device)
         if self._errors:

@@ -145,3 +145,23 @@ def test_large_store_roundtrip_property(kernels):
     back_k = k_cache[table.long()].permute(1, 0, 2, 3).reshape(heads, T, D)
     back_v = v_cache[table.long()].permute(1, 0, 2, 3).reshape(heads, T, D)
     assert torch.equal(back_k, k_src) and torch.equal(back_v, v_src)
+
+
+def test_single_token_sources_with_leftover_strides(kernels):
+    """The reference's decode branch hands over ``[Hkv, 1, D]`` slices whose size-1 dimension keeps the stride of
+    the view it came from (``v`` is a transposed view, ``k`` a fresh tensor, nanoPD/engine/model_runner.py:104-115,
+    190-193): torch calls both contiguous, their strides differ, and the store must take them."""
+    Hkv, D, B = 4, 128, 16
+    torch.manual_seed(3)
+    k = torch.randn(1, Hkv, 1, D, device="cuda").half()                                 # strides (.., D, D, 1)
+    v = torch.randn(1, 1, Hkv, D, device="cuda").half().transpose(1, 2)                 # strides (.., D, Hkv*D, 1)
+    k_src, v_src = k.squeeze(0).contiguous(), v.squeeze(0).contiguous()
+    assert k_src.stride() != v_src.stride() and k_src.is_contiguous() and v_src.is_contiguous()
+    kc = torch.zeros(3, Hkv, B, D, dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    table = torch.tensor([[2, 0, 1]], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([21], dtype=torch.int32, device="cuda")
+    kernels.paged_kv_store(kc, vc, k_src, v_src, table, pos)
+    torch.cuda.synchronize()
+    assert torch.equal(kc[0, :, 5], k_src[:, 0]) and torch.equal(vc[0, :, 5], v_src[:, 0])
+    assert int(torch.count_nonzero(kc)) == int(torch.count_nonzero(k_src))

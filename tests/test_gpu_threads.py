@@ -17,7 +17,7 @@ def _one_worker(kernels, dev, seed, rounds, use_stream):
     output."""
     torch.cuda.set_device(dev)
     b = workloads.make_decode_batch([300 + 97 * i for i in range(12)], 16, 4, 128, 16, torch.bfloat16, device=dev,
-                                    seed=seed, pool_blocks=600)
+                                    seed=seed, pool_blocks=700)
     g = torch.Generator().manual_seed(seed)
     outs = []
     stream = torch.cuda.Stream(device=dev) if use_stream else torch.cuda.current_stream(dev)
