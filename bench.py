@@ -336,6 +336,32 @@ def graph_device_time_us(fns, dev, replays=5):
     return e0.elapsed_time(e1) / (replays * len(fns)) * 1e3
 
 
+def run_shim_host_cost(paged_kernels, dev, calls=3000):
+    """Host time per call of the two reference ops at the reference's operating size (16 running sequences,
+    nanoPD/engine/engine.py:21): wall time of issuing ``calls`` eager calls, the GPU kept far from being the
+    bottleneck by the small batch, so the figure is the Python shim + ctypes + launch."""
+    b = workloads.make_decode_batch([200] * 16, 32, 8, 128, 16, torch.bfloat16, device=dev, seed=1)
+    out = torch.zeros_like(b.query)
+    lens = b.seq_lens_after_store.contiguous()
+    res = {}
+    for name, fn in (("paged_kv_store", lambda: paged_kernels.paged_kv_store(b.k_cache, b.v_cache, b.k_new, b.v_new,
+                                                                             b.block_tables, b.positions)),
+                     ("paged_attention_forward", lambda: paged_kernels.paged_attention_forward(
+                         out, b.query, b.k_cache, b.v_cache, b.block_tables, lens, b.scale, 16, b.max_blocks))):
+        for _ in range(50):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            fn()
+        host = time.perf_counter() - t0
+        torch.cuda.synchronize()
+        total = time.perf_counter() - t0
+        res[name] = {"host_us_per_call": round(host / calls * 1e6, 2), "us_per_call_until_gpu_idle": round(total / calls * 1e6, 2)}
+    res["batch"] = "16 sequences of 200 tokens, Qwen3-8B shape"
+    return res
+
+
 def run_store_kernel_timing(paged_kernels, b, positions, dev):
     """Device time of the KV store kernel: the decode step's 256 tokens, and an 8192-token prompt.  Sources rotate
     over buffers larger than L2 inside one CUDA graph; GB/s counts the rows read and written plus 8 bytes of
@@ -915,7 +941,7 @@ def run_gpu_arm(args):
     def step():
         paged_kernels.paged_kv_store(b.k_cache, b.v_cache, b.k_new, b.v_new, b.block_tables, positions)
         paged_kernels.paged_attention_forward(out, b.query, b.k_cache, b.v_cache, b.block_tables, seq_lens,
-                                              b.scale, B, max_blk)
+                                              b.scale, B, max_blk, max_ctas=args.max_ctas)
 
     for _ in range(warmup):
         step()
@@ -1139,6 +1165,10 @@ def run_gpu_arm(args):
         except Exception as exc:  # noqa: BLE001
             extras["kv_store_kernel_error"] = str(exc)[:200]
         try:
+            extras["shim_host_cost"] = run_shim_host_cost(paged_kernels, dev)
+        except Exception as exc:  # noqa: BLE001
+            extras["shim_host_cost_error"] = str(exc)[:200]
+        try:
             extras["cfg1"] = run_config1(paged_kernels, dev, args.seed)
         except Exception as exc:  # noqa: BLE001
             extras["cfg1_error"] = str(exc)[:200]
@@ -1235,9 +1265,10 @@ def run_gpu_arm(args):
             "gpu_launches": 2 * steps,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
-                         # DRAM bytes per launch from the ncu capture of a batch-64 case (read 1.0087 x algorithmic,
-                         # plus ~7 MB of partial/output writes), scaled by the tokens processed
-                         "traffic": int(attn_bytes * 1.0087 + 7e6), "traffic_source": "profiles/decode_stream_batch64_ncu_full.md",
+                         # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture of a
+                         # batch-64 case of the same kernel (372.72 MB + 5.92 MB for 369.46 MB of algorithmic bytes),
+                         # scaled by the algorithmic bytes of this launch (traffic grows in proportion)
+                         "traffic": int(attn_bytes * (372.716032 + 5.916160) / 369.46), "traffic_source": "profiles/decode_stream_batch64_ncu_full.md",
                          "peak_source": peak_src,
                          "kernel": "paged_decode_stream_kernel<bf16,128,1>",
                          "algorithmic_bytes_per_launch": attn_bytes, "launch_ms": round(ms_stream_max, 5)},
@@ -1265,6 +1296,9 @@ def main():
     ap.add_argument("--workload", choices=["decode", "prefill", "model", "model-tables", "reference-grid", "sampler", "disagg", "poisson"],
                     default="decode",
                     help="decode = the headline configuration 2 (default); prefill = configuration 3's chunked prefill")
+    ap.add_argument("--max-ctas", type=int, default=0,
+                    help="cap the decode-attention grid (0 = one CTA per SM): the launch shape a mixed step uses when "
+                         "it shares the SMs with a prompt chunk; for profiling that instance")
     ap.add_argument("--profile", action="store_true",
                     help="only warm up and run the timed step loop (for short ncu captures); prints no bench line")
     ap.add_argument("--no-model", action="store_true",

@@ -95,7 +95,55 @@ def check_status(device=None, raise_on_error: bool = True) -> int:
 
 
 def _stream_handle(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    return _raw_stream(device.index)
+
+
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream       # the current stream's handle without building a Stream object
+except AttributeError:                                     # pragma: no cover
+    def _raw_stream(device_index: int) -> int:
+        return torch.cuda.current_stream(device_index).cuda_stream
+
+
+# ---------------------------------------------------------------------------
+# Validated call shapes.  The reference's caller is eager and small (at most 16 running sequences,
+# nanoPD/engine/engine.py:21), where the host cost of a call matters as much as the kernel.  Every op therefore
+# remembers the call shapes it has validated: the key is what the checks look at (shape, strides, dtype and device
+# of every tensor, and the integer arguments), the value the scalar arguments of the C call.  A repeated shape skips
+# the checks; a new one takes the checks and is remembered if it needed no conversion.
+# ---------------------------------------------------------------------------
+_PLAN_LIMIT = 1024
+_store_plans: Dict[tuple, tuple] = {}
+_attn_plans: Dict[tuple, tuple] = {}
+_rope_plans: Dict[tuple, tuple] = {}
+
+
+def _sig(*tensors) -> tuple:
+    return tuple([(t.shape, t.stride(), t.dtype, t.device) for t in tensors])
+
+
+def _remember(table: Dict[tuple, tuple], key: tuple, plan: tuple) -> None:
+    if len(table) >= _PLAN_LIMIT:
+        table.clear()
+    table[key] = plan
+
+
+def _call(dev_index: int, fn, *args) -> None:
+    """The C call with ``dev_index`` current (switching only when it is not)."""
+    if torch.cuda.current_device() == dev_index:
+        rc = fn(*args)
+    else:
+        with torch.cuda.device(dev_index):
+            rc = fn(*args)
+    if rc:
+        _lib.check(rc)
+
+
+def _ws_ptr(dev_index: int, handle: int, nbytes: int):
+    ws = _workspaces.get((dev_index, handle))
+    if ws is None or ws.numel() < nbytes:
+        ws = _workspace(torch.device("cuda", dev_index), handle, nbytes)
+    return ws
 
 
 def _cache_geometry(cache: torch.Tensor, name: str):
@@ -121,6 +169,20 @@ def paged_kv_store(k_cache, v_cache, k_src, v_src, block_tables, positions) -> N
     (tests/test_paged_kernels.py:280,311): sources ``[1, Hkv, T, D]``, a 1-D block table of
     the sequence and an ``int`` start position, meaning token ``t`` sits at ``start + t``.
     """
+    key = None
+    if type(positions) is not int:
+        try:
+            key = _sig(k_cache, v_cache, k_src, v_src, block_tables, positions)
+        except AttributeError:
+            key = None
+        plan = _store_plans.get(key) if key is not None else None
+        if plan is not None:
+            dev_index = plan[0]
+            handle = _raw_stream(dev_index)
+            _call(dev_index, _C.npd_kv_store, k_cache.data_ptr(), v_cache.data_ptr(), k_src.data_ptr(), v_src.data_ptr(),
+                  block_tables.data_ptr(), positions.data_ptr(), *plan[1:], _ws_ptr(dev_index, handle, 256).data_ptr(), handle)
+            return
+    given = (k_src, v_src, block_tables, positions)
     _require(k_src.is_cuda, "k src is must be on CUDA")
     _require(v_src.is_cuda, "v src is must be on CUDA")
     if k_src.dim() == 4 and k_src.size(0) == 1:
@@ -159,15 +221,13 @@ def paged_kv_store(k_cache, v_cache, k_src, v_src, block_tables, positions) -> N
         positions = positions.contiguous()
     if T == 0:
         return
-    handle = _stream_handle(dev)
-    ws = _workspace(dev, handle, 256)
-    with torch.cuda.device(dev):
-        _lib.check(_C.npd_kv_store(
-            k_cache.data_ptr(), v_cache.data_ptr(), k_src.data_ptr(), v_src.data_ptr(),
-            block_tables.data_ptr(), positions.data_ptr(),
-            T, hkv, d, bs, nb, block_tables.size(1),
-            cstride, src_head_stride, src_token_stride, block_tables.stride(0),
-            _DTYPE_CODE[k_cache.dtype], ws.data_ptr(), handle))
+    plan = (dev.index, T, hkv, d, bs, nb, block_tables.size(1), cstride, src_head_stride, src_token_stride,
+            block_tables.stride(0), _DTYPE_CODE[k_cache.dtype])
+    if key is not None and all(a is b for a, b in zip(given, (k_src, v_src, block_tables, positions))):
+        _remember(_store_plans, key, plan)
+    handle = _raw_stream(dev.index)
+    _call(dev.index, _C.npd_kv_store, k_cache.data_ptr(), v_cache.data_ptr(), k_src.data_ptr(), v_src.data_ptr(),
+          block_tables.data_ptr(), positions.data_ptr(), *plan[1:], _ws_ptr(dev.index, handle, 256).data_ptr(), handle)
 
 
 # ---------------------------------------------------------------------------
@@ -187,6 +247,25 @@ def paged_qk_norm_rope_store(q, k, v, cos, sin, k_cache, v_cache, block_tables, 
     Returns the rotated queries ``[T, Hq, D]`` (``q_out``, default: in place over ``q``) — the layout
     ``paged_attention_forward`` and ``paged_prefill_attention`` take.
     """
+    if q_out is None:
+        q_out = q
+    try:
+        key = (_sig(q, k, v, cos, sin, k_cache, v_cache, block_tables, positions, q_out),
+               None if q_norm_weight is None else _sig(q_norm_weight),
+               None if k_norm_weight is None else _sig(k_norm_weight))
+    except AttributeError:
+        key = None
+    plan = _rope_plans.get(key) if key is not None else None
+    if plan is not None:
+        dev_index = plan[0]
+        handle = _raw_stream(dev_index)
+        _call(dev_index, _C.npd_qk_norm_rope_store, q_out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+              None if q_norm_weight is None else q_norm_weight.data_ptr(),
+              None if k_norm_weight is None else k_norm_weight.data_ptr(),
+              cos.data_ptr(), sin.data_ptr(), float(eps), k_cache.data_ptr(), v_cache.data_ptr(),
+              block_tables.data_ptr(), positions.data_ptr(), *plan[1:], _ws_ptr(dev_index, handle, 256).data_ptr(), handle)
+        return q_out
+    given = (cos, sin, block_tables, positions)
     _require(q.is_cuda and k.is_cuda and v.is_cuda, "q, k and v must be on CUDA")
     _require(q.dim() == 3 and k.dim() == 3 and v.dim() == 3, "q must be [T, Hq, D] and k, v [T, Hkv, D]")
     T, hq, d = q.shape
@@ -197,8 +276,6 @@ def paged_qk_norm_rope_store(q, k, v, cos, sin, k_cache, v_cache, block_tables, 
         cos, sin = cos[0], sin[0]
     _require(cos.shape == sin.shape and cos.dim() == 2 and cos.size(1) == d and cos.size(0) in (1, T),
              "cos and sin must be [T, D]")
-    if q_out is None:
-        q_out = q
     _require(q_out.shape == q.shape, "q_out must have q's shape")
     for name, t_ in (("q", q), ("k", k), ("v", v), ("q_out", q_out)):
         _require(t_.stride(2) == 1 and t_.stride(1) == d, f"{name}: the last two dims must be contiguous")
@@ -225,19 +302,16 @@ def paged_qk_norm_rope_store(q, k, v, cos, sin, k_cache, v_cache, block_tables, 
         positions = positions.contiguous()
     if T == 0:
         return q_out
-    handle = _stream_handle(dev)
-    ws = _workspace(dev, handle, 256)
-    with torch.cuda.device(dev):
-        _lib.check(_C.npd_qk_norm_rope_store(
-            q_out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-            None if q_norm_weight is None else q_norm_weight.data_ptr(),
-            None if k_norm_weight is None else k_norm_weight.data_ptr(),
-            cos.data_ptr(), sin.data_ptr(), float(eps),
-            k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(), positions.data_ptr(),
-            T, hq, hkv, d, bs, nb, block_tables.size(1), cstride,
-            q.stride(0), k.stride(0), v.stride(0), q_out.stride(0),
-            0 if cos.size(0) == 1 else cos.stride(0), block_tables.stride(0),
-            _DTYPE_CODE[q.dtype], ws.data_ptr(), handle))
+    plan = (dev.index, T, hq, hkv, d, bs, nb, block_tables.size(1), cstride, q.stride(0), k.stride(0), v.stride(0),
+            q_out.stride(0), 0 if cos.size(0) == 1 else cos.stride(0), block_tables.stride(0), _DTYPE_CODE[q.dtype])
+    if key is not None and all(a is b for a, b in zip(given, (cos, sin, block_tables, positions))):
+        _remember(_rope_plans, key, plan)
+    handle = _raw_stream(dev.index)
+    _call(dev.index, _C.npd_qk_norm_rope_store, q_out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+          None if q_norm_weight is None else q_norm_weight.data_ptr(),
+          None if k_norm_weight is None else k_norm_weight.data_ptr(),
+          cos.data_ptr(), sin.data_ptr(), float(eps), k_cache.data_ptr(), v_cache.data_ptr(),
+          block_tables.data_ptr(), positions.data_ptr(), *plan[1:], _ws_ptr(dev.index, handle, 256).data_ptr(), handle)
     return q_out
 
 
@@ -265,6 +339,20 @@ def paged_attention_forward(out, query, key_cache, value_cache, block_tables, se
     ``max_ctas`` (an addition, 0 = one CTA per SM) caps the persistent grid so that the call can share the GPU
     with another kernel on a second stream (see ``paged_forward.paged_attention_step``).
     """
+    try:
+        key = (_sig(out, query, key_cache, value_cache, block_tables, seq_lens), block_size, max_num_blocks_per_seq,
+               _flags, max_ctas)
+    except AttributeError:
+        key = None
+    plan = _attn_plans.get(key) if key is not None else None
+    if plan is not None:
+        dev_index, need, flags = plan[0], plan[1], plan[2]
+        handle = _raw_stream(dev_index)
+        ws = _ws_ptr(dev_index, handle, need)
+        _call(dev_index, _C.npd_paged_decode_attention, out.data_ptr(), query.data_ptr(), key_cache.data_ptr(),
+              value_cache.data_ptr(), block_tables.data_ptr(), seq_lens.data_ptr(), float(scale), *plan[3:],
+              ws.data_ptr(), ws.numel(), flags, handle)
+        return
     _require(query.is_cuda, "query is must be on CUDA")
     _require(query.dim() == 3, "query must be [num seqs, num_heads, head_size]")
     _require(key_cache.dim() in (4, 5), "key_cache must be [num_blocks, num_kv_heads, block_size, head_size] "
@@ -310,16 +398,16 @@ def paged_attention_forward(out, query, key_cache, value_cache, block_tables, se
         _require(block_tables.numel() >= S * max_blk, "block_tables smaller than num_seqs * max_num_blocks_per_seq")
     if S == 0:
         return
-    handle = _stream_handle(dev)
-    with torch.cuda.device(dev):
-        need = _C.npd_decode_workspace_bytes(S, hq, hkv, d, dev.index)
-        ws = _workspace(dev, handle, need)
-        _lib.check(_C.npd_paged_decode_attention(
-            out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
-            block_tables.data_ptr(), seq_lens.data_ptr(), float(scale),
-            S, hq, hkv, d, bs, max_blk, nb, cstride, row_stride,
-            _DTYPE_CODE[query.dtype], ws.data_ptr(), ws.numel(),
-            int(_flags) | ((int(max_ctas) & 0xffff) << 8), handle))
+    need = _C.npd_decode_workspace_bytes(S, hq, hkv, d, dev.index)
+    flags = int(_flags) | ((int(max_ctas) & 0xffff) << 8)
+    plan = (dev.index, need, flags, S, hq, hkv, d, bs, max_blk, nb, cstride, row_stride, _DTYPE_CODE[query.dtype])
+    if key is not None:
+        _remember(_attn_plans, key, plan)
+    handle = _raw_stream(dev.index)
+    ws = _ws_ptr(dev.index, handle, need)
+    _call(dev.index, _C.npd_paged_decode_attention, out.data_ptr(), query.data_ptr(), key_cache.data_ptr(),
+          value_cache.data_ptr(), block_tables.data_ptr(), seq_lens.data_ptr(), float(scale), *plan[3:],
+          ws.data_ptr(), ws.numel(), flags, handle)
 
 
 # ---------------------------------------------------------------------------
