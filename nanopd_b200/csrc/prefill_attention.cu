@@ -15,12 +15,17 @@
 //                    draws the next work item and publishes it to the other roles
 //   warps 9 / 10     issue the tcgen05.mma instructions of tile A / B (one elected lane)
 //   warp  11         idle (completes the third warpgroup for setmaxnreg)
-// TMEM (512 columns): S_A | S_B | O_A | O_B, 128 columns each.  Per key tile and query tile:
-//   S = Q.K^T        tcgen05.mma, both operands in shared memory, fp32 scores in TMEM
-//   P = exp2(S*scale - m), rounded to the input type and written back to TMEM over the first 64 score
-//       columns (masking only on tiles that touch the diagonal)
-//   O += P.V         tcgen05.mma with P as the TMEM A operand and V as the MN-major B operand; O stays in
-//       TMEM and is rescaled only when a row maximum grows by more than 2^8, then read once in the epilogue.
+// TMEM (512 columns): S_A | S_B | O_A | O_B, 128 columns each.  A query tile walks its keys in HALF-STEPS of 64
+// keys; its 128 score columns are a ring of two 64-column buffers, so the scores of half-step c+1 are
+// already in TMEM while the softmax group works on half-step c, and those of c+2 are computed while the
+// PV product of c+1 waits for its probabilities:
+//   S(c) = Q.K(c)^T      tcgen05.mma M128 N64, both operands in shared memory, fp32 scores in buffer c&1
+//   P(c) = exp2(S*scale - m), rounded to the input type and written back over the first 32 columns of
+//          the buffer (masking only on half-steps that touch the diagonal)
+//   O   += P(c).V(c)      tcgen05.mma with P as the TMEM A operand and V as the MN-major B operand; then
+//          S(c+2) is issued into the buffer P(c) has just left (MMAs execute in issue order)
+// O stays in TMEM and is rescaled only when a row maximum grows by more than 2^8 (after waiting for the
+// PV products issued so far), then read once in the epilogue.
 // Completion of MMAs is tracked with tcgen05.commit on mbarriers; every wait is bounded and an
 // abort flag lets all roles leave together, after which TMEM is released.
 //
@@ -38,7 +43,8 @@ constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays
 constexpr int kMaxPairs = 2048;    // query-tile pairs per launch (kernel-parameter array, heaviest first)
 constexpr int kSchedSlots = 4;     // work items the producer may publish ahead of the slowest consumer
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
-constexpr int kKeys = 128;         // keys per tile (UMMA N of the score MMA, K extent of the PV MMA)
+constexpr int kKeys = 128;         // keys per K/V tile in shared memory
+constexpr int kHalfKeys = 64;      // keys per half-step (UMMA N of a score MMA, K extent of a PV MMA batch)
 constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA for A, 10 MMA for B, 11 idle
 constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
 constexpr int kKvHalfBytes = kKeys * 128;           // one 64-element half of a 128-key K or V tile
@@ -49,19 +55,8 @@ template <int kD> struct TileBytes {
     static constexpr int kv = kHalves * kKvHalfBytes;   // 32 KiB at head_dim 128
 };
 constexpr int kStages = 2;                          // K ring and V ring depth
-constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; the packed probabilities of a key
-                                   // tile overwrite the first 64 columns of its scores
-#ifndef NPD_STAGGER
-#define NPD_STAGGER 1
-#endif
-// Tile B starts an item half a step behind tile A: the two softmax groups then alternate on the special-function
-// units and the two MMA streams alternate on the tensor pipe instead of running in lock-step.
-constexpr bool kStagger = NPD_STAGGER != 0;
-constexpr long long kStaggerWaitCycles = 4000;
-#ifndef NPD_POLY_PAIRS_OF_8
-#define NPD_POLY_PAIRS_OF_8 0
-#endif
-constexpr int kPolyPairsOf8 = NPD_POLY_PAIRS_OF_8;           // of every 8 score pairs, this many take the polynomial exp2
+constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; a tile's score columns are two buffers of
+                                   // 64; the packed probabilities of a half-step overwrite the first 32 of its buffer
 constexpr float kRescaleThreshold = 8.f;   // log2 units: O is rescaled only when a row max grows by more
 constexpr long long kWaitCycles = 4000000000LL;
 
@@ -164,6 +159,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+// One 256-bit store (sm_100: st.global.v8.b32); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_32B(void *ptr, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Packed fp32x2 arithmetic (__ffma2_rn / __fadd2_rn: two lanes per instruction on sm_100) halves the
@@ -239,21 +240,24 @@ struct alignas(8) SmemCtrl {
     uint64_t q_empty[2];         // [query tile]: its MMA warp has issued the last score MMA of the item
     uint64_t k_full[kStages], v_full[kStages];     // the K / V tile of a ring stage has landed
     uint64_t k_empty[kStages], v_empty[kStages];   // both MMA warps are done with it (2 arrivals)
-    uint64_t s_full[2];     // [query tile]: the score tile of the next key tile is in TMEM (and every earlier PV done)
-    uint64_t p_half[2];     // [query tile]: the probabilities of the first 64 keys are in TMEM (128 arrivals)
-    uint64_t p_full[2];     // [query tile]: all probabilities are in TMEM (128 arrivals)
-    uint64_t o_full[2];     // [query tile]: the last PV MMA of the work item has completed
+    uint64_t s_full[2][2];  // [query tile][buffer]: the scores of a half-step are in that buffer (and the PV product
+                            // that last read the buffer has completed)
+    uint64_t p_ready[2][2]; // [query tile][buffer]: the probabilities of the half-step are in TMEM (128 arrivals)
+    uint64_t pv_done[2][2]; // [query tile][buffer]: one completion per PV product that read that buffer, in order.  Two
+                            // barriers, because a waiter may find either one or two products still in flight and a
+                            // parity wait cannot tell "two behind" from "done"
     uint64_t o_free[2];     // [query tile]: the epilogue has taken O out of TMEM (128 arrivals)
     uint32_t tmem_base;
     int abort_flag;
-    int sm_progress[2];     // [query tile]: key-tile steps whose first half of P has been released (running count)
 };
 
 // One work item = a pair of 128-row query tiles of one chunk and one kv head.
 struct Item {
     int c, h;
     int start, qoff, ctx_end;
-    int tok0[2], tq_valid[2], ntiles[2];
+    int tok0[2], tq_valid[2];
+    int nhalf[2];           // half-steps of 64 keys each query tile takes (keys [0, start + tok0 + tq_valid))
+    int ntiles[2];          // K/V tiles of 128 keys they lie in
     int n_kv;
 };
 
@@ -273,7 +277,8 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, int item) {
         it.tok0[x] = (2 * pair + x) * p.tq;
         it.tq_valid[x] = max(0, min(p.tq, n_tok - it.tok0[x]));
         // keys [0, start + tok0 + tq_valid) are visible to the tile
-        it.ntiles[x] = it.tq_valid[x] > 0 ? (it.start + it.tok0[x] + it.tq_valid[x] + kKeys - 1) / kKeys : 0;
+        it.nhalf[x] = it.tq_valid[x] > 0 ? (it.start + it.tok0[x] + it.tq_valid[x] + kHalfKeys - 1) / kHalfKeys : 0;
+        it.ntiles[x] = (it.nhalf[x] + 1) / 2;
     }
     it.n_kv = max(it.ntiles[0], it.ntiles[1]);
     return it;
@@ -319,14 +324,15 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         for (int x = 0; x < 2; ++x) {
             mbar_init(smem_u32(&ctrl->q_full[x]), 1);
             mbar_init(smem_u32(&ctrl->q_empty[x]), 1);
-            mbar_init(smem_u32(&ctrl->s_full[x]), 1);
-            mbar_init(smem_u32(&ctrl->p_half[x]), 128);
-            mbar_init(smem_u32(&ctrl->p_full[x]), 128);
-            mbar_init(smem_u32(&ctrl->o_full[x]), 1);
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(smem_u32(&ctrl->s_full[x][b]), 1);
+                mbar_init(smem_u32(&ctrl->p_ready[x][b]), 128);
+            }
+            mbar_init(smem_u32(&ctrl->pv_done[x][0]), 1);
+            mbar_init(smem_u32(&ctrl->pv_done[x][1]), 1);
             mbar_init(smem_u32(&ctrl->o_free[x]), 128);
         }
         ctrl->abort_flag = 0;
-        ctrl->sm_progress[0] = ctrl->sm_progress[1] = 0;
         mbar_fence_init();
     }
     if (warp == 9) {
@@ -450,7 +456,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         {
             const int x = warp - 9;
             constexpr uint32_t fmt = Elem<T>::kDtype == NPD_DTYPE_BF16 ? 1u : 0u;
-            constexpr uint32_t idesc_s = instr_desc(fmt, 0u, kRows, kKeys);
+            constexpr uint32_t idesc_s = instr_desc(fmt, 0u, kRows, kHalfKeys);
             constexpr uint32_t idesc_pv = instr_desc(fmt, 1u, kRows, kD);
             auto wait_all = [&](uint64_t *bar, uint32_t parity) {
                 const bool good = wait_or_abort(smem_u32(bar), parity, abort_flag, p.status);
@@ -460,94 +466,93 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (elect_one()) tc_commit(smem_u32(bar));
                 __syncwarp();
             };
-            // Descriptors are built once; a k-step or a ring stage only adds a constant to the
+            // Descriptors are built once; a k-step, a half or a ring stage only adds a constant to the
             // start-address field (16-byte units).
             const uint64_t q_desc = desc_k_major(smem_u32(q_tiles) + x * kQTileBytes);
             const uint64_t k_desc0 = desc_k_major(smem_u32(k_ring));
             const uint64_t v_desc0 = desc_mn_major(smem_u32(v_ring), kKvHalfBytes);
             const uint32_t t_sx = tmem + x * 128, t_o = tmem + 256 + x * 128;
-            // S_X = Q_X . K^T of ring stage `stage`: 8 k-steps of 16 elements (32 B inside the swizzle atom;
-            // the second 64-element half starts one half-tile further on)
-            auto issue_s = [&](int stage) {
-                const uint64_t kd = k_desc0 + static_cast<uint64_t>((stage * kKvTileBytes) >> 4);
+            // S = Q_X . K^T for the 64 keys of half `h` of ring stage `stage`, into score buffer `buf`, then the commit
+            // that tells the softmax group (it also covers every MMA issued before): kD/16 k-steps of 16 elements
+            // (32 B inside the swizzle atom; the second 64-element half of the head dim starts one half-tile further
+            // on); the keys of half h are rows 64h.. of the K tile, 64 rows x 128 B further on.
+            auto issue_s = [&](int stage, int h, int buf) {
+                const uint64_t kd = k_desc0 + static_cast<uint64_t>((stage * kKvTileBytes + h * kHalfKeys * 128) >> 4);
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kD / 16; ++ks) {
                         const uint64_t a_off = static_cast<uint64_t>(((ks >> 2) * kQHalfBytes + (ks & 3) * 32) >> 4);
                         const uint64_t b_off = static_cast<uint64_t>(((ks >> 2) * kKvHalfBytes + (ks & 3) * 32) >> 4);
-                        tc_mma_ss(t_sx, q_desc + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
+                        tc_mma_ss(t_sx + buf * kHalfKeys, q_desc + a_off, kd + b_off, idesc_s, ks > 0 ? 1u : 0u);
                     }
-                    tc_commit(smem_u32(&ctrl->s_full[x]));
+                    tc_commit(smem_u32(&ctrl->s_full[x][buf]));
                 }
                 __syncwarp();
             };
-            // O_X (+)= P_X . V of ring stage `stage`: P from TMEM (packed pairs over the first 64 score columns,
-            // 8 columns per 16 keys), V MN-major from shared memory (16 keys = two 8-row groups = 2 KiB further on)
-            // (issued in two halves of 64 keys: the first starts while the softmax group still works on the second)
-            auto issue_pv = [&](int stage, int half, bool first, bool last) {
-                const uint64_t vd = v_desc0 + static_cast<uint64_t>((stage * kKvTileBytes) >> 4);
+            // O_X (+)= P . V for the 64 keys of half `h` of ring stage `stage`: P from TMEM (packed pairs over the
+            // first 32 columns of score buffer `buf`, 8 columns per 16 keys), V MN-major from shared memory (16 keys
+            // = two 8-row groups = 2 KiB further on), then the commit that counts this product as done.
+            auto issue_pv = [&](int stage, int h, int buf, bool first) {
+                const uint64_t vd = v_desc0 + static_cast<uint64_t>((stage * kKvTileBytes + h * (kHalfKeys / 16) * 2048) >> 4);
                 if (elect_one()) {
 #pragma unroll
-                    for (int ks = half * (kKeys / 32); ks < (half + 1) * (kKeys / 32); ++ks)
-                        tc_mma_ts(t_o, t_sx + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
-                                  (!first || ks > 0) ? 1u : 0u);
-                    if (last && half == 1) tc_commit(smem_u32(&ctrl->o_full[x]));
+                    for (int ks = 0; ks < kHalfKeys / 16; ++ks)
+                        tc_mma_ts(t_o, t_sx + buf * kHalfKeys + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4),
+                                  idesc_pv, (!first || ks > 0) ? 1u : 0u);
+                    tc_commit(smem_u32(&ctrl->pv_done[x][buf]));
                 }
                 __syncwarp();
             };
 
             int g = 0;         // key tiles seen so far (ring position of the item's first key tile)
-            int cnt = 0;       // own key tiles processed so far (phases of s_full and p_full)
-            int cnt_other = 0; // the other query tile's count at the start of the current item
-            int items_done = 0;   // items in which this query tile had work (phases of o_full and o_free)
+            int c = 0;         // own half-steps so far: buffer c & 1, phase c >> 1 of that buffer's barriers
+            int items_done = 0;   // items in which this query tile had work (phases of q_full and o_free)
             NPD_TRACE_DECL
             bool ok = true;
             for (int k = 0; ok; ++k) {
                 const int item = next_item(k, ok);
                 if (!__all_sync(0xffffffffu, ok) || item < 0) break;
                 const Item it = decode_item(p, item);
-                const int my_tiles = it.ntiles[x];
-                if (my_tiles > 0) {
+                const int U = it.nhalf[x], my_tiles = it.ntiles[x];
+                if (U > 0) {
+                    // the first two half-steps' scores: both buffers are free (the previous item's last PV
+                    // products, which read P from them, were issued before these MMAs)
                     if (!(ok = wait_all(&ctrl->q_full[x], items_done & 1))) break;
-                    if (kStagger && x == 1 && it.ntiles[0] > 0) {
-                        // advisory and bounded: go on once tile A has released half of its first step of this item
-                        const long long t_start = clock64();
-                        while (*reinterpret_cast<volatile int *>(&ctrl->sm_progress[0]) <= cnt_other &&
-                               clock64() - t_start < kStaggerWaitCycles) { }
-                    }
-                    // (the score columns are free: the previous item's last PV, which read P from them, was
-                    // issued before this MMA and MMAs execute in issue order)
                     if (!(ok = wait_all(&ctrl->k_full[g % kStages], (g / kStages) & 1))) break;
                     tc_fence_after();
-                    issue_s(g % kStages);
+                    issue_s(g % kStages, 0, c & 1);
+                    if (U > 1) issue_s(g % kStages, 1, (c + 1) & 1);
                     commit(&ctrl->k_empty[g % kStages]);
+                    if (U <= 2) commit(&ctrl->q_empty[x]);       // no further score MMA of this item reads Q_X
                 }
-                if (my_tiles == 1) commit(&ctrl->q_empty[x]);   // no further score MMA of this item reads Q_X
                 for (int t = 0; ok && t < it.n_kv; ++t) {
                     const int gt = g + t, stage = gt % kStages;
                     if (t < my_tiles) {
-                        const int ct = cnt + t;
-                        // O_X is overwritten by the first PV of an item: the previous epilogue must have read it
-                        if (t == 0 && items_done > 0 && !(ok = wait_all(&ctrl->o_free[x], (items_done - 1) & 1))) break;
-                        if (!(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
-                        NPD_TRACE(x == 0 ? 1 : 4, 10, t);
-                        if (!(ok = wait_all(&ctrl->p_half[x], ct & 1))) break;
-                        tc_fence_after();
-                        issue_pv(stage, 0, t == 0, t + 1 == my_tiles);
-                        if (t + 1 < my_tiles &&
-                            !(ok = wait_all(&ctrl->k_full[(gt + 1) % kStages], ((gt + 1) / kStages) & 1))) break;
-                        if (!(ok = wait_all(&ctrl->p_full[x], ct & 1))) break;
-                        NPD_TRACE(x == 0 ? 1 : 4, 11, t);
-                        tc_fence_after();
-                        issue_pv(stage, 1, t == 0, t + 1 == my_tiles);
-                        commit(&ctrl->v_empty[stage]);
-                        if (t + 1 < my_tiles) {
-                            // S(t+1) overwrites the columns P(t) sits in; it executes after the PV MMAs above
-                            NPD_TRACE(x == 0 ? 1 : 4, 12, t);
-                            issue_s((gt + 1) % kStages);
-                            NPD_TRACE(x == 0 ? 1 : 4, 13, t);
-                            commit(&ctrl->k_empty[(gt + 1) % kStages]);
-                            if (t + 2 == my_tiles) commit(&ctrl->q_empty[x]);   // that was the last one
+                        for (int h = 0; ok && h < 2; ++h) {
+                            const int u = 2 * t + h;
+                            if (u >= U) break;
+                            const int cu = c + u, buf = cu & 1;
+                            // O_X is overwritten by the first PV of an item: the previous epilogue must have read it
+                            if (u == 0 && items_done > 0 && !(ok = wait_all(&ctrl->o_free[x], (items_done - 1) & 1))) break;
+                            if (h == 0 && !(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
+                            NPD_TRACE(x == 0 ? 1 : 4, 10, u);
+                            if (!(ok = wait_all(&ctrl->p_ready[x][buf], (cu >> 1) & 1))) break;
+                            NPD_TRACE(x == 0 ? 1 : 4, 11, u);
+                            tc_fence_after();
+                            issue_pv(stage, h, buf, u == 0);
+                            NPD_TRACE(x == 0 ? 1 : 4, 14, u);
+                            if (h == 1 || u == U - 1) commit(&ctrl->v_empty[stage]);
+                            const int u2 = u + 2;
+                            if (u2 < U) {
+                                // S(u+2) goes into the buffer P(u) sits in; it executes after the PV MMAs above
+                                const int gt2 = gt + 1, stage2 = gt2 % kStages;
+                                if (h == 0 && !(ok = wait_all(&ctrl->k_full[stage2], (gt2 / kStages) & 1))) break;
+                                NPD_TRACE(x == 0 ? 1 : 4, 12, u);
+                                issue_s(stage2, h, buf);
+                                NPD_TRACE(x == 0 ? 1 : 4, 13, u);
+                                if (h == 1 || u2 == U - 1) commit(&ctrl->k_empty[stage2]);
+                                if (u2 == U - 1) commit(&ctrl->q_empty[x]);     // that was the item's last score MMA
+                            }
                         }
                     } else {
                         // a key tile only the other query tile needs: observe it so that ring phases stay in step
@@ -558,9 +563,8 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     }
                 }
                 g += it.n_kv;
-                cnt += my_tiles;
-                cnt_other += it.ntiles[x ^ 1];
-                items_done += my_tiles > 0 ? 1 : 0;
+                c += U;
+                items_done += U > 0 ? 1 : 0;
             }
         }
     } else if (warp >= 11) {
@@ -572,10 +576,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         const int wq = warp & 3;                                 // TMEM lane quarter this warp may touch
         const int row = wq * 32 + lane;                          // == TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-        const uint32_t t_sx = tmem + x * 128 + lane_base;        // scores (128 columns); P overwrites the first 64
+        const uint32_t t_sx = tmem + x * 128 + lane_base;        // two score buffers of 64 columns
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
-        int g = 0, cnt = 0, items_seen = 0;                   // items_seen: items in which this tile had work
+        int g = 0, c = 0;                                     // key tiles / own half-steps so far (barrier phases)
         const int sm_role = wq == 0 ? 2 + x : 5 + x * 3 + (wq - 1);   // trace slot (used only by tracing builds)
         (void)sm_role;
         NPD_TRACE_DECL
@@ -585,20 +589,21 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             const int item = next_item(k, ok);
             if (!ok || item < 0) break;
             const Item it = decode_item(p, item);
-            const int my_tiles = it.ntiles[x];
+            const int U = it.nhalf[x];
             const int pos = it.start + it.tok0[x] + tq_idx;      // last visible key of this row
             float m_run = -INFINITY, l_run = 0.f;
 #pragma unroll 1
-            for (int t = 0; ok && t < my_tiles; ++t) {
-                const int ct = cnt + t;
-                const int gt = g + t, stage = gt % kStages;
-                const int key0 = t * kKeys;
+            for (int u = 0; ok && u < U; ++u) {
+                const int cu = c + u, buf = cu & 1;
+                const int t = u >> 1, gt = g + t, stage = gt % kStages;
+                const int key0 = u * kHalfKeys;
                 // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
-                // there cannot meet a NaN.  Both softmax groups do it (idempotent) before releasing their P.
-                if (key0 + kKeys > it.ctx_end) {
+                // there cannot meet a NaN.  Both softmax groups do it (idempotent), at the first half-step of the
+                // key tile, before they release its probabilities.
+                if ((u & 1) == 0 && t * kKeys + kKeys > it.ctx_end) {
                     if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (gt / kStages) & 1, abort_flag, p.status))) break;
                     uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
-                    const int first = max(it.ctx_end - key0, 0);
+                    const int first = max(it.ctx_end - t * kKeys, 0);
                     constexpr int kPieces = kHalves * 8;           // 16-byte pieces per row
                     const int n16 = (kKeys - first) * kPieces;
                     for (int idx = threadIdx.x & 127; idx < n16; idx += 128) {
@@ -608,46 +613,46 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     }
                     fence_proxy_async_smem();
                 }
-                // s_full(t) also tells that every earlier PV MMA of this query tile has completed (commits
-                // cover all MMAs issued before them), so O may be rescaled below without a further wait.
-                if (lane == 0) NPD_TRACE_FINE(sm_role, 20, t);
-                if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x]), ct & 1, abort_flag, p.status))) break;
-                if (lane == 0) NPD_TRACE(sm_role, 21, t);
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 20, u);
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->s_full[x][buf]), (cu >> 1) & 1, abort_flag, p.status))) break;
+                if (lane == 0) NPD_TRACE(sm_role, 21, u);
                 tc_fence_after();
-                // The whole score row of this key tile (128 fp32) moves to registers: one TMEM read.
-                float sc[4][32];
+                // The 64 scores of this half-step move to registers: one TMEM read.
+                float sc[2][32];
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) tmem_ld32(t_sx + cc * 32, sc[cc]);
+                for (int cc = 0; cc < 2; ++cc) tmem_ld32(t_sx + buf * kHalfKeys + cc * 32, sc[cc]);
                 tmem_wait_ld();
-                if (lane == 0) NPD_TRACE_FINE(sm_role, 22, t);
-                if (key0 + kKeys - 1 > it.start + it.tok0[x]) {  // only tiles that reach past the first row's diagonal
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 22, u);
+                if (key0 + kHalfKeys - 1 > it.start + it.tok0[x]) {  // only half-steps that reach past the first row's diagonal
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc)
+                    for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
                             if (key0 + cc * 32 + i > pos) sc[cc][i] = -INFINITY;
                 }
-                if (lane == 0) NPD_TRACE_FINE(sm_role, 40, t);
-                // ---- row maximum: eight independent chains of three-input max ----
-                float mxa[8];
+                // ---- row maximum: four independent chains of three-input max ----
+                float mxa[4];
 #pragma unroll
-                for (int q8 = 0; q8 < 8; ++q8) mxa[q8] = fmaxf(sc[q8 >> 1][(q8 & 1) * 16], sc[q8 >> 1][(q8 & 1) * 16 + 1]);
+                for (int q4 = 0; q4 < 4; ++q4) mxa[q4] = fmaxf(sc[q4 >> 1][(q4 & 1) * 16], sc[q4 >> 1][(q4 & 1) * 16 + 1]);
 #pragma unroll
                 for (int i = 2; i < 16; i += 2)
 #pragma unroll
-                    for (int q8 = 0; q8 < 8; ++q8)
-                        mxa[q8] = fmax3(mxa[q8], sc[q8 >> 1][(q8 & 1) * 16 + i], sc[q8 >> 1][(q8 & 1) * 16 + i + 1]);
-                const float m_new = fmaxf(fmax3(fmaxf(mxa[0], mxa[1]), mxa[2], mxa[3]),
-                                          fmax3(fmaxf(mxa[4], mxa[5]), mxa[6], mxa[7])) * p.scale_log2;
-                if (lane == 0) NPD_TRACE_FINE(sm_role, 41, t);
-                if (t == 0) {
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        mxa[q4] = fmax3(mxa[q4], sc[q4 >> 1][(q4 & 1) * 16 + i], sc[q4 >> 1][(q4 & 1) * 16 + i + 1]);
+                const float m_new = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])) * p.scale_log2;
+                if (u == 0) {
                     m_run = m_new;                              // key 0 is visible to every row: finite
                 } else {
                     // Lazy correction: O (in TMEM) and l are rescaled only when some row's maximum grew by more
                     // than 2^8; otherwise the stale maximum keeps every probability below 256, exactly cancelled
-                    // by the final division.
+                    // by the final division.  O may be touched once every PV product issued so far has completed:
+                    // PV(u-1) is the last one (PV(u) waits for the probabilities of this half-step); the one before
+                    // it on the same barrier, PV(u-3), is known to be complete (s_full of this buffer covers PV(u-2)).
                     const bool grow = m_new > m_run + kRescaleThreshold;
                     if (__any_sync(0xffffffffu, grow)) {
+                        if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][(cu - 1) & 1]), ((cu - 1) >> 1) & 1, abort_flag,
+                                                 p.status))) break;
+                        tc_fence_after();
                         const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
 #pragma unroll 1
                         for (int cc = 0; cc < kD / 32; ++cc) {
@@ -665,111 +670,73 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                         }
                     }
                 }
-                if (lane == 0) NPD_TRACE_FINE(sm_role, 23, t);
-                // ---- probabilities in place (masked scores are -inf -> 0), packed in pairs over the score
-                //      columns already read ----
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 23, u);
+                // ---- probabilities (masked scores are -inf -> 0), packed in pairs over the first 32 columns of the
+                //      buffer just read ----
                 const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
                 const float2 negm2 = make_float2(-m_run, -m_run);
                 float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
+                for (int cc = 0; cc < 2; ++cc) {
                     uint32_t packed[16];
-                    // The chunk's 16 pairs: the first kPolyPairsOf8 * 2 even-numbered ones take the polynomial on the
-                    // FMA pipes, stage by stage so that their dependent chains interleave; the others the SFU.
-                    constexpr int NP = kPolyPairsOf8 * 2;
-                    float2 xs[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        xs[i] = __ffma2_rn(make_float2(sc[cc][2 * i], sc[cc][2 * i + 1]), scale2, negm2);
-                    float2 pt[NP > 0 ? NP : 1], pf[NP > 0 ? NP : 1], pq[NP > 0 ? NP : 1];
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) {
-                        pf[j].x = fmaxf(xs[2 * j].x, -125.f);
-                        pf[j].y = fmaxf(xs[2 * j].y, -125.f);
-                    }
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) pt[j] = __fadd2_rn(pf[j], make_float2(12582912.f, 12582912.f));
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) pq[j] = __fadd2_rn(pt[j], make_float2(-12582912.f, -12582912.f));
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) pf[j] = __ffma2_rn(pq[j], make_float2(-1.f, -1.f), pf[j]);
-#pragma unroll
-                    for (int j = 0; j < NP; ++j)
-                        pq[j] = __ffma2_rn(make_float2(0.05583828f, 0.05583828f), pf[j], make_float2(0.24263948f, 0.24263948f));
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) pq[j] = __ffma2_rn(pq[j], pf[j], make_float2(0.69313675f, 0.69313675f));
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) pq[j] = __ffma2_rn(pq[j], pf[j], make_float2(0.99992454f, 0.99992454f));
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        float2 pr;
-                        if ((i & 1) == 0 && (i >> 1) < NP) {
-                            const int j = i >> 1;
-                            pr = make_float2(__uint_as_float(__float_as_uint(pq[j].x) + (__float_as_uint(pt[j].x) << 23)),
-                                             __uint_as_float(__float_as_uint(pq[j].y) + (__float_as_uint(pt[j].y) << 23)));
-                        } else {
-                            pr = make_float2(fast_exp2(xs[i].x), fast_exp2(xs[i].y));
-                        }
+                        const float2 xs = __ffma2_rn(make_float2(sc[cc][2 * i], sc[cc][2 * i + 1]), scale2, negm2);
+                        const float2 pr = make_float2(fast_exp2(xs.x), fast_exp2(xs.y));
                         acc2[i & 1] = __fadd2_rn(acc2[i & 1], pr);
                         packed[i] = Elem<T>::pack2(pr.x, pr.y);
                     }
-                    tmem_st16(t_sx + cc * 16, packed);
-                    if (cc == 1) {               // first 64 keys done: their PV MMAs may start
-                        tmem_wait_st();
-                        tc_fence_before();
-                        mbar_arrive(smem_u32(&ctrl->p_half[x]));
-                        if (kStagger && row == 0) *reinterpret_cast<volatile int *>(&ctrl->sm_progress[x]) = ct + 1;
-                    }
-                    if (lane == 0) NPD_TRACE_FINE(sm_role, 50 + cc, t);
+                    tmem_st16(t_sx + buf * kHalfKeys + cc * 16, packed);
                 }
-                l_run += (acc2[0].x + acc2[1].x) + (acc2[0].y + acc2[1].y);
-                if (lane == 0) NPD_TRACE_FINE(sm_role, 24, t);
+                const float psum = (acc2[0].x + acc2[1].x) + (acc2[0].y + acc2[1].y);
+                l_run += psum;
+                if (lane == 0) NPD_TRACE_FINE(sm_role, 24, u);
                 tmem_wait_st();
                 tc_fence_before();           // P is in TMEM, S has been read: the MMA warp may go on
-                mbar_arrive(smem_u32(&ctrl->p_full[x]));
-                if (lane == 0) NPD_TRACE(sm_role, 25, t);
+                mbar_arrive(smem_u32(&ctrl->p_ready[x][buf]));
+                if (lane == 0) NPD_TRACE(sm_role, 25, u);
             }
 
             // ---- epilogue: O / l -> out ----
-            if (ok && my_tiles > 0) {
-                // o_full completes once per work item, after its last PV MMA
+            if (ok && U > 0) {
+                // the item's last PV product (products complete in order, so all of them)
                 if (lane == 0) NPD_TRACE(sm_role, 30, k);
-                ok = wait_or_abort(smem_u32(&ctrl->o_full[x]), items_seen & 1, abort_flag, p.status);
+                const int last = c + U - 1;
+                ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][last & 1]), (last >> 1) & 1, abort_flag, p.status);
                 if (lane == 0) NPD_TRACE(sm_role, 31, k);
-                ++items_seen;
                 if (ok) {
                     tc_fence_after();
                     const bool store = tq_idx < it.tq_valid[x] && row < p.tq * p.group;
                     const float inv = 1.f / l_run;
                     T *dst = static_cast<T *>(p.out) +
                              ((long long)(it.qoff + it.tok0[x] + tq_idx) * p.num_q_heads + (long long)it.h * p.group + hg) * kD;
+                    // the whole accumulator row in one go: kD/32 loads in flight, one wait
+                    float o[kD / 32][32];
 #pragma unroll
-                    for (int cc = 0; cc < kD / 32; ++cc) {
-                        float o[32];
-                        tmem_ld32(t_o + cc * 32, o);
-                        tmem_wait_ld();
-                        if (cc == kD / 32 - 1) {
-                            // O is in registers: the next item's first PV may overwrite the accumulator
-                            tc_fence_before();
-                            mbar_arrive(smem_u32(&ctrl->o_free[x]));
-                        }
-                        if (store) {
+                    for (int cc = 0; cc < kD / 32; ++cc) tmem_ld32(t_o + cc * 32, o[cc]);
+                    tmem_wait_ld();
+                    // O is in registers: the next item's first PV may overwrite the accumulator
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&ctrl->o_free[x]));
+                    if (store) {
+                        // 32 bytes per lane and instruction: a lane's row is contiguous, the lanes of a warp are 256
+                        // bytes apart, so every store instruction fills whole 32-byte sectors
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 w;
-                                w.x = Elem<T>::pack2(o[i] * inv, o[i + 1] * inv);
-                                w.y = Elem<T>::pack2(o[i + 2] * inv, o[i + 3] * inv);
-                                w.z = Elem<T>::pack2(o[i + 4] * inv, o[i + 5] * inv);
-                                w.w = Elem<T>::pack2(o[i + 6] * inv, o[i + 7] * inv);
-                                *reinterpret_cast<uint4 *>(dst + cc * 32 + i) = w;
+                        for (int cc = 0; cc < kD / 32; ++cc)
+#pragma unroll
+                            for (int i = 0; i < 32; i += 16) {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    w[j] = Elem<T>::pack2(o[cc][i + 2 * j] * inv, o[cc][i + 2 * j + 1] * inv);
+                                st_global_32B(dst + cc * 32 + i, w);
                             }
-                        }
                     }
                 }
             }
             if (lane == 0) NPD_TRACE(sm_role, 32, k);
             g += it.n_kv;
-            cnt += my_tiles;
+            c += U;
         }
     }
 
@@ -812,7 +779,8 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                 NPD_ERR_INVALID_ARG, "prefill attention: NULL pointer");
     NPD_REQUIRE(workspace != nullptr && workspace_bytes >= 256, NPD_ERR_WORKSPACE,
                 "prefill attention: workspace of at least 256 bytes needed (status word)");
-    NPD_REQUIRE(npd::aligned16(out) && npd::aligned16(q), NPD_ERR_INVALID_ARG, "prefill attention: q/out alignment");
+    NPD_REQUIRE(npd::aligned16(q) && (reinterpret_cast<uintptr_t>(out) & 31u) == 0, NPD_ERR_INVALID_ARG,
+                "prefill attention: q must be 16-byte and out 32-byte aligned");
     NPD_REQUIRE(num_blocks < INT32_MAX && max_blocks_per_seq * block_size < INT32_MAX, NPD_ERR_INVALID_ARG,
                 "prefill attention: dimension exceeds int32");
 
