@@ -69,6 +69,7 @@ struct PrefillParams {
     int num_q_heads, num_kv_heads, group;
     int tq;                 // query tokens per 128-row tile = 128 / group (floor)
     int block_size;
+    int box_rows;           // rows of a K/V TMA box: 16, or 8 when the block size is 8
     int max_blocks_per_seq;
     int num_blocks;
     long long bt_row_stride;
@@ -289,7 +290,10 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, int item) {
 // ragged chunks balance across the SMs.  All barrier phases are driven by running counters: the producer
 // already loads the next item's K/V tiles (and, once the last score MMA has been issued, its query tiles) while
 // the current item drains, and the epilogue of an item overlaps the first MMAs of the next one.
-template <typename T, int kD>
+// kBox8: blocks of 8 tokens (a 16-key row group of a K/V tile is then two TMA boxes of 8 rows); a template parameter
+// because the producer warp shares a sub-partition's issue slots with two softmax warps, and every instruction it
+// runs per key tile shows in the kernel's time (the run-time form of this choice cost 2.3 %).
+template <typename T, int kD, bool kBox8>
 __global__ void __launch_bounds__(kThreads, 1)
 paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -398,10 +402,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             };
             if (!(ok = load_q(0))) break;
             const int32_t *table = p.block_tables + (long long)it.c * p.bt_row_stride;
-            auto lookup = [&](int t) {
-                const int key = t * kKeys + gi * 16;
+            // A lane's 16 keys lie in one block (one box of 16 rows), or in two blocks of 8 (two boxes of 8 rows).
+            constexpr bool two_boxes = kBox8;
+            auto lookup_one = [&](int t, int key) {
                 int id = 0;
-                if (role < 2 && t < it.n_kv && key < it.ctx_end) {
+                if (t < it.n_kv && key < it.ctx_end) {
                     id = __ldg(table + key / p.block_size);
                     if (id < 0 || id >= p.num_blocks) {
                         atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
@@ -410,11 +415,15 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 return id;
             };
-            int id_next = lookup(0);
+            auto lookup = [&](int t) {
+                const int key = t * kKeys + gi * 16;
+                return make_int2(lookup_one(t, key), two_boxes ? lookup_one(t, key + 8) : 0);
+            };
+            int2 id_next = lookup(0);
             for (int t = 0; t < it.n_kv; ++t, ++g) {
                 const int stage = g % kStages;
                 const int key0 = t * kKeys;
-                const int id = id_next;
+                const int2 id = id_next;
                 id_next = lookup(t + 1);
                 // 16-key row groups holding at least one written key; the rest is never loaded
                 int ngroups = 0;
@@ -431,9 +440,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (role == 0 && gi < ngroups && hf < kHalves)
-                    tma_load_3d(smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->k_full[stage]),
-                                hf * 64, row, id);
+                if (role == 0 && gi < ngroups && hf < kHalves) {
+                    const uint32_t dst = smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off;
+                    tma_load_3d(dst, tm, smem_u32(&ctrl->k_full[stage]), hf * 64, row, id.x);
+                    if (two_boxes) tma_load_3d(dst + 8 * 128, tm, smem_u32(&ctrl->k_full[stage]), hf * 64, row, id.y);
+                }
                 if (t == 0 && !(ok = load_q(1))) break;
                 // ---- V tile (lanes 16-31): free once the PV MMAs two tiles back are done
                 if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
@@ -442,9 +453,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
                 }
                 __syncwarp();
-                if (role == 1 && gi < ngroups && hf < kHalves)
-                    tma_load_3d(smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&ctrl->v_full[stage]),
-                                hf * 64, row, id);
+                if (role == 1 && gi < ngroups && hf < kHalves) {
+                    const uint32_t dst = smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off;
+                    tma_load_3d(dst, tm, smem_u32(&ctrl->v_full[stage]), hf * 64, row, id.x);
+                    if (two_boxes) tma_load_3d(dst + 8 * 128, tm, smem_u32(&ctrl->v_full[stage]), hf * 64, row, id.y);
+                }
             }
             ok = __all_sync(0xffffffffu, ok);
         }
@@ -765,8 +778,8 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                 "prefill attention supports float16 and bfloat16 only (dtype code %d)", dtype);
     NPD_REQUIRE(head_dim == 64 || head_dim == 128, NPD_ERR_UNSUPPORTED,
                 "prefill attention: head_dim %lld not in {64,128}", (long long)head_dim);
-    NPD_REQUIRE(block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
-                "prefill attention: block_size %lld not in {16,32}", (long long)block_size);
+    NPD_REQUIRE(block_size == 8 || block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
+                "prefill attention: block_size %lld not in {8,16,32}", (long long)block_size);
     NPD_REQUIRE(num_chunks >= 0 && num_q_heads > 0 && num_kv_heads > 0 && max_blocks_per_seq > 0 && num_blocks > 0,
                 NPD_ERR_INVALID_ARG, "prefill attention: non-positive dimension");
     NPD_REQUIRE(num_q_heads % num_kv_heads == 0, NPD_ERR_INVALID_ARG,
@@ -804,18 +817,22 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         const int rc = npd::encode_tiled_3d(&tq_map, q, dtype, dims, strides, box);
         if (rc != NPD_OK) return rc;
     }
+    const int box_rows = block_size < 16 ? static_cast<int>(block_size) : 16;
     int rc = npd::encode_cache_tensor_map(&tk, k_cache, dtype, head_dim, num_kv_heads * block_size, num_blocks,
-                                          cache_block_stride, 16);
+                                          cache_block_stride, box_rows);
     if (rc != NPD_OK) return rc;
     rc = npd::encode_cache_tensor_map(&tv, v_cache, dtype, head_dim, num_kv_heads * block_size, num_blocks,
-                                      cache_block_stride, 16);
+                                      cache_block_stride, box_rows);
     if (rc != NPD_OK) return rc;
 
     const size_t halves = static_cast<size_t>(head_dim / 64);
     const size_t smem = 1024 + 2 * halves * kQHalfBytes + 2 * (size_t)kStages * halves * kKvHalfBytes + sizeof(SmemCtrl) + 64;
-    auto kern = head_dim == 128
-                    ? (dtype == NPD_DTYPE_F16 ? paged_prefill_kernel<__half, 128> : paged_prefill_kernel<__nv_bfloat16, 128>)
-                    : (dtype == NPD_DTYPE_F16 ? paged_prefill_kernel<__half, 64> : paged_prefill_kernel<__nv_bfloat16, 64>);
+    const bool f16 = dtype == NPD_DTYPE_F16;
+    auto kern = box_rows == 8
+                    ? (head_dim == 128 ? (f16 ? paged_prefill_kernel<__half, 128, true> : paged_prefill_kernel<__nv_bfloat16, 128, true>)
+                                       : (f16 ? paged_prefill_kernel<__half, 64, true> : paged_prefill_kernel<__nv_bfloat16, 64, true>))
+                    : (head_dim == 128 ? (f16 ? paged_prefill_kernel<__half, 128, false> : paged_prefill_kernel<__nv_bfloat16, 128, false>)
+                                       : (f16 ? paged_prefill_kernel<__half, 64, false> : paged_prefill_kernel<__nv_bfloat16, 64, false>));
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -835,6 +852,7 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.group = group;
         p.tq = tq;
         p.block_size = static_cast<int>(block_size);
+        p.box_rows = box_rows;
         p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
         p.num_blocks = static_cast<int>(num_blocks);
         p.bt_row_stride = bt_row_stride;

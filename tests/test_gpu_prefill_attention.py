@@ -70,6 +70,15 @@ def test_block_size_32(kernels, dtype):
     check_single(kernels, 500, 200, 300, 8, 2, 32, dtype, seed=5)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L,start,n,poison", [(500, 200, 300, False), (77, 0, 77, True), (1100, 1000, 100, True),
+                                              (264, 256, 8, False)])
+def test_block_size_8(kernels, dtype, L, start, n, poison):
+    """Blocks of 8 tokens (what the decode kernel also takes): a 16-key row group of a K/V tile then lies in two
+    blocks and is fetched as two boxes of 8 rows."""
+    check_single(kernels, L, start, n, 8, 2, 8, dtype, seed=6, poison=poison)
+
+
 def test_unwritten_slots_are_never_used(kernels):
     """NaN everywhere outside keys [0, start+n): later tokens of the prompt, the tail of the last page
     and unused blocks must not reach the output."""
@@ -176,10 +185,9 @@ def test_argument_errors(kernels):
         kernels.paged_prefill_attention(out, q, kc, kc, bt, [0], [16], [60], 1.0, 16, 4)
     with pytest.raises(RuntimeError):   # chunk outside q
         kernels.paged_prefill_attention(out, q, kc, kc, bt, [8], [16], [0], 1.0, 16, 4)
-    q8 = torch.zeros(16, 8, 128, dtype=torch.float16, device=DEV)
-    kc8 = torch.zeros(8, 2, 8, 128, dtype=torch.float16, device=DEV)
-    with pytest.raises(RuntimeError):   # block size 8 is outside the tensor-core kernel's set
-        kernels.paged_prefill_attention(torch.zeros_like(q8), q8, kc8, kc8, bt, [0], [16], [0], 1.0, 8, 4)
+    kc4 = torch.zeros(8, 2, 4, 128, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError):   # block size 4 is outside the kernel's set (8, 16, 32)
+        kernels.paged_prefill_attention(out, q, kc4, kc4, bt, [0], [16], [0], 1.0, 4, 4)
 
 
 def test_more_chunks_than_one_launch_takes(kernels):

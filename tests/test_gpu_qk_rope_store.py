@@ -93,6 +93,16 @@ def test_fused_projection_views_and_separate_output(kernels, dtype, D):
     check_close(q_out, q_ref, "q")
     check_close(kc, kc_ref, "k cache")
     assert torch.equal(vc.cpu(), vc_ref)
+    # in place over the strided view of the fused buffer (q_out aliases q, the default): the rotated queries replace
+    # the q columns, the k and v columns of the buffer stay as they were
+    kc.zero_(), vc.zero_()
+    ret = paged_kernels.paged_qk_norm_rope_store(q_d, k_d, v_d, cos.to(DEV), sin.to(DEV), kc, vc, tables.to(DEV),
+                                                 positions.to(DEV), qw.to(DEV), kw.to(DEV), 1e-6)
+    torch.cuda.synchronize()
+    assert ret.data_ptr() == q_d.data_ptr() and ret.stride(0) == (Hq + 2 * Hkv) * D
+    check_close(ret, q_ref, "q in place")
+    assert torch.equal(qkv_d[:, Hq * D:].cpu(), qkv[:, Hq * D:])
+    check_close(kc, kc_ref, "k cache (in-place run)")
     assert paged_kernels.check_status(DEV, raise_on_error=False) == 0
 
 
