@@ -43,16 +43,20 @@ constexpr int kMaxChunks = 64;     // chunks per launch (kernel-parameter arrays
 constexpr int kMaxPairs = 2048;    // query-tile pairs per launch (kernel-parameter array, heaviest first)
 constexpr int kSchedSlots = 4;     // work items the producer may publish ahead of the slowest consumer
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
-constexpr int kKeys = 128;         // keys per K/V tile in shared memory
+constexpr int kKeys = 128;         // keys per K/V tile in shared memory (64 at head_dim 256)
 constexpr int kHalfKeys = 64;      // keys per half-step (UMMA N of a score MMA, K extent of a PV MMA batch)
 constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA for A, 10 MMA for B, 11 idle
 constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
-constexpr int kKvHalfBytes = kKeys * 128;           // one 64-element half of a 128-key K or V tile
-// head_dim kD = 64 * kHalves (64 or 128): a tile is kHalves halves of 16 KiB
+// head_dim kD = 64 * kHalves (64, 128 or 256): a tile is kHalves slabs, each 64 elements wide.  At head_dim 256 an
+// item is ONE query tile (two tiles' accumulators, 2 x 256 columns, would not fit the 512 TMEM columns beside the
+// scores) and a K/V tile holds 64 keys (one half-step), so that the rings still fit shared memory.
 template <int kD> struct TileBytes {
     static constexpr int kHalves = kD / 64;
+    static constexpr int kTileKeys = kD == 256 ? 64 : kKeys;
+    static constexpr int kQueryTiles = kD == 256 ? 1 : 2;
+    static constexpr int kvSlab = kTileKeys * 128;      // one 64-element-wide slab of a K or V tile
     static constexpr int q = kHalves * kQHalfBytes;     // 32 KiB at head_dim 128
-    static constexpr int kv = kHalves * kKvHalfBytes;   // 32 KiB at head_dim 128
+    static constexpr int kv = kHalves * kvSlab;         // 32 KiB at head_dim 128 and 256
 };
 constexpr int kStages = 2;                          // K ring and V ring depth
 constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; a tile's score columns are two buffers of
@@ -70,6 +74,8 @@ struct PrefillParams {
     int tq;                 // query tokens per 128-row tile = 128 / group (floor)
     int block_size;
     int box_rows;           // rows of a K/V TMA box: 16, or 8 when the block size is 8
+    int query_tiles;        // query tiles per work item (2; 1 at head_dim 256)
+    int half_steps_per_tile;   // 64-key half-steps per K/V tile (2; 1 at head_dim 256)
     int max_blocks_per_seq;
     int num_blocks;
     long long bt_row_stride;
@@ -275,11 +281,11 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, int item) {
     it.ctx_end = it.start + n_tok;                              // keys written so far for this sequence
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
-        it.tok0[x] = (2 * pair + x) * p.tq;
-        it.tq_valid[x] = max(0, min(p.tq, n_tok - it.tok0[x]));
+        it.tok0[x] = (p.query_tiles * pair + x) * p.tq;
+        it.tq_valid[x] = x < p.query_tiles ? max(0, min(p.tq, n_tok - it.tok0[x])) : 0;
         // keys [0, start + tok0 + tq_valid) are visible to the tile
         it.nhalf[x] = it.tq_valid[x] > 0 ? (it.start + it.tok0[x] + it.tq_valid[x] + kHalfKeys - 1) / kHalfKeys : 0;
-        it.ntiles[x] = (it.nhalf[x] + 1) / 2;
+        it.ntiles[x] = (it.nhalf[x] + p.half_steps_per_tile - 1) / p.half_steps_per_tile;
     }
     it.n_kv = max(it.ntiles[0], it.ntiles[1]);
     return it;
@@ -303,8 +309,12 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     uint8_t *sbase = smem_raw + pad;
     constexpr int kHalves = TileBytes<kD>::kHalves;
     constexpr int kQTileBytes = TileBytes<kD>::q, kKvTileBytes = TileBytes<kD>::kv;
+    constexpr int kTK = TileBytes<kD>::kTileKeys;               // keys per K/V tile
+    constexpr int kHPT = kTK / kHalfKeys;                       // half-steps per K/V tile
+    constexpr int kKvHalfBytes = TileBytes<kD>::kvSlab;         // one 64-element-wide slab of a K or V tile
+    constexpr int kQueryTiles = TileBytes<kD>::kQueryTiles;
     uint8_t *q_tiles = sbase;                                   // query tiles A and B
-    uint8_t *k_ring = q_tiles + 2 * kQTileBytes;                // kStages K tiles
+    uint8_t *k_ring = q_tiles + kQueryTiles * kQTileBytes;      // kStages K tiles
     uint8_t *v_ring = k_ring + kStages * kKvTileBytes;          // kStages V tiles
     SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStages * kKvTileBytes);
 
@@ -362,7 +372,10 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
         }
-        const int role = lane >> 4, gi = (lane >> 1) & 7, hf = lane & 1;     // role 0 = K, 1 = V
+        // 16 lanes per role (0 = K, 1 = V): one per (16-key row group, 64-element slab) box of a tile — 8 groups x 2
+        // slabs at head_dim <= 128, 4 groups x 4 slabs at head_dim 256
+        const int role = lane >> 4;
+        const int gi = kHalves == 4 ? (lane >> 2) & 3 : (lane >> 1) & 7, hf = kHalves == 4 ? lane & 3 : lane & 1;
         const CUtensorMap *tm = role == 1 ? &tm_v : &tm_k;
         int g = 0;                                              // g: key tiles loaded so far (ring position)
         int q_loads[2] = {0, 0};                                // per query tile: items loaded so far (phases of q_empty)
@@ -416,18 +429,18 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 return id;
             };
             auto lookup = [&](int t) {
-                const int key = t * kKeys + gi * 16;
+                const int key = t * kTK + gi * 16;
                 return make_int2(lookup_one(t, key), two_boxes ? lookup_one(t, key + 8) : 0);
             };
             int2 id_next = lookup(0);
             for (int t = 0; t < it.n_kv; ++t, ++g) {
                 const int stage = g % kStages;
-                const int key0 = t * kKeys;
+                const int key0 = t * kTK;
                 const int2 id = id_next;
                 id_next = lookup(t + 1);
                 // 16-key row groups holding at least one written key; the rest is never loaded
                 int ngroups = 0;
-                for (int g2 = 0; g2 < kKeys / 16; ++g2) ngroups += (key0 + g2 * 16 < it.ctx_end) ? 1 : 0;
+                for (int g2 = 0; g2 < kTK / 16; ++g2) ngroups += (key0 + g2 * 16 < it.ctx_end) ? 1 : 0;
                 const uint32_t bytes = static_cast<uint32_t>(ngroups * kHalves * 16 * 128);
                 const int row = it.h * p.block_size + ((key0 + gi * 16) % p.block_size);
                 const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048);
@@ -445,7 +458,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     tma_load_3d(dst, tm, smem_u32(&ctrl->k_full[stage]), hf * 64, row, id.x);
                     if (two_boxes) tma_load_3d(dst + 8 * 128, tm, smem_u32(&ctrl->k_full[stage]), hf * 64, row, id.y);
                 }
-                if (t == 0 && !(ok = load_q(1))) break;
+                if (kQueryTiles > 1 && t == 0 && !(ok = load_q(1))) break;
                 // ---- V tile (lanes 16-31): free once the PV MMAs two tiles back are done
                 if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
                 if (!__all_sync(0xffffffffu, ok)) break;
@@ -527,53 +540,49 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (!__all_sync(0xffffffffu, ok) || item < 0) break;
                 const Item it = decode_item(p, item);
                 const int U = it.nhalf[x], my_tiles = it.ntiles[x];
+                // Half-step u of the item lies in K/V tile u / kHPT (half u % kHPT of it).  A score batch is followed by
+                // the release of its K tile when it was the last one to read it.
+                auto scores = [&](int u, int buf) {
+                    const int t = u / kHPT, h = u % kHPT, gt = g + t;
+                    if (h == 0 && !wait_all(&ctrl->k_full[gt % kStages], (gt / kStages) & 1)) return false;
+                    tc_fence_after();
+                    NPD_TRACE(x == 0 ? 1 : 4, 12, u);
+                    issue_s(gt % kStages, h, buf);
+                    NPD_TRACE(x == 0 ? 1 : 4, 13, u);
+                    if (h == kHPT - 1 || u == U - 1) commit(&ctrl->k_empty[gt % kStages]);
+                    if (u == U - 1) commit(&ctrl->q_empty[x]);       // no further score MMA of this item reads Q_X
+                    return true;
+                };
                 if (U > 0) {
                     // the first two half-steps' scores: both buffers are free (the previous item's last PV
                     // products, which read P from them, were issued before these MMAs)
                     if (!(ok = wait_all(&ctrl->q_full[x], items_done & 1))) break;
-                    if (!(ok = wait_all(&ctrl->k_full[g % kStages], (g / kStages) & 1))) break;
-                    tc_fence_after();
-                    issue_s(g % kStages, 0, c & 1);
-                    if (U > 1) issue_s(g % kStages, 1, (c + 1) & 1);
-                    commit(&ctrl->k_empty[g % kStages]);
-                    if (U <= 2) commit(&ctrl->q_empty[x]);       // no further score MMA of this item reads Q_X
+                    if (!(ok = scores(0, c & 1))) break;
+                    if (U > 1 && !(ok = scores(1, (c + 1) & 1))) break;
                 }
-                for (int t = 0; ok && t < it.n_kv; ++t) {
+                for (int u = 0; ok && u < U; ++u) {
+                    const int t = u / kHPT, h = u % kHPT, gt = g + t, stage = gt % kStages;
+                    const int cu = c + u, buf = cu & 1;
+                    // O_X is overwritten by the first PV of an item: the previous epilogue must have read it
+                    if (u == 0 && items_done > 0 && !(ok = wait_all(&ctrl->o_free[x], (items_done - 1) & 1))) break;
+                    if (h == 0 && !(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
+                    NPD_TRACE(x == 0 ? 1 : 4, 10, u);
+                    if (!(ok = wait_all(&ctrl->p_ready[x][buf], (cu >> 1) & 1))) break;
+                    NPD_TRACE(x == 0 ? 1 : 4, 11, u);
+                    tc_fence_after();
+                    issue_pv(stage, h, buf, u == 0);
+                    NPD_TRACE(x == 0 ? 1 : 4, 14, u);
+                    if (h == kHPT - 1 || u == U - 1) commit(&ctrl->v_empty[stage]);
+                    // S(u+2) goes into the buffer P(u) sits in; it executes after the PV MMAs above
+                    if (u + 2 < U && !(ok = scores(u + 2, buf))) break;
+                }
+                for (int t = my_tiles; ok && t < it.n_kv; ++t) {
+                    // a key tile only the other query tile needs: observe it so that ring phases stay in step
                     const int gt = g + t, stage = gt % kStages;
-                    if (t < my_tiles) {
-                        for (int h = 0; ok && h < 2; ++h) {
-                            const int u = 2 * t + h;
-                            if (u >= U) break;
-                            const int cu = c + u, buf = cu & 1;
-                            // O_X is overwritten by the first PV of an item: the previous epilogue must have read it
-                            if (u == 0 && items_done > 0 && !(ok = wait_all(&ctrl->o_free[x], (items_done - 1) & 1))) break;
-                            if (h == 0 && !(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
-                            NPD_TRACE(x == 0 ? 1 : 4, 10, u);
-                            if (!(ok = wait_all(&ctrl->p_ready[x][buf], (cu >> 1) & 1))) break;
-                            NPD_TRACE(x == 0 ? 1 : 4, 11, u);
-                            tc_fence_after();
-                            issue_pv(stage, h, buf, u == 0);
-                            NPD_TRACE(x == 0 ? 1 : 4, 14, u);
-                            if (h == 1 || u == U - 1) commit(&ctrl->v_empty[stage]);
-                            const int u2 = u + 2;
-                            if (u2 < U) {
-                                // S(u+2) goes into the buffer P(u) sits in; it executes after the PV MMAs above
-                                const int gt2 = gt + 1, stage2 = gt2 % kStages;
-                                if (h == 0 && !(ok = wait_all(&ctrl->k_full[stage2], (gt2 / kStages) & 1))) break;
-                                NPD_TRACE(x == 0 ? 1 : 4, 12, u);
-                                issue_s(stage2, h, buf);
-                                NPD_TRACE(x == 0 ? 1 : 4, 13, u);
-                                if (h == 1 || u2 == U - 1) commit(&ctrl->k_empty[stage2]);
-                                if (u2 == U - 1) commit(&ctrl->q_empty[x]);     // that was the item's last score MMA
-                            }
-                        }
-                    } else {
-                        // a key tile only the other query tile needs: observe it so that ring phases stay in step
-                        if (!(ok = wait_all(&ctrl->k_full[stage], (gt / kStages) & 1))) break;
-                        commit(&ctrl->k_empty[stage]);
-                        if (!(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
-                        commit(&ctrl->v_empty[stage]);
-                    }
+                    if (!(ok = wait_all(&ctrl->k_full[stage], (gt / kStages) & 1))) break;
+                    commit(&ctrl->k_empty[stage]);
+                    if (!(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
+                    commit(&ctrl->v_empty[stage]);
                 }
                 g += it.n_kv;
                 c += U;
@@ -608,17 +617,17 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll 1
             for (int u = 0; ok && u < U; ++u) {
                 const int cu = c + u, buf = cu & 1;
-                const int t = u >> 1, gt = g + t, stage = gt % kStages;
+                const int t = u / kHPT, gt = g + t, stage = gt % kStages;
                 const int key0 = u * kHalfKeys;
                 // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
                 // there cannot meet a NaN.  Both softmax groups do it (idempotent), at the first half-step of the
                 // key tile, before they release its probabilities.
-                if ((u & 1) == 0 && t * kKeys + kKeys > it.ctx_end) {
+                if (u % kHPT == 0 && t * kTK + kTK > it.ctx_end) {
                     if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (gt / kStages) & 1, abort_flag, p.status))) break;
                     uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
-                    const int first = max(it.ctx_end - t * kKeys, 0);
+                    const int first = max(it.ctx_end - t * kTK, 0);
                     constexpr int kPieces = kHalves * 8;           // 16-byte pieces per row
-                    const int n16 = (kKeys - first) * kPieces;
+                    const int n16 = (kTK - first) * kPieces;
                     for (int idx = threadIdx.x & 127; idx < n16; idx += 128) {
                         const int r = first + idx / kPieces, piece = idx % kPieces;
                         *reinterpret_cast<uint4 *>(v_tile + (piece >> 3) * kKvHalfBytes + r * 128 + ((piece & 7) << 4)) =
@@ -723,27 +732,33 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     const float inv = 1.f / l_run;
                     T *dst = static_cast<T *>(p.out) +
                              ((long long)(it.qoff + it.tok0[x] + tq_idx) * p.num_q_heads + (long long)it.h * p.group + hg) * kD;
-                    // the whole accumulator row in one go: kD/32 loads in flight, one wait
-                    float o[kD / 32][32];
+                    // the accumulator row in groups of up to 128 columns: all loads of a group in flight, one wait
+                    constexpr int kChunks = kD / 32, kGroup = kChunks < 4 ? kChunks : 4;
 #pragma unroll
-                    for (int cc = 0; cc < kD / 32; ++cc) tmem_ld32(t_o + cc * 32, o[cc]);
-                    tmem_wait_ld();
-                    // O is in registers: the next item's first PV may overwrite the accumulator
-                    tc_fence_before();
-                    mbar_arrive(smem_u32(&ctrl->o_free[x]));
-                    if (store) {
-                        // 32 bytes per lane and instruction: a lane's row is contiguous, the lanes of a warp are 256
-                        // bytes apart, so every store instruction fills whole 32-byte sectors
+                    for (int c0 = 0; c0 < kChunks; c0 += kGroup) {
+                        float o[kGroup][32];
 #pragma unroll
-                        for (int cc = 0; cc < kD / 32; ++cc)
+                        for (int cc = 0; cc < kGroup; ++cc) tmem_ld32(t_o + (c0 + cc) * 32, o[cc]);
+                        tmem_wait_ld();
+                        if (c0 + kGroup == kChunks) {
+                            // O is in registers: the next item's first PV may overwrite the accumulator
+                            tc_fence_before();
+                            mbar_arrive(smem_u32(&ctrl->o_free[x]));
+                        }
+                        if (store) {
+                            // 32 bytes per lane and instruction: a lane's row is contiguous and the lanes of a warp are a
+                            // row apart, so every store instruction fills whole 32-byte sectors
 #pragma unroll
-                            for (int i = 0; i < 32; i += 16) {
-                                uint32_t w[8];
+                            for (int cc = 0; cc < kGroup; ++cc)
 #pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    w[j] = Elem<T>::pack2(o[cc][i + 2 * j] * inv, o[cc][i + 2 * j + 1] * inv);
-                                st_global_32B(dst + cc * 32 + i, w);
-                            }
+                                for (int i = 0; i < 32; i += 16) {
+                                    uint32_t w[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j)
+                                        w[j] = Elem<T>::pack2(o[cc][i + 2 * j] * inv, o[cc][i + 2 * j + 1] * inv);
+                                    st_global_32B(dst + (c0 + cc) * 32 + i, w);
+                                }
+                        }
                     }
                 }
             }
@@ -776,8 +791,8 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                                            void *stream) {
     NPD_REQUIRE(dtype == NPD_DTYPE_F16 || dtype == NPD_DTYPE_BF16, NPD_ERR_UNSUPPORTED,
                 "prefill attention supports float16 and bfloat16 only (dtype code %d)", dtype);
-    NPD_REQUIRE(head_dim == 64 || head_dim == 128, NPD_ERR_UNSUPPORTED,
-                "prefill attention: head_dim %lld not in {64,128}", (long long)head_dim);
+    NPD_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, NPD_ERR_UNSUPPORTED,
+                "prefill attention: head_dim %lld not in {64,128,256}", (long long)head_dim);
     NPD_REQUIRE(block_size == 8 || block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
                 "prefill attention: block_size %lld not in {8,16,32}", (long long)block_size);
     NPD_REQUIRE(num_chunks >= 0 && num_q_heads > 0 && num_kv_heads > 0 && max_blocks_per_seq > 0 && num_blocks > 0,
@@ -826,13 +841,19 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
     if (rc != NPD_OK) return rc;
 
     const size_t halves = static_cast<size_t>(head_dim / 64);
-    const size_t smem = 1024 + 2 * halves * kQHalfBytes + 2 * (size_t)kStages * halves * kKvHalfBytes + sizeof(SmemCtrl) + 64;
+    const int query_tiles = head_dim == 256 ? 1 : 2, tile_keys = head_dim == 256 ? 64 : kKeys;
+    const size_t smem = 1024 + query_tiles * halves * kQHalfBytes + 2 * (size_t)kStages * halves * tile_keys * 128 +
+                        sizeof(SmemCtrl) + 64;
     const bool f16 = dtype == NPD_DTYPE_F16;
-    auto kern = box_rows == 8
-                    ? (head_dim == 128 ? (f16 ? paged_prefill_kernel<__half, 128, true> : paged_prefill_kernel<__nv_bfloat16, 128, true>)
-                                       : (f16 ? paged_prefill_kernel<__half, 64, true> : paged_prefill_kernel<__nv_bfloat16, 64, true>))
-                    : (head_dim == 128 ? (f16 ? paged_prefill_kernel<__half, 128, false> : paged_prefill_kernel<__nv_bfloat16, 128, false>)
-                                       : (f16 ? paged_prefill_kernel<__half, 64, false> : paged_prefill_kernel<__nv_bfloat16, 64, false>));
+    using Kernel = void (*)(PrefillParams, CUtensorMap, CUtensorMap, CUtensorMap);
+    Kernel kern = nullptr;
+#define NPD_PICK(D_)                                                                                              \
+    kern = box_rows == 8 ? (f16 ? paged_prefill_kernel<__half, D_, true> : paged_prefill_kernel<__nv_bfloat16, D_, true>)   \
+                         : (f16 ? paged_prefill_kernel<__half, D_, false> : paged_prefill_kernel<__nv_bfloat16, D_, false>)
+    if (head_dim == 64) NPD_PICK(64);
+    else if (head_dim == 128) NPD_PICK(128);
+    else NPD_PICK(256);
+#undef NPD_PICK
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -853,6 +874,8 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
         p.tq = tq;
         p.block_size = static_cast<int>(block_size);
         p.box_rows = box_rows;
+        p.query_tiles = query_tiles;
+        p.half_steps_per_tile = tile_keys / kHalfKeys;
         p.max_blocks_per_seq = static_cast<int>(max_blocks_per_seq);
         p.num_blocks = static_cast<int>(num_blocks);
         p.bt_row_stride = bt_row_stride;
@@ -868,10 +891,10 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
             p.chunk_q_offset[i] = chunk_q_offset_host[c0 + i];
             p.chunk_tokens[i] = chunk_tokens_host[c0 + i];
             p.chunk_start[i] = chunk_start_host[c0 + i];
-            const int pairs = (p.chunk_tokens[i] + 2 * tq - 1) / (2 * tq);
+            const int pairs = (p.chunk_tokens[i] + query_tiles * tq - 1) / (query_tiles * tq);
             NPD_REQUIRE(pairs <= 0xffff, NPD_ERR_INVALID_ARG, "prefill attention: chunk %d is too long", i);
             for (int pr = 0; pr < pairs; ++pr) {
-                const int last_tok = std::min(p.chunk_tokens[i], (2 * pr + 2) * tq);
+                const int last_tok = std::min(p.chunk_tokens[i], (pr + 1) * query_tiles * tq);
                 entries.push_back({(p.chunk_start[i] + last_tok + kKeys - 1) / kKeys,
                                    (static_cast<uint32_t>(i) << 16) | static_cast<uint32_t>(pr)});
             }

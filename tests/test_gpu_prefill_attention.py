@@ -232,9 +232,17 @@ def test_head_dim_64(kernels, dtype, L, start, n, Hq, Hkv, B):
     check_single(kernels, L, start, n, Hq, Hkv, B, dtype, seed=L + 1, poison=True, D=64)
 
 
-def test_head_dim_256_is_refused(kernels):
-    q = torch.zeros(4, 2, 256, dtype=torch.float16, device=DEV)
-    kc = torch.zeros(2, 2, 16, 256, dtype=torch.float16, device=DEV)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L,start,n,Hq,Hkv,B", [(200, 0, 200, 4, 1, 16), (700, 512, 188, 8, 2, 16), (130, 129, 1, 4, 2, 32),
+                                                (1024, 512, 512, 4, 1, 16), (300, 100, 150, 2, 2, 8), (65, 0, 65, 16, 1, 16)])
+def test_head_dim_256(kernels, dtype, L, start, n, Hq, Hkv, B):
+    """head_dim 256 (what the decode kernel also takes): one query tile per work item, K/V tiles of 64 keys."""
+    check_single(kernels, L, start, n, Hq, Hkv, B, dtype, seed=9, poison=(start > 0), D=256)
+
+
+def test_head_dim_96_is_refused(kernels):
+    q = torch.zeros(4, 2, 96, dtype=torch.float16, device=DEV)
+    kc = torch.zeros(2, 2, 16, 96, dtype=torch.float16, device=DEV)
     with pytest.raises(RuntimeError, match="head_dim"):
         kernels.paged_prefill_attention(torch.zeros_like(q), q, kc, kc.clone(), torch.zeros(1, 1, dtype=torch.int32, device=DEV),
                                         [0], [4], [0], 1.0, 16, 1)

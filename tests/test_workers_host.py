@@ -126,3 +126,29 @@ def test_requests_not_yet_arrived_are_left_waiting():
     import time
     sched._t0 = time.perf_counter()
     assert sched._take_batch(sched.prefill_workers[0]) == []
+
+
+def test_synthetic_request_streams_follow_the_named_distributions():
+    """Configuration 4: Poisson arrivals, lognormal prompts clipped to [16, 4096], geometric outputs capped at 1024;
+    configuration 5: prompts uniform in [2048, 16384], 128 output tokens.  Seeded, so two draws agree."""
+    pin = torch.Tensor.pin_memory
+    torch.Tensor.pin_memory = lambda self, *a, **k: self          # no CUDA here: pinning is a no-op for this check
+    try:
+        from nanopd_b200 import serving
+        a = serving.poisson_requests(32.0, 20.0, 1000, seed=3)
+        b = serving.poisson_requests(32.0, 20.0, 1000, seed=3)
+        d = serving.disagg_requests(200, 1000, seed=3)
+    finally:
+        torch.Tensor.pin_memory = pin
+    assert [r.prompt_len for r in a] == [r.prompt_len for r in b] and [r.arrival for r in a] == [r.arrival for r in b]
+    n = len(a)
+    assert 500 < n < 780                                            # 32 req/s over 20 s
+    arrivals = np.array([r.arrival for r in a])
+    assert (np.diff(arrivals) > 0).all() and arrivals[-1] < 20.0
+    lens = np.array([r.prompt_len for r in a])
+    assert lens.min() >= 16 and lens.max() <= 4096 and 400 < np.median(lens) < 650
+    outs = np.array([r.output_len for r in a])
+    assert outs.min() >= 1 and outs.max() <= 1024 and 200 < outs.mean() < 320
+    dl = np.array([r.prompt_len for r in d])
+    assert dl.min() >= 2048 and dl.max() <= 16384 and 8000 < dl.mean() < 10400 and all(r.output_len == 128 for r in d)
+    assert all(int(r.prompt.max()) < 1000 and r.prompt.dtype == torch.int64 for r in d[:5])
