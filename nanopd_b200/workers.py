@@ -346,7 +346,7 @@ class DecodeWorker:
         # verification runs: keep finished requests' blocks, and copy every step's tokens to pinned host memory
         self.keep_blocks = False
         self.record_tokens = False
-        self.token_log: List[Tuple[torch.Tensor, List[object]]] = []
+        self._inflight: Deque[torch.cuda.Event] = deque()      # events behind the last few steps (host pacing)
 
     # ---- admission control: a request reserves its blocks and a slot before its prefill starts ----
     def blocks_for(self, req: Request) -> int:
@@ -440,13 +440,14 @@ class DecodeWorker:
         for handoff in ready:
             req = handoff.request
             handoff.release()                                     # the prefill GPU may reuse the source blocks
-            with self._lock:
-                self._reserved_slots -= 1
             req.stats["t_first_token"] = time.perf_counter()
-            if req.decode_steps == 0:
+            with self._lock:                                      # the reservation becomes a slot in one step
+                self._reserved_slots -= 1
+                slot = (self.slots.table.admit(req, req.dst_blocks, req.prompt_len, req.decode_steps)
+                        if req.decode_steps > 0 else None)
+            if slot is None:
                 self._finish(req)
                 continue
-            slot = self.slots.table.admit(req, req.dst_blocks, req.prompt_len, req.decode_steps)
             self.model.token_ids[slot:slot + 1].copy_(handoff.first_token, non_blocking=True)
             if self.record_tokens:
                 first = torch.empty(1, dtype=torch.int64, pin_memory=True)
@@ -498,10 +499,9 @@ class DecodeWorker:
     def _pace(self, ahead: int = 2) -> None:
         ev = torch.cuda.Event()
         ev.record(self.compute_stream)
-        q = self.__dict__.setdefault("_inflight", deque())
-        q.append(ev)
-        while len(q) > ahead:
-            q.popleft().synchronize()
+        self._inflight.append(ev)
+        while len(self._inflight) > ahead:
+            self._inflight.popleft().synchronize()
 
     @property
     def idle(self) -> bool:
