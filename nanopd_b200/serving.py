@@ -181,10 +181,14 @@ def run_disagg_split(models: Dict[int, decoder_step.SyntheticDecoder], prefill_g
     out_tokens = sum(r.output_len for r in done)
     mig_bytes = sum(r.stats["migrated_bytes"] for r in done)
     exposed = [r.stats["exposed_transfer_ms"] for r in done]
+    prefill_window = max(r.stats["t_first_token"] for r in done)
     res: Dict[str, object] = {
         "prefill_gpus": list(prefill_gpus), "decode_gpus": list(decode_gpus), "layerwise_pull": layerwise,
         "requests": len(done), "prompt_tokens": prompt_tokens, "output_tokens": out_tokens, "wall_s": round(wall, 3),
-        "prefill_tok_s": round(prompt_tokens / wall, 1), "output_tok_s": round(out_tokens / wall, 1),
+        # the run ends with the decode of the last request (its 127 steps after the last prompt): prompt throughput is
+        # taken over the window in which prompts were computed, up to the arrival of the last one's pages
+        "prefill_window_s": round(prefill_window, 3), "prefill_tok_s": round(prompt_tokens / prefill_window, 1),
+        "output_tok_s": round(out_tokens / wall, 1),
         "prefill_ms_per_request_median": round(statistics.median(r.stats["prefill_ms"] for r in done), 2),
         "migrated_bytes": mig_bytes, "migrated_gb_per_request_mean": round(mig_bytes / len(done) / 1e9, 3),
         "exposed_transfer_ms": {"median": round(statistics.median(exposed), 3), "p95": round(_pct(exposed, 0.95), 3),
