@@ -10,11 +10,13 @@
 // Persistent grid, one CTA of 384 threads per SM; items are handed out heaviest first through an atomic
 // counter.  Warp roles:
 //   warps 0-3 / 4-7  softmax of query tile A / B: thread i owns row i == TMEM lane i (no shuffles)
-//   warp  8          TMA producer: query tiles, then K and V tiles into two 2-stage shared-memory rings
-//                    (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA operand layout); it also
-//                    draws the next work item and publishes it to the other roles
+//   warp  8          TMA producer of the query tiles and of the K tiles (a ring of 3 tiles in shared memory;
+//                    cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA operand layout); it also draws
+//                    the next work item and publishes it to the other roles
+//   warp  11         TMA producer of the V tiles (a ring of 2 tiles).  Two producer warps, because the rate at
+//                    which ONE warp can issue tiled copies (about 100 clocks per 2 KiB box) is what bounded the
+//                    kernel when a single warp issued the 32 boxes of a 128-key step
 //   warps 9 / 10     issue the tcgen05.mma instructions of tile A / B (one elected lane)
-//   warp  11         idle (completes the third warpgroup for setmaxnreg)
 // TMEM (512 columns): S_A | S_B | O_A | O_B, 128 columns each.  A query tile walks its keys in HALF-STEPS of 64
 // keys; its 128 score columns are a ring of two 64-column buffers, so the scores of half-step c+1 are
 // already in TMEM while the softmax group works on half-step c, and those of c+2 are computed while the
@@ -45,7 +47,7 @@ constexpr int kSchedSlots = 4;     // work items the producer may publish ahead 
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
 constexpr int kKeys = 128;         // keys per K/V tile in shared memory (64 at head_dim 256)
 constexpr int kHalfKeys = 64;      // keys per half-step (UMMA N of a score MMA, K extent of a PV MMA batch)
-constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA, 9 MMA for A, 10 MMA for B, 11 idle
+constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA (Q, K), 9 MMA for A, 10 MMA for B, 11 TMA (V)
 constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
 // head_dim kD = 64 * kHalves (64, 128 or 256): a tile is kHalves slabs, each 64 elements wide.  At head_dim 256 an
 // item is ONE query tile (two tiles' accumulators, 2 x 256 columns, would not fit the 512 TMEM columns beside the
@@ -58,7 +60,14 @@ template <int kD> struct TileBytes {
     static constexpr int q = kHalves * kQHalfBytes;     // 32 KiB at head_dim 128
     static constexpr int kv = kHalves * kvSlab;         // 32 KiB at head_dim 128 and 256
 };
-constexpr int kStages = 2;                          // K ring and V ring depth
+#ifndef NPD_K_STAGES
+#define NPD_K_STAGES 3
+#endif
+#ifndef NPD_V_STAGES
+#define NPD_V_STAGES 2
+#endif
+constexpr int kStagesK = NPD_K_STAGES;              // K ring depth
+constexpr int kStagesV = NPD_V_STAGES;              // V ring depth
 constexpr int kTmemCols = 512;     // S_A | S_B | O_A | O_B, 128 columns each; a tile's score columns are two buffers of
                                    // 64; the packed probabilities of a half-step overwrite the first 32 of its buffer
 constexpr float kRescaleThreshold = 8.f;   // log2 units: O is rescaled only when a row max grows by more
@@ -245,8 +254,8 @@ struct alignas(8) SmemCtrl {
     int sched_item[kSchedSlots];
     uint64_t q_full[2];          // [query tile]: its rows of the current work item have landed
     uint64_t q_empty[2];         // [query tile]: its MMA warp has issued the last score MMA of the item
-    uint64_t k_full[kStages], v_full[kStages];     // the K / V tile of a ring stage has landed
-    uint64_t k_empty[kStages], v_empty[kStages];   // both MMA warps are done with it (2 arrivals)
+    uint64_t k_full[kStagesK], v_full[kStagesV];     // the K / V tile of a ring stage has landed
+    uint64_t k_empty[kStagesK], v_empty[kStagesV];   // both MMA warps are done with it (2 arrivals)
     uint64_t s_full[2][2];  // [query tile][buffer]: the scores of a half-step are in that buffer (and the PV product
                             // that last read the buffer has completed)
     uint64_t p_ready[2][2]; // [query tile][buffer]: the probabilities of the half-step are in TMEM (128 arrivals)
@@ -314,9 +323,9 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     constexpr int kKvHalfBytes = TileBytes<kD>::kvSlab;         // one 64-element-wide slab of a K or V tile
     constexpr int kQueryTiles = TileBytes<kD>::kQueryTiles;
     uint8_t *q_tiles = sbase;                                   // query tiles A and B
-    uint8_t *k_ring = q_tiles + kQueryTiles * kQTileBytes;      // kStages K tiles
-    uint8_t *v_ring = k_ring + kStages * kKvTileBytes;          // kStages V tiles
-    SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStages * kKvTileBytes);
+    uint8_t *k_ring = q_tiles + kQueryTiles * kQTileBytes;      // kStagesK K tiles
+    uint8_t *v_ring = k_ring + kStagesK * kKvTileBytes;         // kStagesV V tiles
+    SmemCtrl *ctrl = reinterpret_cast<SmemCtrl *>(v_ring + kStagesV * kKvTileBytes);
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int total_items = p.num_pairs * p.num_kv_heads;
@@ -329,10 +338,12 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kSchedSlots; ++i) mbar_init(smem_u32(&ctrl->sched_full[i]), 1);
-        for (int i = 0; i < kStages; ++i) {
+        for (int i = 0; i < kStagesK; ++i) {
             mbar_init(smem_u32(&ctrl->k_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->v_full[i]), 1);
             mbar_init(smem_u32(&ctrl->k_empty[i]), 2);
+        }
+        for (int i = 0; i < kStagesV; ++i) {
+            mbar_init(smem_u32(&ctrl->v_full[i]), 1);
             mbar_init(smem_u32(&ctrl->v_empty[i]), 2);
         }
         for (int x = 0; x < 2; ++x) {
@@ -360,39 +371,50 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     volatile int *abort_flag = &ctrl->abort_flag;
 
     // Register re-allocation between warpgroups (first statement of every role): the two softmax groups
-    // work on whole score rows in registers, the third group (TMA, two MMA warps, one idle warp) needs few.
-    if (warp == 8) {
+    // work on whole score rows in registers, the third group (two TMA warps, two MMA warps) needs few.
+    if (warp == 8 || warp == 11) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-        // =========================== TMA producer (whole warp issues) ===========================
-        // A K or V tile of 128 keys is 16 boxes of 2 KiB (8 groups of 16 keys x 2 halves of 64 elements).
-        // Lanes 0-15 issue the K boxes and lanes 16-31 the V boxes, each lane looking up its own block id
-        // one tile ahead, so neither the table reads nor a serial issue sit on the critical path.
+        // =========================== TMA producers: warp 8 (query tiles, K tiles), warp 11 (V tiles) ===========================
+        // A K or V tile is 16 boxes of 2 KiB (16-key row groups x 64-element slabs; 32 boxes of 1 KiB with blocks
+        // of 8 tokens), one box per lane, issued by ONE instruction of the warp.  Issuing tiled copies costs the
+        // issuing warp about 50 clocks per box plus several hundred per instruction, whatever the box holds, while
+        // the copy engine itself takes boxes from several warps at once: one warp issuing both tiles of a 128-key
+        // step (32 boxes) needed as long as the step's arithmetic, two warps need half of it.  Each lane looks its
+        // block id up one tile ahead, so the table reads are off the critical path too.
+        const bool k_role = warp == 8;
+        const CUtensorMap *tm = k_role ? &tm_k : &tm_v;
         if (lane == 0) {
-            tma_prefetch_desc(&tm_q);
-            tma_prefetch_desc(&tm_k);
-            tma_prefetch_desc(&tm_v);
+            if (k_role) tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(tm);
         }
-        // 16 lanes per role (0 = K, 1 = V): one per (16-key row group, 64-element slab) box of a tile — 8 groups x 2
-        // slabs at head_dim <= 128, 4 groups x 4 slabs at head_dim 256
-        const int role = lane >> 4;
-        const int gi = kHalves == 4 ? (lane >> 2) & 3 : (lane >> 1) & 7, hf = kHalves == 4 ? lane & 3 : lane & 1;
-        const CUtensorMap *tm = role == 1 ? &tm_v : &tm_k;
-        int g = 0;                                              // g: key tiles loaded so far (ring position)
+        // lane -> box: (16-key row group gi, 64-element slab hf, 8-row half `sub` of the group when blocks hold 8 tokens)
+        const int sub = kBox8 ? (lane & 1) : 0, l2 = kBox8 ? (lane >> 1) : lane;
+        const int hf = l2 % kHalves, gi = l2 / kHalves;
+        const bool has_box = gi < kTK / 16;
+        uint8_t *ring = k_role ? k_ring : v_ring;
+        uint64_t *full = k_role ? ctrl->k_full : ctrl->v_full, *empty = k_role ? ctrl->k_empty : ctrl->v_empty;
+        const int stages = k_role ? kStagesK : kStagesV;
+        int stage = 0, round = 0;                               // ring position of the next tile
         int q_loads[2] = {0, 0};                                // per query tile: items loaded so far (phases of q_empty)
         NPD_TRACE_DECL
         bool ok = true;
         for (int k = 0; ok; ++k) {
-            // Fetch and publish the next work item.  A slot is reused kSchedSlots items later; by then every
-            // role has long read it (the producer cannot run more than two items ahead of the MMA warps,
-            // which cannot run ahead of the softmax groups).
+            // Warp 8 fetches and publishes the next work item; warp 11 reads it like the other roles.  A slot is
+            // reused kSchedSlots items later; by then every role has long read it (warp 8 cannot run more than
+            // two items ahead of the MMA warps, which cannot run ahead of the V tiles or the softmax groups).
             int item = 0;
-            if (lane == 0) {
-                item = atomicAdd(p.work_counter, 1);
-                if (item >= total_items) item = -1;
-                *reinterpret_cast<volatile int *>(&ctrl->sched_item[k % kSchedSlots]) = item;
-                mbar_arrive(smem_u32(&ctrl->sched_full[k % kSchedSlots]));
+            if (k_role) {
+                if (lane == 0) {
+                    item = atomicAdd(p.work_counter, 1);
+                    if (item >= total_items) item = -1;
+                    *reinterpret_cast<volatile int *>(&ctrl->sched_item[k % kSchedSlots]) = item;
+                    mbar_arrive(smem_u32(&ctrl->sched_full[k % kSchedSlots]));
+                }
+                item = __shfl_sync(0xffffffffu, item, 0);
+            } else {
+                item = next_item(k, ok);
+                if (!__all_sync(0xffffffffu, ok)) break;
             }
-            item = __shfl_sync(0xffffffffu, item, 0);
             if (item < 0) break;
             const Item it = decode_item(p, item);
             // ---- query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch.
@@ -413,13 +435,13 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 return true;
             };
-            if (!(ok = load_q(0))) break;
+            if (k_role && !(ok = load_q(0))) break;
             const int32_t *table = p.block_tables + (long long)it.c * p.bt_row_stride;
-            // A lane's 16 keys lie in one block (one box of 16 rows), or in two blocks of 8 (two boxes of 8 rows).
-            constexpr bool two_boxes = kBox8;
-            auto lookup_one = [&](int t, int key) {
+            // A lane's box lies in one block: 16 keys of a block of 16 or 32, or 8 keys of a block of 8.
+            auto lookup = [&](int t) {
+                const int key = t * kTK + gi * 16 + sub * 8;
                 int id = 0;
-                if (t < it.n_kv && key < it.ctx_end) {
+                if (has_box && t < it.n_kv && key < it.ctx_end) {
                     id = __ldg(table + key / p.block_size);
                     if (id < 0 || id >= p.num_blocks) {
                         atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
@@ -428,49 +450,33 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 return id;
             };
-            auto lookup = [&](int t) {
-                const int key = t * kTK + gi * 16;
-                return make_int2(lookup_one(t, key), two_boxes ? lookup_one(t, key + 8) : 0);
-            };
-            int2 id_next = lookup(0);
-            for (int t = 0; t < it.n_kv; ++t, ++g) {
-                const int stage = g % kStages;
+            int id_next = lookup(0);
+            const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048 + sub * 8 * 128);
+            for (int t = 0; t < it.n_kv; ++t) {
                 const int key0 = t * kTK;
-                const int2 id = id_next;
+                const int id = id_next;
                 id_next = lookup(t + 1);
                 // 16-key row groups holding at least one written key; the rest is never loaded
                 int ngroups = 0;
                 for (int g2 = 0; g2 < kTK / 16; ++g2) ngroups += (key0 + g2 * 16 < it.ctx_end) ? 1 : 0;
                 const uint32_t bytes = static_cast<uint32_t>(ngroups * kHalves * 16 * 128);
-                const int row = it.h * p.block_size + ((key0 + gi * 16) % p.block_size);
-                const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048);
-                const uint32_t par = ((g / kStages) - 1) & 1;
-                // ---- K tile (lanes 0-15): its stage is free as soon as the score MMAs two tiles back are done
-                if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->k_empty[stage]), par, abort_flag, p.status);
+                const int row = it.h * p.block_size + ((key0 + gi * 16 + sub * 8) % p.block_size);
+                // the stage is free once the MMAs that read the tile `stages` tiles back are done: the score MMAs
+                // for a K tile, the PV MMAs for a V tile
+                if (round > 0) ok = wait_or_abort(smem_u32(&empty[stage]), (round - 1) & 1, abort_flag, p.status);
                 if (!__all_sync(0xffffffffu, ok)) break;
                 if (lane == 0) {
-                    NPD_TRACE(0, 1, t);
-                    mbar_expect_tx(smem_u32(&ctrl->k_full[stage]), bytes);
+                    if (k_role) NPD_TRACE(0, 1, t);
+                    mbar_expect_tx(smem_u32(&full[stage]), bytes);
                 }
                 __syncwarp();
-                if (role == 0 && gi < ngroups && hf < kHalves) {
-                    const uint32_t dst = smem_u32(k_ring + (size_t)stage * kKvTileBytes) + off;
-                    tma_load_3d(dst, tm, smem_u32(&ctrl->k_full[stage]), hf * 64, row, id.x);
-                    if (two_boxes) tma_load_3d(dst + 8 * 128, tm, smem_u32(&ctrl->k_full[stage]), hf * 64, row, id.y);
+                if (has_box && gi < ngroups)
+                    tma_load_3d(smem_u32(ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&full[stage]), hf * 64, row, id);
+                if (++stage == stages) {
+                    stage = 0;
+                    ++round;
                 }
-                if (kQueryTiles > 1 && t == 0 && !(ok = load_q(1))) break;
-                // ---- V tile (lanes 16-31): free once the PV MMAs two tiles back are done
-                if (g >= kStages) ok = wait_or_abort(smem_u32(&ctrl->v_empty[stage]), par, abort_flag, p.status);
-                if (!__all_sync(0xffffffffu, ok)) break;
-                if (lane == 0) {
-                    mbar_expect_tx(smem_u32(&ctrl->v_full[stage]), bytes);
-                }
-                __syncwarp();
-                if (role == 1 && gi < ngroups && hf < kHalves) {
-                    const uint32_t dst = smem_u32(v_ring + (size_t)stage * kKvTileBytes) + off;
-                    tma_load_3d(dst, tm, smem_u32(&ctrl->v_full[stage]), hf * 64, row, id.x);
-                    if (two_boxes) tma_load_3d(dst + 8 * 128, tm, smem_u32(&ctrl->v_full[stage]), hf * 64, row, id.y);
-                }
+                if (k_role && kQueryTiles > 1 && t == 0 && !(ok = load_q(1))) break;
             }
             ok = __all_sync(0xffffffffu, ok);
         }
@@ -544,12 +550,12 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 // the release of its K tile when it was the last one to read it.
                 auto scores = [&](int u, int buf) {
                     const int t = u / kHPT, h = u % kHPT, gt = g + t;
-                    if (h == 0 && !wait_all(&ctrl->k_full[gt % kStages], (gt / kStages) & 1)) return false;
+                    if (h == 0 && !wait_all(&ctrl->k_full[gt % kStagesK], (gt / kStagesK) & 1)) return false;
                     tc_fence_after();
                     NPD_TRACE(x == 0 ? 1 : 4, 12, u);
-                    issue_s(gt % kStages, h, buf);
+                    issue_s(gt % kStagesK, h, buf);
                     NPD_TRACE(x == 0 ? 1 : 4, 13, u);
-                    if (h == kHPT - 1 || u == U - 1) commit(&ctrl->k_empty[gt % kStages]);
+                    if (h == kHPT - 1 || u == U - 1) commit(&ctrl->k_empty[gt % kStagesK]);
                     if (u == U - 1) commit(&ctrl->q_empty[x]);       // no further score MMA of this item reads Q_X
                     return true;
                 };
@@ -561,11 +567,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     if (U > 1 && !(ok = scores(1, (c + 1) & 1))) break;
                 }
                 for (int u = 0; ok && u < U; ++u) {
-                    const int t = u / kHPT, h = u % kHPT, gt = g + t, stage = gt % kStages;
+                    const int t = u / kHPT, h = u % kHPT, gt = g + t, stage = gt % kStagesV;
                     const int cu = c + u, buf = cu & 1;
                     // O_X is overwritten by the first PV of an item: the previous epilogue must have read it
                     if (u == 0 && items_done > 0 && !(ok = wait_all(&ctrl->o_free[x], (items_done - 1) & 1))) break;
-                    if (h == 0 && !(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
+                    if (h == 0 && !(ok = wait_all(&ctrl->v_full[stage], (gt / kStagesV) & 1))) break;
                     NPD_TRACE(x == 0 ? 1 : 4, 10, u);
                     if (!(ok = wait_all(&ctrl->p_ready[x][buf], (cu >> 1) & 1))) break;
                     NPD_TRACE(x == 0 ? 1 : 4, 11, u);
@@ -578,19 +584,17 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 for (int t = my_tiles; ok && t < it.n_kv; ++t) {
                     // a key tile only the other query tile needs: observe it so that ring phases stay in step
-                    const int gt = g + t, stage = gt % kStages;
-                    if (!(ok = wait_all(&ctrl->k_full[stage], (gt / kStages) & 1))) break;
-                    commit(&ctrl->k_empty[stage]);
-                    if (!(ok = wait_all(&ctrl->v_full[stage], (gt / kStages) & 1))) break;
-                    commit(&ctrl->v_empty[stage]);
+                    const int gt = g + t;
+                    if (!(ok = wait_all(&ctrl->k_full[gt % kStagesK], (gt / kStagesK) & 1))) break;
+                    commit(&ctrl->k_empty[gt % kStagesK]);
+                    if (!(ok = wait_all(&ctrl->v_full[gt % kStagesV], (gt / kStagesV) & 1))) break;
+                    commit(&ctrl->v_empty[gt % kStagesV]);
                 }
                 g += it.n_kv;
                 c += U;
                 items_done += U > 0 ? 1 : 0;
             }
         }
-    } else if (warp >= 11) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // =========================== softmax + correction + epilogue (warps 0-7) ===========================
@@ -617,13 +621,13 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll 1
             for (int u = 0; ok && u < U; ++u) {
                 const int cu = c + u, buf = cu & 1;
-                const int t = u / kHPT, gt = g + t, stage = gt % kStages;
+                const int t = u / kHPT, gt = g + t, stage = gt % kStagesV;
                 const int key0 = u * kHalfKeys;
                 // V rows at or past ctx_end were never written (or never loaded): clear them so that P = 0
                 // there cannot meet a NaN.  Both softmax groups do it (idempotent), at the first half-step of the
                 // key tile, before they release its probabilities.
                 if (u % kHPT == 0 && t * kTK + kTK > it.ctx_end) {
-                    if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (gt / kStages) & 1, abort_flag, p.status))) break;
+                    if (!(ok = wait_or_abort(smem_u32(&ctrl->v_full[stage]), (gt / kStagesV) & 1, abort_flag, p.status))) break;
                     uint8_t *v_tile = v_ring + (size_t)stage * kKvTileBytes;
                     const int first = max(it.ctx_end - t * kTK, 0);
                     constexpr int kPieces = kHalves * 8;           // 16-byte pieces per row
@@ -842,7 +846,7 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
 
     const size_t halves = static_cast<size_t>(head_dim / 64);
     const int query_tiles = head_dim == 256 ? 1 : 2, tile_keys = head_dim == 256 ? 64 : kKeys;
-    const size_t smem = 1024 + query_tiles * halves * kQHalfBytes + 2 * (size_t)kStages * halves * tile_keys * 128 +
+    const size_t smem = 1024 + query_tiles * halves * kQHalfBytes + (size_t)(kStagesK + kStagesV) * halves * tile_keys * 128 +
                         sizeof(SmemCtrl) + 64;
     const bool f16 = dtype == NPD_DTYPE_F16;
     using Kernel = void (*)(PrefillParams, CUtensorMap, CUtensorMap, CUtensorMap);
