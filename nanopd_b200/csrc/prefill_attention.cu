@@ -7,7 +7,7 @@
 // from the pages like any other key, which the reference's prefill branch does not do
 // (nanoPD/engine/model_runner.py:125-127,152-168 attends to the current chunk only).
 //
-// Persistent grid, one CTA of 384 threads per SM; items are handed out heaviest first through an atomic
+// Persistent grid, one CTA of 512 threads per SM; items are handed out heaviest first through an atomic
 // counter.  Warp roles:
 //   warps 0-3 / 4-7  softmax of query tile A / B: thread i owns row i == TMEM lane i (no shuffles)
 //   warp  8          TMA producer of the query tiles and of the K tiles (a ring of 3 tiles in shared memory;
@@ -17,6 +17,7 @@
 //                    which ONE warp can issue tiled copies (about 100 clocks per 2 KiB box) is what bounded the
 //                    kernel when a single warp issued the 32 boxes of a 128-key step
 //   warps 9 / 10     issue the tcgen05.mma instructions of tile A / B (one elected lane)
+//   warps 12-15      epilogue of both tiles: O / l -> out, while the softmax groups are already on the next item
 // TMEM (512 columns): S_A | S_B | O_A | O_B, 128 columns each.  A query tile walks its keys in HALF-STEPS of 64
 // keys; its 128 score columns are a ring of two 64-column buffers, so the scores of half-step c+1 are
 // already in TMEM while the softmax group works on half-step c, and those of c+2 are computed while the
@@ -27,7 +28,7 @@
 //   O   += P(c).V(c)      tcgen05.mma with P as the TMEM A operand and V as the MN-major B operand; then
 //          S(c+2) is issued into the buffer P(c) has just left (MMAs execute in issue order)
 // O stays in TMEM and is rescaled only when a row maximum grows by more than 2^8 (after waiting for the
-// PV products issued so far), then read once in the epilogue.
+// PV products issued so far), then read once by the epilogue warps.
 // Completion of MMAs is tracked with tcgen05.commit on mbarriers; every wait is bounded and an
 // abort flag lets all roles leave together, after which TMEM is released.
 //
@@ -47,7 +48,8 @@ constexpr int kSchedSlots = 4;     // work items the producer may publish ahead 
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
 constexpr int kKeys = 128;         // keys per K/V tile in shared memory (64 at head_dim 256)
 constexpr int kHalfKeys = 64;      // keys per half-step (UMMA N of a score MMA, K extent of a PV MMA batch)
-constexpr int kThreads = 384;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA (Q, K), 9 MMA for A, 10 MMA for B, 11 TMA (V)
+constexpr int kThreads = 512;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA (Q, K), 9 MMA for A, 10 MMA for B, 11 TMA (V),
+                                   // 12-15 epilogue
 constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
 // head_dim kD = 64 * kHalves (64, 128 or 256): a tile is kHalves slabs, each 64 elements wide.  At head_dim 256 an
 // item is ONE query tile (two tiles' accumulators, 2 x 256 columns, would not fit the 512 TMEM columns beside the
@@ -175,9 +177,10 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
-// One 256-bit store (sm_100: st.global.v8.b32); the address must be 32-byte aligned.
+// One 256-bit store (sm_100: st.global.v8.b32); the address must be 32-byte aligned.  The output is written once
+// and not read again by this kernel: no L1 allocation (+0.9 % on configuration 3).
 __device__ __forceinline__ void st_global_32B(void *ptr, const uint32_t (&w)[8]) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+    asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
                  "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
                  : "memory");
 }
@@ -281,6 +284,8 @@ struct alignas(8) SmemCtrl {
                             // barriers, because a waiter may find either one or two products still in flight and a
                             // parity wait cannot tell "two behind" from "done"
     uint64_t o_free[2];     // [query tile]: the epilogue has taken O out of TMEM (128 arrivals)
+    uint64_t epi_ready[2];  // [query tile]: the softmax group has finished the item and left its row sums (128 arrivals)
+    float l_sum[2][kRows];  // [query tile][row]: the row sums of the finished item, for the epilogue warps
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -374,6 +379,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             mbar_init(smem_u32(&ctrl->pv_done[x][0]), 1);
             mbar_init(smem_u32(&ctrl->pv_done[x][1]), 1);
             mbar_init(smem_u32(&ctrl->o_free[x]), 128);
+            mbar_init(smem_u32(&ctrl->epi_ready[x]), 128);
         }
         ctrl->abort_flag = 0;
         mbar_fence_init();
@@ -388,8 +394,9 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     const uint32_t tmem = ctrl->tmem_base;
     volatile int *abort_flag = &ctrl->abort_flag;
 
-    // Register re-allocation between warpgroups (first statement of every role): the two softmax groups
-    // work on whole score rows in registers, the third group (two TMA warps, two MMA warps) needs few.
+    // Register re-allocation between warpgroups (first statement of every role).  512 threads start with 128
+    // registers each: the two softmax groups, which work on whole score rows in registers, go up to 168; the third
+    // group (two TMA warps, two MMA warps) gives up 56 per thread and the epilogue group 24 — 65 536 in all.
     if (warp == 8 || warp == 11) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         // =========================== TMA producers: warp 8 (query tiles, K tiles), warp 11 (V tiles) ===========================
@@ -613,9 +620,75 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 items_done += U > 0 ? 1 : 0;
             }
         }
+    } else if (warp >= 12) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        // =========================== epilogue (warps 12-15): O / l -> out, for both query tiles ===========================
+        // Warp 12 + w reads TMEM lane quarter w, as softmax warps w and 4 + w do.  The softmax group of a tile hands an
+        // item over as soon as it has released the last half-step's probabilities (its row sums go through shared
+        // memory) and starts on the next item; these warps wait for the item's last PV product, take O out of TMEM —
+        // only then may the next item's first PV product overwrite it — and write the normalised rows.  The stores of
+        // a tile (32 KiB as 32-byte pieces) take the SM 2-3 thousand clocks, which were 7 % of configuration 3 while
+        // the softmax warps did them.
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;                          // == TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+        const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
+        int c[2] = {0, 0};                                       // per query tile: half-steps so far (phases of pv_done)
+        int items_done[2] = {0, 0};                              // per query tile: items handed over so far
+        bool ok = true;
+        for (int k = 0; ok; ++k) {
+            const int item = next_item(k, ok);
+            if (!ok || item < 0) break;
+            const Item it = decode_item(p, item);
+#pragma unroll
+            for (int x = 0; x < kQueryTiles; ++x) {
+                const int U = it.nhalf[x];
+                if (U == 0 || !ok) continue;
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->epi_ready[x]), items_done[x] & 1, abort_flag, p.status))) continue;
+                const float inv = 1.f / ctrl->l_sum[x][row];
+                // the item's last PV product (products complete in order, so all of them)
+                const int last = c[x] + U - 1;
+                if (!(ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][last & 1]), (last >> 1) & 1, abort_flag, p.status))) continue;
+                tc_fence_after();
+                const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
+                const bool store = tq_idx < it.tq_valid[x] && row < p.tq * p.group;
+                T *dst = static_cast<T *>(p.out) +
+                         ((long long)(it.qoff + it.tok0[x] + tq_idx) * p.num_q_heads + (long long)it.h * p.group + hg) * kD;
+                // the accumulator row in groups of 64 columns: both loads of a group in flight, one wait
+                constexpr int kChunks = kD / 32, kGroup = kChunks < 2 ? kChunks : 2;
+#pragma unroll
+                for (int c0 = 0; c0 < kChunks; c0 += kGroup) {
+                    float o[kGroup][32];
+#pragma unroll
+                    for (int cc = 0; cc < kGroup; ++cc) tmem_ld32(t_o + (c0 + cc) * 32, o[cc]);
+                    tmem_wait_ld();
+                    if (c0 + kGroup == kChunks) {
+                        // O is in registers: the next item's first PV may overwrite the accumulator
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&ctrl->o_free[x]));
+                    }
+                    if (store) {
+                        // 32 bytes per lane and instruction: a lane's row is contiguous and the lanes of a warp are a
+                        // row apart, so every store instruction fills whole 32-byte sectors
+#pragma unroll
+                        for (int cc = 0; cc < kGroup; ++cc)
+#pragma unroll
+                            for (int i = 0; i < 32; i += 16) {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    w[j] = Elem<T>::pack2(o[cc][i + 2 * j] * inv, o[cc][i + 2 * j + 1] * inv);
+                                st_global_32B(dst + (c0 + cc) * 32 + i, w);
+                            }
+                    }
+                }
+                c[x] += U;
+                ++items_done[x];
+            }
+        }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-        // =========================== softmax + correction + epilogue (warps 0-7) ===========================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+        // =========================== softmax + correction (warps 0-7) ===========================
         const int x = warp >> 2;                                 // query tile A or B
         const int wq = warp & 3;                                 // TMEM lane quarter this warp may touch
         const int row = wq * 32 + lane;                          // == TMEM lane
@@ -743,48 +816,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (lane == 0) NPD_TRACE(sm_role, 25, u);
             }
 
-            // ---- epilogue: O / l -> out ----
+            // ---- hand the item over to the epilogue warps: the row sums, then the arrival ----
             if (ok && U > 0) {
-                // the item's last PV product (products complete in order, so all of them)
                 if (lane == 0) NPD_TRACE(sm_role, 30, k);
-                const int last = c + U - 1;
-                ok = wait_or_abort(smem_u32(&ctrl->pv_done[x][last & 1]), (last >> 1) & 1, abort_flag, p.status);
-                if (lane == 0) NPD_TRACE(sm_role, 31, k);
-                if (ok) {
-                    tc_fence_after();
-                    const bool store = tq_idx < it.tq_valid[x] && row < p.tq * p.group;
-                    const float inv = 1.f / l_run;
-                    T *dst = static_cast<T *>(p.out) +
-                             ((long long)(it.qoff + it.tok0[x] + tq_idx) * p.num_q_heads + (long long)it.h * p.group + hg) * kD;
-                    // the accumulator row in groups of up to 128 columns: all loads of a group in flight, one wait
-                    constexpr int kChunks = kD / 32, kGroup = kChunks < 4 ? kChunks : 4;
-#pragma unroll
-                    for (int c0 = 0; c0 < kChunks; c0 += kGroup) {
-                        float o[kGroup][32];
-#pragma unroll
-                        for (int cc = 0; cc < kGroup; ++cc) tmem_ld32(t_o + (c0 + cc) * 32, o[cc]);
-                        tmem_wait_ld();
-                        if (c0 + kGroup == kChunks) {
-                            // O is in registers: the next item's first PV may overwrite the accumulator
-                            tc_fence_before();
-                            mbar_arrive(smem_u32(&ctrl->o_free[x]));
-                        }
-                        if (store) {
-                            // 32 bytes per lane and instruction: a lane's row is contiguous and the lanes of a warp are a
-                            // row apart, so every store instruction fills whole 32-byte sectors
-#pragma unroll
-                            for (int cc = 0; cc < kGroup; ++cc)
-#pragma unroll
-                                for (int i = 0; i < 32; i += 16) {
-                                    uint32_t w[8];
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j)
-                                        w[j] = Elem<T>::pack2(o[cc][i + 2 * j] * inv, o[cc][i + 2 * j + 1] * inv);
-                                    st_global_32B(dst + (c0 + cc) * 32 + i, w);
-                                }
-                        }
-                    }
-                }
+                ctrl->l_sum[x][row] = l_run;
+                mbar_arrive(smem_u32(&ctrl->epi_ready[x]));
             }
             if (lane == 0) NPD_TRACE(sm_role, 32, k);
             g += it.n_kv;
