@@ -33,7 +33,8 @@
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 256;                   // threads that examine the slices (8 warps); one more warp issues the copies
+constexpr int kBlockThreads = kThreads + 32;
 constexpr int kLoads = 8;                       // 16-byte pieces per thread and slice: 64 (16-bit) or 32 (fp32) logits
 constexpr int kSliceBytes = kThreads * kLoads * 16;
 constexpr int kStages = 3;                      // ring of slices in shared memory; two CTAs of 96 KiB fit an SM
@@ -61,6 +62,9 @@ struct SampleParams {
     int top_k;
     int64_t items;          // rows of this launch x slices, dealt to the CTAs in equal consecutive runs
 };
+
+// Barrier among the kThreads examining threads (the copy warp takes no part in it).
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
 // (value, id) order: larger value first, equal values by the lower id.  Bitwise on purpose: no branches in the
 // counting loops.
@@ -222,7 +226,7 @@ __device__ __noinline__ float first_bound(Scratch &sh, const uint8_t *stage, con
     const int groups = kThreads >> group_shift;
     for (int o = 1; o < (1 << group_shift); o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((tid & ((1 << group_shift) - 1)) == 0) sh.group_max[tid >> group_shift] = m;
-    __syncthreads();
+    consumer_sync();
     if (tid < groups) {
         const float mine = sh.group_max[tid];
         int rank = 0;
@@ -234,7 +238,7 @@ __device__ __noinline__ float first_bound(Scratch &sh, const uint8_t *stage, con
         }
         if (rank == k - 1) sh.bound = mine;
     }
-    __syncthreads();
+    consumer_sync();
     return sh.bound;
 }
 
@@ -282,7 +286,7 @@ __device__ __noinline__ int arg_max_rounds(Scratch &sh, const uint8_t *stage, co
             sh.warp_value[tid >> 5] = wv;
             sh.warp_id[tid >> 5] = wi;
         }
-        __syncthreads();
+        consumer_sync();
         wv = sh.warp_value[0];
         wi = sh.warp_id[0];
 #pragma unroll
@@ -300,7 +304,7 @@ __device__ __noinline__ int arg_max_rounds(Scratch &sh, const uint8_t *stage, co
             }
             ++count;
         }
-        __syncthreads();
+        consumer_sync();
     }
     return count;
 }
@@ -323,7 +327,7 @@ __device__ __noinline__ void rank_pool(Scratch &sh, int count, int n_top, int si
             sh.top_id[side ^ 1][rank] = mi;
         }
     }
-    __syncthreads();
+    consumer_sync();
 }
 
 // The k best of a whole row are in side `side`: probabilities (softmax over the k values, rounded to the logits'
@@ -379,9 +383,9 @@ __device__ __noinline__ bool hand_over_part(Scratch &sh, float *row_value, int32
         row_id[slot * k + r] = r < n_top ? sh.top_id[side][r] : -1;
     }
     __threadfence();
-    __syncthreads();
+    consumer_sync();
     if (tid == 0) sh.is_last = atomicAdd(ticket, 1u) == static_cast<uint32_t>(parts - 1);
-    __syncthreads();
+    consumer_sync();
     if (!sh.is_last) return false;
     __threadfence();
     const int total = parts * k;                    // at most kSliceCandidates: the pool is idle here
@@ -390,18 +394,20 @@ __device__ __noinline__ bool hand_over_part(Scratch &sh, float *row_value, int32
         sh.pool_id[i] = __ldcg(row_id + i);
     }
     if (tid == 0) *ticket = 0;                      // every part has arrived: ready for the next launch
-    __syncthreads();
+    consumer_sync();
     rank_pool(sh, total, 0, side, k);
     return true;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleParams p) {
+__global__ void __launch_bounds__(kBlockThreads, 2) top_k_sample_kernel(const SampleParams p) {
     using L = Logit<T>;
     constexpr int kVec = 16 / sizeof(T);
     constexpr int kSlice = kThreads * kLoads * kVec;
     extern __shared__ __align__(128) uint8_t ring[];        // kStages slices
-    __shared__ uint64_t full[kStages];
+    __shared__ uint64_t full[kStages];                      // the slice of a stage has landed
+    __shared__ uint64_t empty[kStages];                     // every examining thread is done with the stage
+    __shared__ int copies_lost;                             // the copy warp gave up waiting for a stage
     __shared__ Scratch sh;
 
     const int tid = threadIdx.x;
@@ -413,11 +419,14 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     const float replacement = L::round(1e4f);
     if (tid < 2) sh.gathered[tid] = 0;
 
-    // The ring: thread 0 starts the copy of this CTA's t-th slice into stage t % kStages and, once the slice in a
-    // stage has been examined, of the slice kStages further on — across the ends of rows, so the copies never stop
-    // while the CTA has work.  Every wait is bounded: a thread that gives up stops waiting, examines whatever the
-    // stage holds (all accesses stay inside the ring and the rows) and the launch reports NPD_STATUS_WAIT_TIMEOUT;
-    // thread 0 then gives the copies it started a last bounded chance to land.
+    // The ring: the copy warp (the last warp of the CTA, one lane) starts the copy of this CTA's t-th slice into
+    // stage t % kStages as soon as the slice that was there has been examined — across the ends of rows, so the
+    // copies never stop while the CTA has work.  A warp of its own, because fence + expect + issue take a thread
+    // ≈850 clocks per slice: done by thread 0 of the examining threads, that chain stood between every two slices
+    // of the whole CTA (all wait for thread 0 at the next barrier) and made a slice cost ≈2000 clocks, of which the
+    // data was waited for during 400.  Every wait is bounded: a thread that gives up stops waiting, examines
+    // whatever the stage holds (all accesses stay inside the ring and the rows) and the launch reports
+    // NPD_STATUS_WAIT_TIMEOUT; the copy warp then gives the copies it started a last bounded chance to land.
     const int64_t row_bytes = static_cast<int64_t>(p.vocab) * sizeof(T);
     int64_t copy_row = item_begin / p.slices;           // thread 0: the slice the next copy brings in
     int copy_slice = static_cast<int>(item_begin - copy_row * p.slices);
@@ -442,12 +451,40 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
     auto owner_of = [&](int64_t i) { return ((i + 1) * grid - 1) / p.items; };
 
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) npd::mbar_init(npd::smem_u32(&full[i]), 1);
+        for (int i = 0; i < kStages; ++i) {
+            npd::mbar_init(npd::smem_u32(&full[i]), 1);
+            npd::mbar_init(npd::smem_u32(&empty[i]), 1);
+        }
+        copies_lost = 0;
         npd::mbar_fence_init();
-        npd::fence_proxy_async_smem();
-        for (int t = 0; t < kStages && t < n_items; ++t) start_copy(t);
     }
-    __syncthreads();
+    __syncthreads();                                    // all kBlockThreads: the only barrier the copy warp takes part in
+    if (tid >= kThreads) {
+        // ---- the copy warp ----
+        if (tid == kThreads) {
+            npd::fence_proxy_async_smem();
+            bool gave_up = false;
+            int t = 0;
+            for (; t < n_items && !gave_up; ++t) {
+                if (t >= kStages) {
+                    if (!npd::mbar_wait_bounded(npd::smem_u32(&empty[t % kStages]), ((t / kStages) - 1) & 1, kWaitLimit)) {
+                        gave_up = true;
+                        break;
+                    }
+                    npd::fence_proxy_async_smem();
+                }
+                start_copy(t);
+            }
+            if (gave_up) {
+                *reinterpret_cast<volatile int *>(&copies_lost) = 1;
+                if (p.status) atomicOr(p.status, NPD_STATUS_WAIT_TIMEOUT);
+            }
+            // the copies in flight write into this CTA's shared memory: they must have landed before it is given up
+            for (int u = (t > kStages ? t - kStages : 0); u < t; ++u)
+                npd::mbar_wait_bounded(npd::smem_u32(&full[u % kStages]), (u / kStages) & 1, kWaitLimit);
+        }
+        return;
+    }
 
     // This CTA's run of slices may start and end inside a row; a stretch of one row is a "part".  The part's k best
     // so far live in side `side` of the scratch, best first; n_top of them, and `tau` is the k-th.  A later slice of
@@ -470,7 +507,9 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
         const uint8_t *stage = ring + (t % kStages) * kSliceBytes;
         const T *logits = all_logits + row * p.row_stride;
         const int base = s * kSlice;
-        if (!lost && !npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit)) lost = true;
+        if (!lost && (*reinterpret_cast<volatile int *>(&copies_lost) ||
+                      !npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit)))
+            lost = true;
 
         float limit = tau;
         if (first) {
@@ -515,16 +554,13 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
                 }
             }
         }
-        __syncthreads();
+        consumer_sync();
         int count = sh.gathered[bank];
         if (count > kSliceCandidates)
             count = arg_max_rounds<T>(sh, stage, logits, p.vocab, base, k, pooled, replacement);
         pooled = count;
-        // Every read of the stage lies before a barrier all threads have passed: the stage can be refilled.
-        if (tid == 0 && !lost && t + kStages < n_items) {
-            npd::fence_proxy_async_smem();
-            start_copy(t + kStages);
-        }
+        // Every read of the stage lies before a barrier all examining threads have passed: the stage can be refilled.
+        if (tid == 0) npd::mbar_arrive(npd::smem_u32(&empty[t % kStages]));
 
         if (count > 0 && (first || count >= (k > 8 ? k : 8) || last)) {
             if (tid == 0) sh.gathered[bank ^ 1] = 0;    // last read before the previous ranking's closing barrier
@@ -550,12 +586,7 @@ __global__ void __launch_bounds__(kThreads, 2) top_k_sample_kernel(const SampleP
             if (whole) draw_row<T>(sh, side, k, p.uniforms ? p.uniforms + p.first_row + row : nullptr, p.out + p.first_row + row);
         }
     }
-    if (lost) {
-        if (p.status) atomicOr(p.status, NPD_STATUS_WAIT_TIMEOUT);
-        if (tid == 0)
-            for (int t = 0; t < n_items; ++t)
-                npd::mbar_wait_bounded(npd::smem_u32(&full[t % kStages]), (t / kStages) & 1, kWaitLimit);
-    }
+    if (lost && p.status) atomicOr(p.status, NPD_STATUS_WAIT_TIMEOUT);
 }
 
 int slices_of(int64_t vocab, int slice) { return static_cast<int>((vocab + slice - 1) / slice); }
@@ -619,7 +650,7 @@ cudaError_t launch(const SampleParams &p, unsigned grid, cudaStream_t stream) {
     e = cudaFuncSetAttribute(top_k_sample_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
-    top_k_sample_kernel<T><<<grid, kThreads, kRingBytes, stream>>>(p);
+    top_k_sample_kernel<T><<<grid, kBlockThreads, kRingBytes, stream>>>(p);
     return cudaGetLastError();
 }
 
