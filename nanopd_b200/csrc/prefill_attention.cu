@@ -697,6 +697,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         const int tq_idx = row / p.group, hg = row - tq_idx * p.group;
         int g = 0, c = 0;                                     // key tiles / own half-steps so far (barrier phases)
+        int items_handed = 0;                                 // items handed to the epilogue warps so far
         const int sm_role = wq == 0 ? 2 + x : 5 + x * 3 + (wq - 1);   // trace slot (used only by tracing builds)
         (void)sm_role;
         NPD_TRACE_DECL
@@ -819,8 +820,15 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             // ---- hand the item over to the epilogue warps: the row sums, then the arrival ----
             if (ok && U > 0) {
                 if (lane == 0) NPD_TRACE(sm_role, 30, k);
+                // The epilogue warps must have taken the previous item's row sums (they arrive on o_free after
+                // reading them).  An item of two or more half-steps cannot get here before that — its first PV
+                // product waits for o_free — but an item of a single half-step can; the wait also keeps
+                // epi_ready at most one phase ahead of its waiters.
+                if (items_handed > 0 &&
+                    !(ok = wait_or_abort(smem_u32(&ctrl->o_free[x]), (items_handed - 1) & 1, abort_flag, p.status))) break;
                 ctrl->l_sum[x][row] = l_run;
                 mbar_arrive(smem_u32(&ctrl->epi_ready[x]));
+                ++items_handed;
             }
             if (lane == 0) NPD_TRACE(sm_role, 32, k);
             g += it.n_kv;

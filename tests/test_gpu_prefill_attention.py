@@ -118,6 +118,43 @@ def test_several_chunks_in_one_call(kernels):
         assert (got[offsets[i]:offsets[i] + n] - want).abs().max().item() <= TOL[torch.bfloat16]
 
 
+def test_many_items_of_a_single_half_step(kernels):
+    """64 short prompts (33-64 tokens, so every work item is ONE 64-key half-step per query tile) in one launch,
+    a few items per SM in a row: a softmax group then finishes its next item before the epilogue warps have
+    written the one before, the case its hand-over has to wait for."""
+    D, B, Hq, Hkv = 128, 16, 32, 8
+    scale = D ** -0.5
+    lens = [33 + (7 * i) % 32 for i in range(64)]
+    prompts = [build_prompt(L, Hq, Hkv, D, B, torch.bfloat16, seed=100 + i, extra_blocks=1) for i, L in enumerate(lens)]
+    base, tables, kcs, vcs = 0, [], [], []
+    for (_, table, kc, vc) in prompts:
+        tables.append(table + base)
+        kcs.append(kc)
+        vcs.append(vc)
+        base += kc.size(0)
+    kc, vc = torch.cat(kcs), torch.cat(vcs)
+    max_blk = max(t.numel() for t in tables)
+    bt = torch.zeros(len(lens), max_blk, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :t.numel()] = t
+    q_rows = torch.cat([p[0] for p in prompts])
+    offsets, off = [], 0
+    for L in lens:
+        offsets.append(off)
+        off += L
+    starts = [0] * len(lens)
+    for _ in range(3):      # the hand-over depends on timing: more than one launch
+        got = run_chunks(kernels, q_rows.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), offsets, lens, starts, scale, B)
+    assert kernels.check_status(DEV, raise_on_error=False) == 0
+    got = got.float().cpu()
+    for i, L in enumerate(lens):
+        want = paged_oracle.paged_prefill_attention(q_rows[offsets[i]:offsets[i] + L], kc, vc, tables[i], 0, scale)
+        # rows that see only a few keys are as large as the values themselves (|x| up to 4, where one bf16 rounding
+        # step is 0.016): the absolute tolerance of the other tests plus half a rounding step of the result
+        err = (got[offsets[i]:offsets[i] + L] - want).abs()
+        assert (err <= TOL[torch.bfloat16] + want.abs() * 2.0 ** -8).all(), err.max().item()
+
+
 def test_store_then_prefill_chunks_compose(kernels):
     """The caller's order on the GPU: store each 128-token chunk, then attend; the rows of all chunks
     together equal full causal attention over the prompt."""
