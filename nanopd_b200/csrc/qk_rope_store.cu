@@ -14,8 +14,9 @@
 //   rotate_half(y) = concat(-y[D/2:], y[:D/2]),   T(.) = round to the tensor's 16-bit type.
 // A (token, head) row is D/8 lanes of 16 bytes; the two elements a rotation pairs sit at the same place
 // of two lanes half a row apart (one shuffle), the mean of squares is a reduction over the row's lanes,
-// every warp keeps two passes of rows in flight, and the products and sums that the reference rounds to
-// 16 bits are packed 16-bit instructions.  HBM-bound, launch-latency bound at decode sizes.
+// a warp works through eight passes of rows of one token with all their loads in flight, and the products and
+// sums that the reference rounds to 16 bits are packed 16-bit instructions.  HBM-bound, launch-latency bound at
+// decode sizes.
 #include "npd_common.cuh"
 
 namespace {
@@ -82,85 +83,95 @@ __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
 
 // A row of D elements is D/8 pieces of 16 bytes, one per lane: LPR = D/8 lanes per row, 32/LPR rows per warp pass,
 // the lower LPR/2 lanes of a row hold its first half and the upper ones the second half, so the element a rotation
-// pairs with sits at the same place of lane ^ (LPR/2).  Two passes are kept in flight (loads of both first).
+// pairs with sits at the same place of lane ^ (LPR/2).
+// A warp takes a UNIT at a time: kPasses consecutive passes over the rows of ONE token (16 rows at head_dim 128; a
+// token of the Qwen3-8B shape, 32 q + 8 k + 8 v rows, is three units).  What the rows of a token share is then
+// fetched once per unit instead of once per row: the lane's piece of the token's cos and sin rows (which were two
+// of every three load instructions), the position and the page lookup.  All row loads of a unit are issued before
+// the first is used.
 template <typename T, int D>
 __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStoreParams p) {
     constexpr int LPR = D / 8;                 // lanes per row
     constexpr int RPW = 32 / LPR;              // rows per warp pass
-    constexpr int UNROLL = 2;
+    constexpr int kPasses = 8;                 // passes per unit
+    constexpr int kChunk = RPW * kPasses;      // rows per unit
     const int lane = threadIdx.x & 31;
     const int sub = lane % LPR, row_in_pass = lane / LPR;
     const bool upper = sub >= LPR / 2;
-    const unsigned rows_per_token = static_cast<unsigned>(p.num_q_heads + 2 * p.num_kv_heads);
-    const unsigned total = static_cast<unsigned>(p.num_tokens) * rows_per_token;      // < 2^31, checked by the host
+    const int rows_per_token = p.num_q_heads + 2 * p.num_kv_heads;
+    const unsigned units_per_token = static_cast<unsigned>((rows_per_token + kChunk - 1) / kChunk);
+    const unsigned total = static_cast<unsigned>(p.num_tokens) * units_per_token;      // < 2^31, checked by the host
     const unsigned warps = gridDim.x * (blockDim.x >> 5);
     const unsigned w0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint32_t sign = upper ? 0u : 0x80008000u;            // rotate_half: (-second half, first half)
-    for (unsigned base = w0 * (RPW * UNROLL); base < total; base += warps * (RPW * UNROLL)) {
-        uint4 raw[UNROLL], craw[UNROLL], sraw[UNROLL];
-        T *dst[UNROLL];
-        int kind[UNROLL];
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    // the norm weights are the same for every row of a kind
+    const uint4 q_wv = p.q_w ? __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.q_w) + sub * 8)) : zero4;
+    const uint4 k_wv = p.k_w ? __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.k_w) + sub * 8)) : zero4;
+    for (unsigned unit = w0; unit < total; unit += warps) {
+        const unsigned t32 = unit / units_per_token;
+        const int row0 = static_cast<int>(unit - t32 * units_per_token) * kChunk;
+        const int row_end = min(row0 + kChunk, rows_per_token);
+        const long long t = t32;
+        // ---- what the unit's rows share ----
+        uint4 c = zero4, sn = zero4;
+        if (row0 < p.num_q_heads + p.num_kv_heads) {           // it has q or k rows
+            c = __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.cos) + t * p.cs_row_stride + sub * 8));
+            sn = __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.sin) + t * p.cs_row_stride + sub * 8));
+        }
+        long long slot = -1;                                    // element offset of (head 0, this position) in the page
+        if (row_end > p.num_q_heads) {                          // it has k or v rows: their page slot
+            const int pos = __ldg(p.positions + t);
+            const int blk_idx = pos / p.block_size;
+            const int off = pos - blk_idx * p.block_size;
+            if (pos < 0 || blk_idx >= p.max_blocks_per_seq) {
+                if (p.status && lane == 0) atomicOr(p.status, NPD_STATUS_BAD_POSITION);
+            } else {
+                const int phys = __ldg(p.block_tables + t * p.bt_row_stride + blk_idx);
+                if (phys < 0 || phys >= p.num_blocks) {
+                    if (p.status && lane == 0) atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
+                } else {
+                    slot = phys * p.cache_block_stride + (long long)off * D;
+                }
+            }
+        }
+        // ---- the rows: all loads first ----
+        uint4 raw[kPasses];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const unsigned w = base + u * RPW + row_in_pass;
-            dst[u] = nullptr;
-            kind[u] = 2;
-            raw[u] = craw[u] = sraw[u] = make_uint4(0, 0, 0, 0);
-            if (w >= total) continue;
-            const unsigned t32 = w / rows_per_token;
-            const int r = static_cast<int>(w - t32 * rows_per_token);
-            const long long t = t32;
+        for (int u = 0; u < kPasses; ++u) {
+            const int r = row0 + u * RPW + row_in_pass;
+            raw[u] = zero4;
+            if (r >= row_end) continue;
             const int kd = r < p.num_q_heads ? 0 : (r < p.num_q_heads + p.num_kv_heads ? 1 : 2);   // q, k, v
             const int h = kd == 0 ? r : (kd == 1 ? r - p.num_q_heads : r - p.num_q_heads - p.num_kv_heads);
-            kind[u] = kd;
             const T *src = kd == 0 ? static_cast<const T *>(p.q) + t * p.q_token_stride
                          : kd == 1 ? static_cast<const T *>(p.k) + t * p.k_token_stride
                                    : static_cast<const T *>(p.v) + t * p.v_token_stride;
             // a plain (coherent) load: q_out may alias q, and a non-coherent load of memory the same kernel writes
             // is undefined
             raw[u] = *reinterpret_cast<const uint4 *>(src + (long long)h * D + sub * 8);
-            if (kd != 2) {
-                craw[u] = __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.cos) + t * p.cs_row_stride + sub * 8));
-                sraw[u] = __ldg(reinterpret_cast<const uint4 *>(static_cast<const T *>(p.sin) + t * p.cs_row_stride + sub * 8));
-            }
-            if (kd == 0) {
-                dst[u] = static_cast<T *>(p.q_out) + t * p.q_out_token_stride + (long long)h * D + sub * 8;
-            } else {
-                // destination of a k or v row: its page slot
-                const int pos = __ldg(p.positions + t);
-                const int blk_idx = pos / p.block_size;
-                const int off = pos - blk_idx * p.block_size;
-                if (pos < 0 || blk_idx >= p.max_blocks_per_seq) {
-                    if (p.status && sub == 0) atomicOr(p.status, NPD_STATUS_BAD_POSITION);
-                    continue;
-                }
-                const int phys = __ldg(p.block_tables + t * p.bt_row_stride + blk_idx);
-                if (phys < 0 || phys >= p.num_blocks) {
-                    if (p.status && sub == 0) atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
-                    continue;
-                }
-                dst[u] = static_cast<T *>(kd == 1 ? p.k_cache : p.v_cache) + phys * p.cache_block_stride +
-                         ((long long)h * p.block_size + off) * D + sub * 8;
-            }
         }
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
+        for (int u = 0; u < kPasses; ++u) {
             // every lane takes part in the shuffles; rows without work carry zeros
+            const int r = row0 + u * RPW + row_in_pass;
+            const int kd = r >= row_end ? 3 : (r < p.num_q_heads ? 0 : (r < p.num_q_heads + p.num_kv_heads ? 1 : 2));
+            const int h = kd == 0 ? r : (kd == 1 ? r - p.num_q_heads : r - p.num_q_heads - p.num_kv_heads);
             float x[8];
             unpack8<T>(raw[u], x);
-            const T *wgt = static_cast<const T *>(kind[u] == 0 ? p.q_w : (kind[u] == 1 ? p.k_w : nullptr));
+            const bool normed = (kd == 0 && p.q_w != nullptr) || (kd == 1 && p.k_w != nullptr);
             float ss = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
 #pragma unroll
-            for (int s = LPR / 2; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+            for (int s2 = LPR / 2; s2 > 0; s2 >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s2);
             uint4 mine = raw[u];
-            if (wgt != nullptr) {
+            if (normed) {
                 const float inv = rsqrtf(ss * (1.f / D) + p.eps);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) x[i] *= inv;
                 const uint4 y = pack8<T>(x);                       // rounded to T, as the norm module does
-                const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(wgt + sub * 8));
+                const uint4 wv = kd == 0 ? q_wv : k_wv;
                 mine = make_uint4(mul2<T>(wv.x, y.x), mul2<T>(wv.y, y.y), mul2<T>(wv.z, y.z), mul2<T>(wv.w, y.w));
             }
             // the partner half of the row, as the 16-bit values the rotation reads
@@ -169,24 +180,28 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStore
             other.y = __shfl_xor_sync(0xffffffffu, mine.y, LPR / 2);
             other.z = __shfl_xor_sync(0xffffffffu, mine.z, LPR / 2);
             other.w = __shfl_xor_sync(0xffffffffu, mine.w, LPR / 2);
-            if (kind[u] != 2) {
-                const uint4 c = craw[u], sn = sraw[u];
+            if (kd < 2) {
                 mine.x = add2<T>(mul2<T>(mine.x, c.x), mul2<T>(other.x ^ sign, sn.x));
                 mine.y = add2<T>(mul2<T>(mine.y, c.y), mul2<T>(other.y ^ sign, sn.y));
                 mine.z = add2<T>(mul2<T>(mine.z, c.z), mul2<T>(other.z ^ sign, sn.z));
                 mine.w = add2<T>(mul2<T>(mine.w, c.w), mul2<T>(other.w ^ sign, sn.w));
             }
-            if (dst[u] != nullptr) *reinterpret_cast<uint4 *>(dst[u]) = mine;
+            if (kd == 0) {
+                *reinterpret_cast<uint4 *>(static_cast<T *>(p.q_out) + t * p.q_out_token_stride + (long long)h * D + sub * 8) = mine;
+            } else if (kd < 3 && slot >= 0) {
+                *reinterpret_cast<uint4 *>(static_cast<T *>(kd == 1 ? p.k_cache : p.v_cache) + slot +
+                                           (long long)h * p.block_size * D + sub * 8) = mine;
+            }
         }
     }
 }
 
 template <typename T>
 int launch(const RopeStoreParams &p, int head_dim, int device, cudaStream_t stream) {
-    const long long total = p.num_tokens * (p.num_q_heads + 2 * p.num_kv_heads);
+    const int rows_per_unit = (32 / (head_dim / 8)) * 8;                       // rows per warp pass x passes per unit
+    const long long units = p.num_tokens * ((p.num_q_heads + 2 * p.num_kv_heads + rows_per_unit - 1) / rows_per_unit);
     const int threads = 256;
-    const long long rows_per_block = 8LL * (32 / (head_dim / 8)) * 2;      // warps x rows per pass x passes in flight
-    long long blocks = (total + rows_per_block - 1) / rows_per_block;
+    long long blocks = (units + 7) / 8;                                        // one unit per warp
     const long long cap = (long long)npd::sm_count(device) * 8;
     if (blocks > cap) blocks = cap;
     switch (head_dim) {
