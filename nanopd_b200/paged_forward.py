@@ -124,7 +124,7 @@ def build_step_context(ctx: Dict, device, block_size: int = 16) -> StepContext:
 # one CTA per SM.  Run one after the other, each leaves the other's resource idle.  In a mixed step they are
 # launched side by side instead, each capped to its share of the SMs; the split minimises the longer of the two
 # estimated times.
-_PREFILL_FLOPS_PER_S = 0.95e15     # measured rates of the two kernels on a B200, only used for the split
+_PREFILL_FLOPS_PER_S = 1.1e15      # measured rates of the two kernels on a B200, only used for the split
 _DECODE_BYTES_PER_S = 6.0e12
 _MIN_OVERLAP_SECONDS = 15e-6       # below this much estimated work on either side, fork and join cost more than they save
 _side_streams: Dict[int, "torch.cuda.Stream"] = {}
