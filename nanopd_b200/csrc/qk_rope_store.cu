@@ -84,16 +84,25 @@ __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
 // A row of D elements is D/8 pieces of 16 bytes, one per lane: LPR = D/8 lanes per row, 32/LPR rows per warp pass,
 // the lower LPR/2 lanes of a row hold its first half and the upper ones the second half, so the element a rotation
 // pairs with sits at the same place of lane ^ (LPR/2).
-// A warp takes a UNIT at a time: kPasses consecutive passes over the rows of ONE token (16 rows at head_dim 128; a
-// token of the Qwen3-8B shape, 32 q + 8 k + 8 v rows, is three units).  What the rows of a token share is then
+// A warp takes a UNIT at a time: kPasses consecutive passes over the rows of ONE token (8 rows at head_dim 128; a
+// token of the Qwen3-8B shape, 32 q + 8 k + 8 v rows, is six units).  What the rows of a token share is then
 // fetched once per unit instead of once per row: the lane's piece of the token's cos and sin rows (which were two
 // of every three load instructions), the position and the page lookup.  All row loads of a unit are issued before
 // the first is used.
+// Four passes per unit and at least four CTAs of 256 threads per SM (64 registers): 42 us for 8192 tokens of the
+// Qwen3-8B shape; eight passes per unit at the 80-95 registers the compiler then takes (two or three CTAs per SM)
+// 47-55 us, eight passes squeezed into 64 registers 43 us, six CTAs per SM (40 registers, spills) 54 us.
+#ifndef NPD_ROPE_PASSES
+#define NPD_ROPE_PASSES 4
+#endif
+#ifndef NPD_ROPE_MIN_CTAS
+#define NPD_ROPE_MIN_CTAS 4
+#endif
 template <typename T, int D>
-__global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStoreParams p) {
+__global__ void __launch_bounds__(256, NPD_ROPE_MIN_CTAS) qk_norm_rope_store_kernel(const RopeStoreParams p) {
     constexpr int LPR = D / 8;                 // lanes per row
     constexpr int RPW = 32 / LPR;              // rows per warp pass
-    constexpr int kPasses = 8;                 // passes per unit
+    constexpr int kPasses = NPD_ROPE_PASSES;   // passes per unit
     constexpr int kChunk = RPW * kPasses;      // rows per unit
     const int lane = threadIdx.x & 31;
     const int sub = lane % LPR, row_in_pass = lane / LPR;
@@ -198,7 +207,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const RopeStore
 
 template <typename T>
 int launch(const RopeStoreParams &p, int head_dim, int device, cudaStream_t stream) {
-    const int rows_per_unit = (32 / (head_dim / 8)) * 8;                       // rows per warp pass x passes per unit
+    const int rows_per_unit = (32 / (head_dim / 8)) * NPD_ROPE_PASSES;         // rows per warp pass x passes per unit
     const long long units = p.num_tokens * ((p.num_q_heads + 2 * p.num_kv_heads + rows_per_unit - 1) / rows_per_unit);
     const int threads = 256;
     long long blocks = (units + 7) / 8;                                        // one unit per warp
