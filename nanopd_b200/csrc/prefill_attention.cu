@@ -94,7 +94,8 @@ struct PrefillParams {
     int chunk_tokens[kMaxChunks];
     int chunk_start[kMaxChunks];
     int num_pairs;                    // entries of pair_order
-    int *work_counter;                // device int32, zero before the launch: next work item to hand out
+    int *work_counter;                // two device int32, zero before the launch and put back to zero by its last
+                                      // CTA: [0] items handed out beyond the first gridDim.x, [1] CTAs that have left
     uint32_t pair_order[kMaxPairs];   // (chunk << 16 | pair of query tiles), sorted by key tiles, heaviest first
 #ifdef NPD_PREFILL_TRACE
     long long *trace;
@@ -430,7 +431,9 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             int item = 0;
             if (k_role) {
                 if (lane == 0) {
-                    item = atomicAdd(p.work_counter, 1);
+                    // the first item of a CTA is its own index (no round trip to the counter before the first load);
+                    // the counter hands out the items behind the first gridDim.x
+                    item = k == 0 ? static_cast<int>(blockIdx.x) : static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
                     if (item >= total_items) item = -1;
                     *reinterpret_cast<volatile int *>(&ctrl->sched_item[k % kSchedSlots]) = item;
                     mbar_arrive(smem_u32(&ctrl->sched_full[k % kSchedSlots]));
@@ -843,6 +846,12 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
+    // The last CTA to leave puts the two counters back to zero for the next launch on this workspace (every CTA
+    // has drawn its last item by now: its producer warp only leaves its loop on an item past the end, or on abort).
+    if (threadIdx.x == 0 && atomicAdd(p.work_counter + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+        p.work_counter[0] = 0;
+        p.work_counter[1] = 0;
+    }
 }
 
 }  // namespace
@@ -973,8 +982,7 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
             const int ne = static_cast<int>(std::min<size_t>(kMaxPairs, entries.size() - e0));
             for (int e = 0; e < ne; ++e) p.pair_order[e] = entries[e0 + e].code;
             p.num_pairs = ne;
-            p.work_counter = reinterpret_cast<int *>(static_cast<uint8_t *>(workspace) + 64);
-            NPD_CUDA_TRY(cudaMemsetAsync(p.work_counter, 0, sizeof(int), launch_stream));
+            p.work_counter = reinterpret_cast<int *>(static_cast<uint8_t *>(workspace) + 64);   // zero: see the kernel's end
             const long long items = (long long)ne * num_kv_heads;
             long long grid = items < sms ? items : sms;           // persistent: one CTA per SM
             const int cta_cap = (flags >> 8) & 0xffff;
