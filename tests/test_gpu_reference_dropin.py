@@ -11,7 +11,10 @@ where they lie.
    nanoPD/engine/model_runner.py:48-213) applied to a small random-init Qwen3 model built from a config (the
    constructor's tokenizer and checkpoint download, :8-13, is the only part bypassed): one whole-prompt prefill and
    several decode steps must give the logits of the same weights run by Hugging Face's own attention with its own
-   KV cache."""
+   KV cache.
+3. The reference's workers (``PrefillWorker.prefill_batch_and_extract``, ``DecodeWorker.receive_kv_async`` and
+   ``step``) with this repository's ``kv_transfer`` under the module name they import: prefill of two prompts in one
+   forward, extract, hand-over, six decode steps; the tokens equal Hugging Face's greedy generation."""
 import copy
 import os
 import subprocess
@@ -110,5 +113,75 @@ def test_reference_paged_forward_matches_hugging_face_cache():
             assert err <= 2e-2 * want.abs().max().item(), f"decode step {step}: max-abs logit error {err}"
             assert int(got.argmax()) == int(want.argmax())
             token = want.argmax().view(1, 1)
+    import paged_kernels
+    assert paged_kernels.check_status(device, raise_on_error=False) == 0
+
+
+def test_reference_workers_hand_over_through_this_kv_transfer(monkeypatch):
+    """The reference's own ``PrefillWorker.prefill_batch_and_extract`` and ``DecodeWorker.receive_kv_async`` /
+    ``step`` (nanoPD/workers/prefill_worker.py:92-112, decode_worker.py:39-126), run where they lie, with this
+    repository's ``kv_transfer`` under the module name they import and its ``paged_kernels`` behind their runners:
+    two prompts are prefilled in one forward, extracted, handed over and decoded for several steps.  Sampling is
+    made greedy in both workers so that the tokens can be compared with Hugging Face's own generation."""
+    import types
+    device = "cuda:0"
+    block_size, max_blocks = 16, 64
+    sys.path.insert(0, str(Path(REF) / "nanoPD"))
+    if str(ROOT) not in sys.path:
+        sys.path.insert(0, str(ROOT))
+    import nanopd_b200.kv_transfer as ours
+    monkeypatch.setitem(sys.modules, "workers.kv_transfer", ours)          # what `from workers.kv_transfer import` finds
+    from block_manager.block_manager import BlockSpaceManager
+    from block_manager.sequence import Sequence, SequenceGroup
+    import workers.prefill_worker as ref_prefill
+    import workers.decode_worker as ref_decode
+    assert ref_prefill.extract_kv_to_pinned is ours.extract_kv_to_pinned and ref_decode.transfer_kv is ours.transfer_kv
+    greedy = lambda logit, top_k=10: logit.argmax()
+    monkeypatch.setattr(ref_prefill, "top_k_sample", greedy)
+    monkeypatch.setattr(ref_decode, "top_k_sample", greedy)
+
+    hf_model = _small_qwen3(device, torch.float16)
+    bm = BlockSpaceManager(block_size=block_size, num_gpu_blocks=max_blocks)      # one manager for both workers, as there
+    pre = ref_prefill.PrefillWorker.__new__(ref_prefill.PrefillWorker)
+    pre.device, pre.block_manager, pre.block_size, pre._busy = device, bm, block_size, False
+    pre.runner = _patched_runner(copy.deepcopy(hf_model), device, max_blocks, block_size)
+    dec = ref_decode.DecodeWorker.__new__(ref_decode.DecodeWorker)
+    dec.device, dec.block_manager, dec.block_size = device, bm, block_size
+    dec.runner = _patched_runner(copy.deepcopy(hf_model), device, max_blocks, block_size)
+    dec.runner.tokenizer = types.SimpleNamespace(eos_token_id=-1)
+    dec.running, dec.finished, dec._pending = [], [], []
+    dec.compute_stream = torch.cuda.Stream(device=device)
+    dec.transfer_stream = torch.cuda.Stream(device=device)
+
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (45, 70)]
+    groups = [SequenceGroup(str(i), [Sequence(i, p, block_size)]) for i, p in enumerate(prompts)]
+    steps = 6
+    with torch.inference_mode():
+        results = pre.prefill_batch_and_extract(groups)
+        for group, (first_token, block_table, buf, src_k, src_v) in zip(groups, results):
+            # the extract: the pinned buffer holds the request's blocks, layer by layer
+            for i, blk in enumerate(block_table):
+                assert torch.equal(buf.k[:, i], src_k[:, blk].cpu()) and torch.equal(buf.v[:, i], src_v[:, blk].cpu())
+            path = dec.receive_kv_async(group, block_table, buf, src_k=src_k, src_v=src_v)
+            assert path in ("p2p", "pinned_relay")
+        torch.cuda.synchronize(device)
+        for group, (_, block_table, _, src_k, src_v) in zip(groups, results):
+            idx = torch.tensor(block_table, device=device)
+            assert torch.equal(dec.runner.k_cache[:, idx], src_k[:, idx]) and torch.equal(dec.runner.v_cache[:, idx], src_v[:, idx])
+        produced = {0: [results[0][0]], 1: [results[1][0]]}
+        for _ in range(steps):
+            for group, tok in dec.step():
+                produced[int(group.request_id)].append(tok)
+        # Hugging Face's own greedy generation from the same weights
+        for i, prompt in enumerate(prompts):
+            ids = torch.tensor([prompt], device=device)
+            ref = hf_model(ids, use_cache=True)
+            past, want = ref.past_key_values, [int(ref.logits[0, -1].argmax())]
+            for _ in range(steps):
+                ref = hf_model(torch.tensor([[want[-1]]], device=device), past_key_values=past, use_cache=True)
+                past = ref.past_key_values
+                want.append(int(ref.logits[0, 0].argmax()))
+            assert produced[i] == want, (i, produced[i], want)
     import paged_kernels
     assert paged_kernels.check_status(device, raise_on_error=False) == 0
