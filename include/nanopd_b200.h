@@ -85,7 +85,8 @@ int npd_kv_store(void *k_cache, void *v_cache, const void *k_src, const void *v_
  * over the first seq_lens[s] tokens of the pages block_tables[s, :]; the kv head of
  * q head h is h / (num_q_heads / num_kv_heads).  out, q: [num_seqs, num_q_heads,
  * head_dim] contiguous.  Caches as in npd_kv_store.  fp32 accumulation throughout.
- * Supported: dtype f16/bf16, head_dim in {64,128,256}, block_size in {8,16,32},
+ * Supported: dtype f16/bf16, head_dim in {64,128,256}, block_size in {4,8,16,32} (8 and up with
+ * NPD_DECODE_KV_INTERLEAVED),
  * num_q_heads/num_kv_heads <= 32.  A sequence with seq_lens[s] == 0 gets a zero row.
  * `workspace` is caller-owned device memory of at least
  * npd_decode_workspace_bytes(...) bytes, 256-byte aligned, ZEROED ONCE before first

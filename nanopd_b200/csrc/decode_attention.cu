@@ -184,13 +184,14 @@ __device__ __forceinline__ int table_lookup(TableWindow &w, int s, int page, int
 
 // Byte offset of 16-byte piece `c` of token row `r` inside a K or V tile.  A tile is made of
 // 16/box_rows boxes; a box is [half][box_rows][128 B] with the 128-byte swizzle TMA applies
-// (piece index XOR row%8; box_rows is 8 or 16 and boxes are 1024-byte aligned).
+// (piece index XOR the 128-byte row's index within its 1024-byte atom: TMA takes it from the shared-memory
+// address, which is row%8 for boxes of 8 or 16 rows and differs for boxes of 4).
 template <int D>
 __device__ __forceinline__ uint32_t tile_offset(int r, int c, int box_rows) {
     constexpr int NH = D / 64;
     const int box = r / box_rows, rr = r - box * box_rows;
-    return static_cast<uint32_t>(box * (NH * box_rows * 128) + (c >> 3) * (box_rows * 128) + rr * 128 +
-                                 (((c & 7) ^ (r & 7)) << 4));
+    const int row_off = box * (NH * box_rows * 128) + (c >> 3) * (box_rows * 128) + rr * 128;
+    return static_cast<uint32_t>(row_off + (((c & 7) ^ ((row_off >> 7) & 7)) << 4));
 }
 
 template <typename T, int D, int NT>
@@ -402,6 +403,13 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
     const int k_row_off = (k_r / p.box_rows) * (NH * p.box_rows * 128) + (k_r % p.box_rows) * 128;
     const int v_row_off = (v_r / p.box_rows) * (NH * p.box_rows * 128) + (v_r % p.box_rows) * 128;
     const int half_bytes = p.box_rows * 128;
+    // swizzle phase of this lane's row in each 64-element slab: the row's 128-byte index within its 1024-byte atom
+    int k_phase[NH], v_phase[NH];
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+        k_phase[hf] = ((k_row_off + hf * half_bytes) >> 7) & 7;
+        v_phase[hf] = ((v_row_off + hf * half_bytes) >> 7) & 7;
+    }
     // interleaved layouts: a box holds box_rows tokens; K box = [D/8 pieces][box_rows][16 B], V box = [D][box_rows x 2 B]
     const int box_bytes = p.box_rows * D * 2;
     const int il_k_off = (k_r / p.box_rows) * box_bytes + (k_r % p.box_rows) * 16;       // + piece * box_rows * 16
@@ -541,7 +549,7 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
                 uint32_t a[4];
                 const int c = 2 * ks + (mi >> 1);
                 if (IL) ldmatrix_x4(a, ks_addr + il_k_off + c * (p.box_rows * 16));
-                else ldmatrix_x4(a, ks_addr + k_row_off + (c >> 3) * half_bytes + (((c & 7) ^ (k_r & 7)) << 4));
+                else ldmatrix_x4(a, ks_addr + k_row_off + (ks >> 2) * half_bytes + (((c & 7) ^ k_phase[ks >> 2]) << 4));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     if (ks & 1) Elem<T>::mma16816(sb[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
@@ -595,7 +603,7 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
                 uint32_t a[4];
                 const int c = 2 * j + (mi & 1);
                 if (IL) ldmatrix_x4(a, vs_addr + il_v_off + j * 16 * (p.box_rows * 2));
-                else ldmatrix_x4_trans(a, vs_addr + v_row_off + (c >> 3) * half_bytes + (((c & 7) ^ (v_r & 7)) << 4));
+                else ldmatrix_x4_trans(a, vs_addr + v_row_off + (j >> 2) * half_bytes + (((c & 7) ^ v_phase[j >> 2]) << 4));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) Elem<T>::mma16816(st.o[nt][j], a, pb[nt][0], pb[nt][1]);
             }
@@ -784,8 +792,8 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
                 "decode attention supports float16 and bfloat16 only (dtype code %d)", dtype);
     NPD_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, NPD_ERR_UNSUPPORTED,
                 "decode attention: head_dim %lld not in {64,128,256}", (long long)head_dim);
-    NPD_REQUIRE(block_size == 8 || block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
-                "decode attention: block_size %lld not in {8,16,32}", (long long)block_size);
+    NPD_REQUIRE(block_size == 4 || block_size == 8 || block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
+                "decode attention: block_size %lld not in {4,8,16,32}", (long long)block_size);
     NPD_REQUIRE(num_seqs >= 0 && num_q_heads > 0 && num_kv_heads > 0 && max_blocks_per_seq > 0 && num_blocks > 0,
                 NPD_ERR_INVALID_ARG, "decode attention: non-positive dimension");
     NPD_REQUIRE(num_q_heads % num_kv_heads == 0, NPD_ERR_INVALID_ARG,
@@ -817,6 +825,9 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
     const bool interleaved = (flags & NPD_DECODE_KV_INTERLEAVED) != 0;
     int rc;
     if (interleaved) {
+        NPD_REQUIRE(block_size >= 8, NPD_ERR_UNSUPPORTED,
+                    "decode attention: the interleaved layouts need block_size >= 8 (a V row of a block is "
+                    "block_size * 2 bytes, and a TMA box row is at least 16)");
         // K [blocks, Hkv, D/8, B, 8]: rows of B*8 elements, one per (kv head, 8-element piece of the head dim);
         // V [blocks, Hkv, D, B]: rows of B elements, one per (kv head, head-dim element).  No swizzle.
         const uint64_t kdims[3] = {(uint64_t)block_size * 8, (uint64_t)(num_kv_heads * head_dim / 8), (uint64_t)num_blocks};

@@ -62,10 +62,18 @@ def test_various_seq_lens(kernels, seq_len):
     check(kernels, *_inputs(1, 4, 4, 128, [seq_len], 16, torch.float16))
 
 
-@pytest.mark.parametrize("block_size", [8, 16, 32])
+@pytest.mark.parametrize("block_size", [4, 8, 16, 32])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_block_sizes(kernels, block_size, dtype):
     check(kernels, *_inputs(4, 4, 4, 128, [48, 32, 7, 131], block_size, dtype))
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_block_size_4(kernels, D):
+    """Blocks of 4 tokens (the smallest size of the reference's kernel tests,
+    nanoPD/paged_attention/tests/test_paged_attention.py:192-203): four TMA boxes of 4 rows per 16-token tile."""
+    check(kernels, *_inputs(3, 8, 2, D, [24, 16, 77], 4, torch.float16))
+    check(kernels, *_inputs(2, 4, 4, D, [3, 130], 4, torch.bfloat16))
 
 
 @pytest.mark.parametrize("D", [64, 128, 256])

@@ -5,8 +5,10 @@ tests/golden/ use); skipped where there is none.  Nothing of the reference is co
 where they lie.
 
 1. ``nanoPD/paged_attention/tests/test_paged_kernels.py`` — the reference's kernel tests (5-D K / transposed-V
-   caches, the older ``paged_kv_store`` call shape, int64 tables must raise) — run unchanged in a child pytest with
-   this repository's root first on the module path, so ``import paged_kernels`` finds this implementation.
+   caches, the older ``paged_kv_store`` call shape, int64 tables must raise) — and ``test_paged_attention.py``
+   beside it (the older module name ``paged_attn``; block sizes 4 to 32) run unchanged in a child pytest with
+   this repository's root first on the module path, so ``import paged_kernels`` / ``import paged_attn`` find this
+   implementation.
 2. ``ModelRunner`` 's monkey-patch (``_patch_attention_layers`` / ``paged_forward``,
    nanoPD/engine/model_runner.py:48-213) applied to a small random-init Qwen3 model built from a config (the
    constructor's tokenizer and checkpoint download, :8-13, is the only part bypassed): one whole-prompt prefill and
@@ -31,8 +33,9 @@ pytestmark = [pytest.mark.gpu,
                                  reason="set NANOPD_REFERENCE to a checkout of the reference")]
 
 
-def test_reference_kernel_tests_pass_unchanged(tmp_path):
-    test_file = Path(REF) / "nanoPD" / "paged_attention" / "tests" / "test_paged_kernels.py"
+@pytest.mark.parametrize("name", ["test_paged_kernels.py", "test_paged_attention.py"])
+def test_reference_kernel_tests_pass_unchanged(tmp_path, name):
+    test_file = Path(REF) / "nanoPD" / "paged_attention" / "tests" / name
     env = dict(os.environ, PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
     res = subprocess.run([sys.executable, "-m", "pytest", str(test_file), "-q", "-p", "no:cacheprovider",
                           "--rootdir", str(tmp_path), "-c", os.devnull],
