@@ -56,6 +56,9 @@ CASES = [
     ("len512_f16", 1, 2, 1, 128, [512], 16, torch.float16),
     ("block32_f16", 2, 4, 4, 128, [48, 32], 32, torch.float16),
     ("block8_d64_f16", 2, 4, 2, 64, [9, 24], 8, torch.float16),
+    # the smallest block of the older test file beside it (test_paged_attention.py:192-203)
+    ("block4_d64_f16", 2, 4, 4, 64, [24, 16], 4, torch.float16),
+    ("block4_gqa_bf16", 2, 8, 2, 128, [7, 41], 4, torch.bfloat16),
 ]
 
 
