@@ -94,6 +94,15 @@ def load_sampling_cases():
     return cases
 
 
+@pytest.fixture(autouse=True)
+def _first_gpu_is_current():
+    """Every test starts with device 0 current, whatever an earlier test on a box with several GPUs left behind
+    (a worker of tests/test_gpu_threads.py binds its thread — the main thread, in the serial half — to its GPU)."""
+    if torch.cuda.is_available():
+        torch.cuda.set_device(0)
+    yield
+
+
 @pytest.fixture(scope="session")
 def decode_cases():
     return load_decode_cases()
