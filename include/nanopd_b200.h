@@ -142,7 +142,7 @@ int npd_paged_decode_attention_static(void *out, const void *q, const void *k_ca
  *   block_tables[c*bt_row_stride + ...]; the chunk's own K/V must already be stored.
  * q, out: [total_q_tokens, num_q_heads, head_dim] contiguous.  The three chunk arrays
  * are HOST int32 arrays (the scheduler knows them; nanoPD/engine/engine.py:68-90).
- * Supported: f16/bf16, head_dim 64/128/256, block_size 8/16/32; out 32-byte aligned.
+ * Supported: f16/bf16, head_dim 64/128/256, block_size 4/8/16/32; out 32-byte aligned.
  * `workspace`: device memory of at least npd_prefill_workspace_bytes(...) bytes, ZEROED
  * ONCE before first use (status word, then two counters every launch leaves at zero);
  * two calls that may overlap on the GPU need two workspaces.                              */

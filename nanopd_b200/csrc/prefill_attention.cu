@@ -84,7 +84,7 @@ struct PrefillParams {
     int num_q_heads, num_kv_heads, group;
     int tq;                 // query tokens per 128-row tile = 128 / group (floor)
     int block_size;
-    int box_rows;           // rows of a K/V TMA box: 16, or 8 when the block size is 8
+    int box_rows;           // rows of a K/V TMA box: 16, or the block size when that is 8 or 4
     int query_tiles;        // query tiles per work item (2; 1 at head_dim 256)
     int half_steps_per_tile;   // 64-key half-steps per K/V tile (2; 1 at head_dim 256)
     int max_blocks_per_seq;
@@ -329,10 +329,12 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, int item) {
 // ragged chunks balance across the SMs.  All barrier phases are driven by running counters: the producer
 // already loads the next item's K/V tiles (and, once the last score MMA has been issued, its query tiles) while
 // the current item drains, and the epilogue of an item overlaps the first MMAs of the next one.
-// kBox8: blocks of 8 tokens (a 16-key row group of a K/V tile is then two TMA boxes of 8 rows); a template parameter
-// because the producer warp shares a sub-partition's issue slots with two softmax warps, and every instruction it
-// runs per key tile shows in the kernel's time (the run-time form of this choice cost 2.3 %).
-template <typename T, int kD, bool kBox8>
+// kBoxRows: rows of a K/V TMA box — 16, or the block size when blocks hold 8 or 4 tokens (a 16-key row group of a
+// tile is then two or four boxes; the 128-byte swizzle follows the shared-memory address, so the tile in shared
+// memory is the same).  A template parameter because the producer warps share their sub-partitions' issue slots
+// with two softmax warps each, and every instruction they run per key tile shows in the kernel's time (the
+// run-time form of this choice cost 2.3 %).
+template <typename T, int kD, int kBoxRows>
 __global__ void __launch_bounds__(kThreads, 1)
 paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -402,7 +404,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         // =========================== TMA producers: warp 8 (query tiles, K tiles), warp 11 (V tiles) ===========================
         // A K or V tile is 16 boxes of 2 KiB (16-key row groups x 64-element slabs; 32 boxes of 1 KiB with blocks
-        // of 8 tokens), one box per lane, issued by ONE instruction of the warp.  Issuing tiled copies costs the
+        // of 8 tokens, 64 of 512 B with blocks of 4), one box per lane, issued by ONE instruction of the warp per 32.  Issuing tiled copies costs the
         // issuing warp about 50 clocks per box plus several hundred per instruction, whatever the box holds, while
         // the copy engine itself takes boxes from several warps at once: one warp issuing both tiles of a 128-key
         // step (32 boxes) needed as long as the step's arithmetic, two warps need half of it.  Each lane looks its
@@ -413,10 +415,23 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             if (k_role) tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(tm);
         }
-        // lane -> box: (16-key row group gi, 64-element slab hf, 8-row half `sub` of the group when blocks hold 8 tokens)
-        const int sub = kBox8 ? (lane & 1) : 0, l2 = kBox8 ? (lane >> 1) : lane;
-        const int hf = l2 % kHalves, gi = l2 / kHalves;
-        const bool has_box = gi < kTK / 16;
+        // box b of a tile = (16-key row group gi, 64-element slab hf, piece `sub` of the group's 16 / kBoxRows boxes when
+        // blocks hold fewer than 16 tokens); lane l issues boxes l, l + 32, ... — one instruction per 32 boxes
+        constexpr int kSubs = 16 / kBoxRows;
+        constexpr int kBoxes = (kTK / 16) * kHalves * kSubs;
+        constexpr int kIssues = (kBoxes + 31) / 32;
+        int sub[kIssues], hf[kIssues], gi[kIssues];
+        bool has_box[kIssues];
+        uint32_t off[kIssues];
+#pragma unroll
+        for (int i = 0; i < kIssues; ++i) {
+            const int b = i * 32 + lane, l2 = b / kSubs;
+            sub[i] = b % kSubs;
+            hf[i] = l2 % kHalves;
+            gi[i] = l2 / kHalves;
+            has_box[i] = b < kBoxes;
+            off[i] = static_cast<uint32_t>(hf[i] * kKvHalfBytes + gi[i] * 2048 + sub[i] * kBoxRows * 128);
+        }
         uint8_t *ring = k_role ? k_ring : v_ring;
         uint64_t *full = k_role ? ctrl->k_full : ctrl->v_full, *empty = k_role ? ctrl->k_empty : ctrl->v_empty;
         const int stages = k_role ? kStagesK : kStagesV;
@@ -465,11 +480,11 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             };
             if (k_role && !(ok = load_q(0))) break;
             const int32_t *table = p.block_tables + (long long)it.c * p.bt_row_stride;
-            // A lane's box lies in one block: 16 keys of a block of 16 or 32, or 8 keys of a block of 8.
-            auto lookup = [&](int t) {
-                const int key = t * kTK + gi * 16 + sub * 8;
+            // A box lies in one block: 16 keys of a block of 16 or 32, or all keys of a block of 8 or 4.
+            auto lookup = [&](int t, int i) {
+                const int key = t * kTK + gi[i] * 16 + sub[i] * kBoxRows;
                 int id = 0;
-                if (has_box && t < it.n_kv && key < it.ctx_end) {
+                if (has_box[i] && t < it.n_kv && key < it.ctx_end) {
                     id = __ldg(table + key / p.block_size);
                     if (id < 0 || id >= p.num_blocks) {
                         atomicOr(p.status, NPD_STATUS_BAD_BLOCK_ID);
@@ -478,17 +493,21 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 }
                 return id;
             };
-            int id_next = lookup(0);
-            const uint32_t off = static_cast<uint32_t>(hf * kKvHalfBytes + gi * 2048 + sub * 8 * 128);
+            int id_next[kIssues];
+#pragma unroll
+            for (int i = 0; i < kIssues; ++i) id_next[i] = lookup(0, i);
             for (int t = 0; t < it.n_kv; ++t) {
                 const int key0 = t * kTK;
-                const int id = id_next;
-                id_next = lookup(t + 1);
+                int id[kIssues];
+#pragma unroll
+                for (int i = 0; i < kIssues; ++i) {
+                    id[i] = id_next[i];
+                    id_next[i] = lookup(t + 1, i);
+                }
                 // 16-key row groups holding at least one written key; the rest is never loaded
                 int ngroups = 0;
                 for (int g2 = 0; g2 < kTK / 16; ++g2) ngroups += (key0 + g2 * 16 < it.ctx_end) ? 1 : 0;
                 const uint32_t bytes = static_cast<uint32_t>(ngroups * kHalves * 16 * 128);
-                const int row = it.h * p.block_size + ((key0 + gi * 16 + sub * 8) % p.block_size);
                 // the stage is free once the MMAs that read the tile `stages` tiles back are done: the score MMAs
                 // for a K tile, the PV MMAs for a V tile
                 if (round > 0) ok = wait_or_abort(smem_u32(&empty[stage]), (round - 1) & 1, abort_flag, p.status);
@@ -498,8 +517,13 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     mbar_expect_tx(smem_u32(&full[stage]), bytes);
                 }
                 __syncwarp();
-                if (has_box && gi < ngroups)
-                    tma_load_3d(smem_u32(ring + (size_t)stage * kKvTileBytes) + off, tm, smem_u32(&full[stage]), hf * 64, row, id);
+#pragma unroll
+                for (int i = 0; i < kIssues; ++i) {
+                    const int row = it.h * p.block_size + ((key0 + gi[i] * 16 + sub[i] * kBoxRows) % p.block_size);
+                    if (has_box[i] && gi[i] < ngroups)
+                        tma_load_3d(smem_u32(ring + (size_t)stage * kKvTileBytes) + off[i], tm, smem_u32(&full[stage]),
+                                    hf[i] * 64, row, id[i]);
+                }
                 if (++stage == stages) {
                     stage = 0;
                     ++round;
@@ -870,8 +894,8 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
                 "prefill attention supports float16 and bfloat16 only (dtype code %d)", dtype);
     NPD_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, NPD_ERR_UNSUPPORTED,
                 "prefill attention: head_dim %lld not in {64,128,256}", (long long)head_dim);
-    NPD_REQUIRE(block_size == 8 || block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
-                "prefill attention: block_size %lld not in {8,16,32}", (long long)block_size);
+    NPD_REQUIRE(block_size == 4 || block_size == 8 || block_size == 16 || block_size == 32, NPD_ERR_UNSUPPORTED,
+                "prefill attention: block_size %lld not in {4,8,16,32}", (long long)block_size);
     NPD_REQUIRE(num_chunks >= 0 && num_q_heads > 0 && num_kv_heads > 0 && max_blocks_per_seq > 0 && num_blocks > 0,
                 NPD_ERR_INVALID_ARG, "prefill attention: non-positive dimension");
     NPD_REQUIRE(num_q_heads % num_kv_heads == 0, NPD_ERR_INVALID_ARG,
@@ -924,13 +948,13 @@ extern "C" int npd_paged_prefill_attention(void *out, const void *q, const void 
     const bool f16 = dtype == NPD_DTYPE_F16;
     using Kernel = void (*)(PrefillParams, CUtensorMap, CUtensorMap, CUtensorMap);
     Kernel kern = nullptr;
-#define NPD_PICK(D_)                                                                                              \
-    kern = box_rows == 8 ? (f16 ? paged_prefill_kernel<__half, D_, true> : paged_prefill_kernel<__nv_bfloat16, D_, true>)   \
-                         : (f16 ? paged_prefill_kernel<__half, D_, false> : paged_prefill_kernel<__nv_bfloat16, D_, false>)
+#define NPD_PICK_B(D_, B_) (f16 ? paged_prefill_kernel<__half, D_, B_> : paged_prefill_kernel<__nv_bfloat16, D_, B_>)
+#define NPD_PICK(D_) kern = box_rows == 4 ? NPD_PICK_B(D_, 4) : (box_rows == 8 ? NPD_PICK_B(D_, 8) : NPD_PICK_B(D_, 16))
     if (head_dim == 64) NPD_PICK(64);
     else if (head_dim == 128) NPD_PICK(128);
     else NPD_PICK(256);
 #undef NPD_PICK
+#undef NPD_PICK_B
     NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -79,6 +79,15 @@ def test_block_size_8(kernels, dtype, L, start, n, poison):
     check_single(kernels, L, start, n, 8, 2, 8, dtype, seed=6, poison=poison)
 
 
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 4, 4), (128, 8, 2), (256, 4, 1)])
+@pytest.mark.parametrize("L,start,n,poison", [(500, 200, 300, False), (77, 0, 77, True), (264, 256, 8, False)])
+def test_block_size_4(kernels, D, Hq, Hkv, L, start, n, poison):
+    """Blocks of 4 tokens, the smallest size the decode kernel takes: a 16-key row group is four boxes of 4 rows
+    (64 boxes per 128-key tile, two copy instructions per producer warp)."""
+    check_single(kernels, L, start, n, Hq, Hkv, 4, torch.float16, seed=16, poison=poison, D=D)
+    check_single(kernels, L, start, n, Hq, Hkv, 4, torch.bfloat16, seed=17, poison=poison, D=D)
+
+
 def test_unwritten_slots_are_never_used(kernels):
     """NaN everywhere outside keys [0, start+n): later tokens of the prompt, the tail of the last page
     and unused blocks must not reach the output."""
@@ -222,9 +231,9 @@ def test_argument_errors(kernels):
         kernels.paged_prefill_attention(out, q, kc, kc, bt, [0], [16], [60], 1.0, 16, 4)
     with pytest.raises(RuntimeError):   # chunk outside q
         kernels.paged_prefill_attention(out, q, kc, kc, bt, [8], [16], [0], 1.0, 16, 4)
-    kc4 = torch.zeros(8, 2, 4, 128, dtype=torch.float16, device=DEV)
-    with pytest.raises(RuntimeError):   # block size 4 is outside the kernel's set (8, 16, 32)
-        kernels.paged_prefill_attention(out, q, kc4, kc4, bt, [0], [16], [0], 1.0, 4, 4)
+    kc2 = torch.zeros(16, 2, 2, 128, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError):   # block size 2 is outside the kernel's set (4, 8, 16, 32)
+        kernels.paged_prefill_attention(out, q, kc2, kc2, torch.zeros(1, 8, dtype=torch.int32, device=DEV), [0], [16], [0], 1.0, 2, 8)
 
 
 def test_more_chunks_than_one_launch_takes(kernels):
