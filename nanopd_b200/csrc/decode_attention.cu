@@ -270,6 +270,54 @@ __device__ __forceinline__ void write_partial(const AttnState<T, D, NT> &st, flo
     }
 }
 
+// Folds `count` records that lie `stride_floats` apart (shared memory: plain loads) into `st`: the maximum over all
+// records first, then the weighted sum.
+template <typename T, int D, int NT>
+__device__ __forceinline__ void merge_records(AttnState<T, D, NT> &st, const float *first, size_t stride_floats, int count,
+                                              int lane) {
+    constexpr int KS = D / 16;
+    const int t4 = lane & 3;
+    float mg[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mg[nt][0] = mg[nt][1] = -INFINITY;
+    for (int w = 0; w < count; ++w) {
+        const float4 *ml4 = reinterpret_cast<const float4 *>(first + w * stride_floats + NT * KS * 128);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const float4 ml = ml4[nt * 4 + t4];
+            mg[nt][0] = fmaxf(mg[nt][0], ml.x);
+            mg[nt][1] = fmaxf(mg[nt][1], ml.y);
+        }
+    }
+    st.reset();
+    for (int w = 0; w < count; ++w) {
+        const float *rec = first + w * stride_floats;
+        const float4 *o4 = reinterpret_cast<const float4 *>(rec);
+        const float4 *ml4 = reinterpret_cast<const float4 *>(rec + NT * KS * 128);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const float4 ml = ml4[nt * 4 + t4];
+            const float sn0 = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - mg[nt][0]);
+            const float sn1 = ml.y == -INFINITY ? 0.f : fast_exp2(ml.y - mg[nt][1]);
+            st.l[nt][0] += ml.z * sn0;
+            st.l[nt][1] += ml.w * sn1;
+#pragma unroll
+            for (int j = 0; j < KS; ++j) {
+                const float4 o = o4[(nt * KS + j) * 32 + lane];
+                st.o[nt][j][0] += o.x * sn0;
+                st.o[nt][j][1] += o.y * sn1;
+                st.o[nt][j][2] += o.z * sn0;
+                st.o[nt][j][3] += o.w * sn1;
+            }
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        st.m[nt][0] = mg[nt][0];
+        st.m[nt][1] = mg[nt][1];
+    }
+}
+
 // Folds the partial records of workers wf..wl (one (sequence, kv head) cut by range boundaries) into `st`.
 // Records were written by other SMs during this launch: read them through L2 (ld.global.cg), never L1.
 // Two passes, so that no load waits for arithmetic on an earlier one: first the maximum over all records (eight
@@ -348,7 +396,13 @@ __device__ __forceinline__ void merge_partials(AttnState<T, D, NT> &st, const De
 #ifndef NPD_DECODE_MAX_WARPS
 #define NPD_DECODE_MAX_WARPS 12
 #endif
-template <typename T, int D, int NT, bool IL, int MAXW>
+// SMALL: the form for small batches of short sequences (the reference's operating range: up to 16 sequences of a
+// few hundred tokens).  There the equal-work split of the streaming form costs more than it saves — a prefix over
+// all sequences, a dozen partial records per (sequence, kv head) written to global memory, a ticket and a merge by
+// the last worker: 12-14 us for a launch whose copies take one.  In the small form a CTA owns ONE (sequence, kv
+// head): its warps take equal runs of the sequence's tiles, leave their partial records in shared memory (each in
+// its own, by then idle, ring) and warp 0 merges them.  No prefix, no workspace traffic, no ticket.
+template <typename T, int D, int NT, bool IL, int MAXW, bool SMALL = false>
 __global__ void __maxnreg__(MAXW <= 8 ? 224 : 168)
 paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v) {
@@ -379,22 +433,49 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
     }
-    build_tile_prefix(p, pre);   // ends with __syncthreads(): barriers are initialised for everyone
-    // Empty sequences get zero rows, as the reference's kernel leaves them
-    // (nanoPD/paged_attention/csrc/attention/paged_attention_kernel.cu:117-150 with seq_len 0).
-    for (int s0 = blockIdx.x; s0 < p.num_seqs; s0 += gridDim.x) {
-        if (pre[s0 + 1] != pre[s0]) continue;
-        uint32_t *row = reinterpret_cast<uint32_t *>(static_cast<T *>(p.out) + (long long)s0 * p.num_q_heads * D);
-        for (int i = threadIdx.x; i < p.num_q_heads * D / 2; i += blockDim.x) row[i] = 0u;
-    }
+    long long W = 0;
+    int worker = 0, my_tiles = 0;
+    Cursor pc, cc;                   // producer / consumer cursors over the same range
+    if (SMALL) {
+        __syncthreads();             // barriers are initialised for everyone
+        const int s0 = blockIdx.x / p.num_vheads, h0 = blockIdx.x - s0 * p.num_vheads;
+        const int raw = __ldg(p.seq_lens + s0);
+        if ((raw < 0 || raw > (long long)p.max_blocks_per_seq * p.block_size) && h0 == 0 && threadIdx.x == 0)
+            atomicOr(p.status, NPD_STATUS_BAD_POSITION);
+        const int len0 = clamped_len(p, s0), n0 = (len0 + kTile - 1) / kTile;
+        if (n0 == 0) {
+            // an empty sequence gets zero rows (see below); this CTA writes those of its own q heads
+            uint32_t *row = reinterpret_cast<uint32_t *>(static_cast<T *>(p.out) +
+                                                         ((long long)s0 * p.num_q_heads + (long long)h0 * p.group) * D);
+            for (int i = threadIdx.x; i < p.group * D / 2; i += blockDim.x) row[i] = 0u;
+            return;                  // the whole CTA leaves here: no barrier follows for anyone
+        }
+        const int per_warp = (n0 + nwarps - 1) / nwarps;
+        const int t0 = warp * per_warp;
+        W = per_warp;
+        worker = warp;
+        my_tiles = max(0, min(per_warp, n0 - t0));
+        pc.s = s0, pc.h = h0, pc.t = min(t0, n0 - 1), pc.n = n0, pc.len = len0;
+    } else {
+        build_tile_prefix(p, pre);   // ends with __syncthreads(): barriers are initialised for everyone
+        // Empty sequences get zero rows, as the reference's kernel leaves them
+        // (nanoPD/paged_attention/csrc/attention/paged_attention_kernel.cu:117-150 with seq_len 0).
+        for (int s0 = blockIdx.x; s0 < p.num_seqs; s0 += gridDim.x) {
+            if (pre[s0 + 1] != pre[s0]) continue;
+            uint32_t *row = reinterpret_cast<uint32_t *>(static_cast<T *>(p.out) + (long long)s0 * p.num_q_heads * D);
+            for (int i = threadIdx.x; i < p.num_q_heads * D / 2; i += blockDim.x) row[i] = 0u;
+        }
 
-    const long long total = (long long)p.num_vheads * pre[p.num_seqs];
-    const long long W = tiles_per_worker(total, p.num_workers, (long long)p.num_vheads * p.num_seqs);
-    const int worker = blockIdx.x * nwarps + warp;
-    const long long f_begin = (long long)worker * W;
-    if (f_begin >= total) return;
-    const long long f_end = min(f_begin + W, total);
-    const int my_tiles = static_cast<int>(f_end - f_begin);
+        const long long total = (long long)p.num_vheads * pre[p.num_seqs];
+        W = tiles_per_worker(total, p.num_workers, (long long)p.num_vheads * p.num_seqs);
+        worker = blockIdx.x * nwarps + warp;
+        const long long f_begin = (long long)worker * W;
+        if (f_begin >= total) return;
+        const long long f_end = min(f_begin + W, total);
+        my_tiles = static_cast<int>(f_end - f_begin);
+        cursor_seek(pc, f_begin, pre, p);
+    }
+    cc = pc;
 
     // ---- per-lane shared-memory offsets of the ldmatrix rows (same for every tile) ----
     const int mi = lane >> 3, mrow = lane & 7;
@@ -417,9 +498,6 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
     const int il_v_off = (il_v_tok / p.box_rows) * box_bytes + (il_v_tok % p.box_rows) * 2 +
                          ((mi & 1) * 8 + mrow) * (p.box_rows * 2);                         // + 16 j rows
 
-    Cursor pc, cc;                   // producer / consumer cursors over the same range
-    cursor_seek(pc, f_begin, pre, p);
-    cc = pc;
     TableWindow win{-1, 0, 0};
 
     int issued = 0;
@@ -621,7 +699,10 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
         if (dead) break;
 
         st.reduce_l();
-        if (!head_cut && !tail_cut) {
+        if (SMALL) {
+            // this warp's run is done and nothing is in flight into its ring: the record goes there
+            write_partial<T, D, NT>(st, reinterpret_cast<float *>(stage_base), lane);
+        } else if (!head_cut && !tail_cut) {
             write_output<T, D, NT>(st, p, seg_s, seg_h, lane);
         } else {
             float *rec = p.partials + ((size_t)worker * 2 + (head_cut ? 0 : 1)) * rec_floats<D, NT>();
@@ -647,6 +728,16 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
         }
     }
 
+    if (SMALL) {
+        __syncthreads();             // every warp's record is in shared memory (all warps of the CTA get here)
+        if (warp == 0) {
+            const int n_records = (pc.n + static_cast<int>(W) - 1) / static_cast<int>(W);     // warps that had tiles
+            AttnState<T, D, NT> merged;
+            merge_records<T, D, NT>(merged, reinterpret_cast<const float *>(sbase), (size_t)nst * STAGE_BYTES / sizeof(float),
+                                    n_records, lane);
+            write_output<T, D, NT>(merged, p, pc.s, pc.h, lane);
+        }
+    }
     if (dead) {
         // Give copies still in flight one more bounded chance to land before the CTA's shared
         // memory can be handed to another CTA.
@@ -666,6 +757,7 @@ paged_decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtenso
 // ---------------------------------------------------------------------------
 struct LaunchShape {
     int nwarps, nstages, grid;
+    bool small;     // the small-batch form: one CTA per (sequence, virtual kv head)
 };
 
 int env_int(const char *name, int fallback) {
@@ -703,7 +795,28 @@ LaunchShape launch_shape(int head_dim, int block_size, int cta_cap, long long nu
     int nst = knob_stages > 0 ? knob_stages : stages;
     while (nst > 1 && (long long)ls.nwarps * nst * stage_bytes > 192 * 1024) --nst;
     ls.nstages = nst;
+    ls.small = false;
     return ls;
+}
+
+// The small-batch form is taken when no sequence can be longer than kSmallMaxTokens (the table's width bounds it:
+// the reference's caller pads its tables to the longest sequence of the batch, nanoPD/engine/model_runner.py:176-187)
+// and every (sequence, virtual kv head) gets an SM of its own.  Standard layout, uncapped grid.  Device time per
+// launch on a B200, small form / streaming form (Qwen3-8B shape, bf16): 1 sequence of up to 512 tokens 6.3 / 10.0 us,
+// 8 x 512: 9.6 / 14.9, 16 x 256: 7.6 / 15.0, 16 x 1024: 16.0 / 19.5, 16 x 2048: 26.6 / 26.7, 4 x 2048: 22.6 / 18.4 —
+// beyond a thousand tokens a CTA's eight warps stream too long for the saved merge to pay.
+constexpr long long kSmallMaxTokens = 1024;
+void consider_small_form(LaunchShape &ls, int head_dim, long long max_tokens, long long seq_heads, int cta_cap,
+                         bool interleaved, int flags, int device) {
+    static const int knob = env_int("NPD_DECODE_SMALL", 1);      // 2 = off (for experiments; read once per process)
+    if (knob == 2 || (flags & NPD_DECODE_NO_SMALL) || interleaved || cta_cap > 0) return;
+    if (max_tokens > kSmallMaxTokens || seq_heads < 1 || seq_heads > npd::sm_count(device)) return;
+    const int stage_bytes = 2 * kTile * head_dim * 2;
+    ls.small = true;
+    ls.grid = static_cast<int>(seq_heads);
+    ls.nwarps = 8;
+    ls.nstages = head_dim == 256 ? 1 : (head_dim == 128 ? 3 : 4);
+    while (ls.nstages > 1 && (long long)ls.nwarps * ls.nstages * stage_bytes > 192 * 1024) --ls.nstages;
 }
 
 // Smallest split of the group into virtual kv heads whose q-head count fits the n-tiles.
@@ -722,7 +835,14 @@ int launch_decode(const DecodeParams &p, const CUtensorMap &tk, const CUtensorMa
     const size_t smem = 1024 + (size_t)ls.nwarps * ls.nstages * (STAGE_BYTES + 8) + ((size_t)p.num_seqs + 1) * 4 + 16;
     // Largest shared-memory carve-out on both instances: the SM then has room for a small CTA of another stream
     // (the page migration kernel asks for the same), instead of being configured for this CTA alone.
-    if (ls.nwarps <= 8) {
+    if (ls.small) {
+        if constexpr (!IL) {
+            auto kern = paged_decode_stream_kernel<T, D, NT, false, 8, true>;
+            NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            kern<<<ls.grid, ls.nwarps * 32, smem, stream>>>(p, tk, tv);
+        }
+    } else if (ls.nwarps <= 8) {
         auto kern = paged_decode_stream_kernel<T, D, NT, IL, 8>;
         NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         NPD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
@@ -812,11 +932,14 @@ extern "C" int npd_paged_decode_attention(void *out, const void *q, const void *
 
     int dev = 0;
     NPD_CUDA_TRY(cudaGetDevice(&dev));
-    const LaunchShape ls = launch_shape(static_cast<int>(head_dim), static_cast<int>(block_size), (flags >> 8) & 0xffff,
-                                        (long long)num_seqs * num_kv_heads, dev);
+    LaunchShape ls = launch_shape(static_cast<int>(head_dim), static_cast<int>(block_size), (flags >> 8) & 0xffff,
+                                  (long long)num_seqs * num_kv_heads, dev);
     const WorkspacePlan wp = plan_workspace(num_seqs, num_q_heads, num_kv_heads, head_dim, ls);
     NPD_REQUIRE(workspace != nullptr && workspace_bytes >= wp.total, NPD_ERR_WORKSPACE,
                 "decode attention: workspace of %zu bytes given, %zu needed", workspace_bytes, wp.total);
+    consider_small_form(ls, static_cast<int>(head_dim), (long long)max_blocks_per_seq * block_size,
+                        (long long)num_seqs * num_kv_heads * wp.kv_rep, (flags >> 8) & 0xffff,
+                        (flags & NPD_DECODE_KV_INTERLEAVED) != 0, flags, dev);
     NPD_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, NPD_ERR_WORKSPACE,
                 "decode attention: workspace must be 256-byte aligned");
 

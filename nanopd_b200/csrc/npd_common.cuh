@@ -16,6 +16,8 @@
 // Internal diagnostic flag of the decode launcher (bit 0 of `flags`): sequences split across workers stay
 // unmerged, which leaves wrong rows for those.  Not part of the public ABI.
 #define NPD_DECODE_SKIP_MERGE 1
+// Bit 2: always take the streaming form, also where the small-batch form would be chosen (for tests of the former).
+#define NPD_DECODE_NO_SMALL 4
 
 // ---------------------------------------------------------------------------
 // Host-side error plumbing: every entry point returns a code and leaves a message.

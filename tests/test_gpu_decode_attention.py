@@ -68,6 +68,37 @@ def test_block_sizes(kernels, block_size, dtype):
     check(kernels, *_inputs(4, 4, 4, 128, [48, 32, 7, 131], block_size, dtype))
 
 
+@pytest.mark.parametrize("S,Hq,Hkv,D,B,lens", [
+    (8, 12, 2, 128, 16, [16, 100, 512, 333, 1, 47, 250, 64]),          # the shape of configuration 1
+    (16, 32, 8, 128, 16, [200] * 16),                                  # the reference's operating size; one sequence is emptied below
+    (1, 32, 8, 128, 16, [1024]),                                       # the longest context the small form takes
+    (2, 32, 8, 128, 16, [1025, 3]),                                    # one token more: both runs take the streaming form
+    (3, 40, 2, 128, 16, [5, 700, 33]),                                 # group 20: two virtual kv heads per head
+    (5, 8, 2, 256, 32, [31, 32, 33, 1000, 7]),
+    (4, 16, 16, 64, 8, [9, 130, 77, 1500]),
+])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_small_batch_form_and_streaming_form_agree(kernels, S, Hq, Hkv, D, B, lens, dtype):
+    """Small batches of short sequences take the form with one CTA per (sequence, kv head) and a merge in shared
+    memory; the private flag bit 2 forces the streaming form (equal-work split, merge through the workspace) on the
+    same inputs.  Both must match the oracle; their results differ at most by the order of the merges."""
+    q, kc, vc, bt, sl, scale = _inputs(S, Hq, Hkv, D, lens, B, dtype)
+    if S == 16:
+        sl[5] = 0                                                       # an empty sequence: a zero row
+    want = paged_oracle.paged_decode_attention(q, kc, vc, bt, sl, scale)
+    qd, kd, vd, btd, sld = q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV)
+    outs = []
+    for flags in (0, 4):
+        out = torch.full_like(qd, float("nan"))
+        kernels.paged_attention_forward(out, qd, kd, vd, btd, sld, scale, B, btd.size(1), _flags=flags)
+        torch.cuda.synchronize()
+        got = out.float().cpu()
+        assert torch.isfinite(got).all()
+        assert (got - want).abs().max().item() <= TOL[dtype]
+        outs.append(got)
+    assert (outs[0] - outs[1]).abs().max().item() <= TOL[dtype]
+
+
 @pytest.mark.parametrize("D", [64, 128, 256])
 def test_block_size_4(kernels, D):
     """Blocks of 4 tokens (the smallest size of the reference's kernel tests,
