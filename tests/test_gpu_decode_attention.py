@@ -252,3 +252,19 @@ def test_more_sequences_than_one_launch_takes(kernels):
                      b.ctx_lens.to(DEV), b.scale)
     empty = (b.ctx_lens == 0)
     assert int(empty.sum()) > 0 and torch.count_nonzero(got[empty.to(DEV)]) == 0
+
+
+def test_streaming_form_on_the_small_shapes():
+    """The golden cases, block sizes, lengths and head counts of this file are batches of short sequences, which
+    the launcher gives to the small-batch form; a child process with that form switched off (the library reads
+    NPD_DECODE_SMALL once) runs them through the streaming form as well."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    env = dict(os.environ, NPD_DECODE_SMALL="2")
+    res = subprocess.run([sys.executable, "-m", "pytest", str(Path(__file__).resolve()), "-q", "-x", "-p", "no:cacheprovider",
+                          "-k", "golden or block_size or seq_lens or head_dims or group or empty or poison"],
+                         env=env, capture_output=True, text=True, timeout=900, cwd=str(Path(__file__).resolve().parents[1]))
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert " passed" in res.stdout and "failed" not in res.stdout, res.stdout[-2000:]
