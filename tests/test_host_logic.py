@@ -89,3 +89,19 @@ def test_kv_transfer_exports_the_reference_module_names():
                                                                           "stream"]
     assert list(inspect.signature(PinnedKVBuffer.__init__).parameters)[1:] == ["num_layers", "num_block", "num_kv_heads",
                                                                                "block_size", "head_dim", "dtype"]
+
+
+def test_both_module_names_of_the_reference_resolve_to_this_implementation():
+    """``paged_kernels`` is what ``ModelRunner.paged_forward`` imports (nanoPD/engine/model_runner.py:94,270),
+    ``paged_attn`` what the older kernel tests import (nanoPD/paged_attention/tests/test_paged_attention.py:18);
+    the positional signature of the attention op is the reference's."""
+    import inspect
+
+    import paged_attn
+    import paged_kernels
+    assert paged_attn.paged_attention_forward is paged_kernels.paged_attention_forward
+    assert list(inspect.signature(paged_kernels.paged_attention_forward).parameters)[:9] == [
+        "out", "query", "key_cache", "value_cache", "block_tables", "seq_lens", "scale", "block_size",
+        "max_num_blocks_per_seq"]
+    assert list(inspect.signature(paged_kernels.paged_kv_store).parameters) == [
+        "k_cache", "v_cache", "k_src", "v_src", "block_tables", "positions"]
