@@ -271,9 +271,23 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 #define NPD_TRACE_FINE(role, tag, j) do { } while (0)
 #endif
 
+// One work item = a pair of 128-row query tiles of one chunk and one kv head.
+struct Item {
+    int c, h;
+    int start, qoff, ctx_end;
+    int tok0[2], tq_valid[2];
+    int nhalf[2];           // half-steps of 64 keys each query tile takes (keys [0, start + tok0 + tq_valid))
+    int ntiles[2];          // K/V tiles of 128 keys they lie in
+    int n_kv;
+};
+
 struct alignas(8) SmemCtrl {
     uint64_t sched_full[kSchedSlots];   // the producer warp has published the next work item
     int sched_item[kSchedSlots];
+    Item sched_desc[kSchedSlots];       // the published item, decoded once by the producer warp: the other roles'
+                                        // way from one item to the next stays a few loads (their decoding it
+                                        // themselves — divisions, indexed kernel parameters, cold code — took a
+                                        // softmax group ~2500 clocks per item)
     uint64_t q_full[2];          // [query tile]: its rows of the current work item have landed
     uint64_t q_empty[2];         // [query tile]: its MMA warp has issued the last score MMA of the item
     uint64_t k_full[kStagesK], v_full[kStagesV];     // the K / V tile of a ring stage has landed
@@ -291,15 +305,6 @@ struct alignas(8) SmemCtrl {
     int abort_flag;
 };
 
-// One work item = a pair of 128-row query tiles of one chunk and one kv head.
-struct Item {
-    int c, h;
-    int start, qoff, ctx_end;
-    int tok0[2], tq_valid[2];
-    int nhalf[2];           // half-steps of 64 keys each query tile takes (keys [0, start + tok0 + tq_valid))
-    int ntiles[2];          // K/V tiles of 128 keys they lie in
-    int n_kv;
-};
 
 // Work item `item` = kv head (item % Hkv) of entry (item / Hkv) of the host-sorted pair list.
 __device__ __forceinline__ Item decode_item(const PrefillParams &p, int item) {
@@ -450,16 +455,25 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     // the counter hands out the items behind the first gridDim.x
                     item = k == 0 ? static_cast<int>(blockIdx.x) : static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
                     if (item >= total_items) item = -1;
-                    *reinterpret_cast<volatile int *>(&ctrl->sched_item[k % kSchedSlots]) = item;
-                    mbar_arrive(smem_u32(&ctrl->sched_full[k % kSchedSlots]));
                 }
                 item = __shfl_sync(0xffffffffu, item, 0);
             } else {
                 item = next_item(k, ok);
                 if (!__all_sync(0xffffffffu, ok)) break;
             }
-            if (item < 0) break;
-            const Item it = decode_item(p, item);
+            Item it;
+            if (k_role) {
+                if (item >= 0) it = decode_item(p, item);
+                if (lane == 0) {
+                    if (item >= 0) ctrl->sched_desc[k % kSchedSlots] = it;
+                    *reinterpret_cast<volatile int *>(&ctrl->sched_item[k % kSchedSlots]) = item;
+                    mbar_arrive(smem_u32(&ctrl->sched_full[k % kSchedSlots]));
+                }
+                if (item < 0) break;
+            } else {
+                if (item < 0) break;
+                it = ctrl->sched_desc[k % kSchedSlots];
+            }
             // ---- query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch.
             //      Each tile has its own barriers, so a tile that finishes an item early moves on alone.  Tile B's
             //      rows are requested after the first K tile: tile A, half a step ahead, needs that one first.
@@ -596,7 +610,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             for (int k = 0; ok; ++k) {
                 const int item = next_item(k, ok);
                 if (!__all_sync(0xffffffffu, ok) || item < 0) break;
-                const Item it = decode_item(p, item);
+                const Item it = ctrl->sched_desc[k % kSchedSlots];
                 const int U = it.nhalf[x], my_tiles = it.ntiles[x];
                 // Half-step u of the item lies in K/V tile u / kHPT (half u % kHPT of it).  A score batch is followed by
                 // the release of its K tile when it was the last one to read it.
@@ -666,7 +680,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         for (int k = 0; ok; ++k) {
             const int item = next_item(k, ok);
             if (!ok || item < 0) break;
-            const Item it = decode_item(p, item);
+            const Item it = ctrl->sched_desc[k % kSchedSlots];
 #pragma unroll
             for (int x = 0; x < kQueryTiles; ++x) {
                 const int U = it.nhalf[x];
@@ -733,7 +747,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         for (int k = 0; ok; ++k) {
             const int item = next_item(k, ok);
             if (!ok || item < 0) break;
-            const Item it = decode_item(p, item);
+            const Item it = ctrl->sched_desc[k % kSchedSlots];
             const int U = it.nhalf[x];
             const int pos = it.start + it.tok0[x] + tq_idx;      // last visible key of this row
             float m_run = -INFINITY, l_run = 0.f;
