@@ -103,6 +103,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test of a phase (try_wait may suspend the thread for a while before it answers "not yet").
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after ~`limit_cycles` SM clocks and returns false, so a lost
 // completion can never hang the GPU.  Two seconds at 2 GHz by default.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,

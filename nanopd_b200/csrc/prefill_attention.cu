@@ -10,13 +10,14 @@
 // Persistent grid, one CTA of 512 threads per SM; items are handed out heaviest first through an atomic
 // counter.  Warp roles:
 //   warps 0-3 / 4-7  softmax of query tile A / B: thread i owns row i == TMEM lane i (no shuffles)
-//   warp  8          TMA producer of the query tiles and of the K tiles (a ring of 3 tiles in shared memory;
-//                    cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA operand layout); it also draws
-//                    the next work item and publishes it to the other roles
+//   warp  8          TMA producer of the K tiles (a ring of 3 tiles in shared memory; cp.async.bulk.tensor,
+//                    128-byte swizzle = the canonical UMMA operand layout); it also draws the next work item,
+//                    decodes it and publishes it to the other roles
 //   warp  11         TMA producer of the V tiles (a ring of 2 tiles).  Two producer warps, because the rate at
 //                    which ONE warp can issue tiled copies (about 100 clocks per 2 KiB box) is what bounded the
 //                    kernel when a single warp issued the 32 boxes of a 128-key step
-//   warps 9 / 10     issue the tcgen05.mma instructions of tile A / B (one elected lane)
+//   warps 9 / 10     issue the tcgen05.mma instructions of tile A / B (one elected lane) and request the tile's
+//                    query rows (the next item's as soon as this item's last score MMA has completed)
 //   warps 12-15      epilogue of both tiles: O / l -> out, while the softmax groups are already on the next item
 // TMEM (512 columns): S_A | S_B | O_A | O_B, 128 columns each.  A query tile walks its keys in HALF-STEPS of 64
 // keys; its 128 score columns are a ring of two 64-column buffers, so the scores of half-step c+1 are
@@ -48,7 +49,7 @@ constexpr int kSchedSlots = 4;     // work items the producer may publish ahead 
 constexpr int kRows = 128;         // UMMA M: rows of one query tile
 constexpr int kKeys = 128;         // keys per K/V tile in shared memory (64 at head_dim 256)
 constexpr int kHalfKeys = 64;      // keys per half-step (UMMA N of a score MMA, K extent of a PV MMA batch)
-constexpr int kThreads = 512;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA (Q, K), 9 MMA for A, 10 MMA for B, 11 TMA (V),
+constexpr int kThreads = 512;      // warps 0-3 softmax A, 4-7 softmax B, 8 TMA (K), 9 MMA + Q for A, 10 MMA + Q for B, 11 TMA (V),
                                    // 12-15 epilogue
 constexpr int kQHalfBytes = kRows * 128;            // one 64-element half of a 128-row query tile
 // head_dim kD = 64 * kHalves (64, 128 or 256): a tile is kHalves slabs, each 64 elements wide.  At head_dim 256 an
@@ -331,9 +332,9 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, int item) {
 
 // Persistent kernel: one CTA per SM.  Work items are handed out heaviest first through an atomic counter (the
 // producer warp fetches the next one and publishes it to the other roles through a small shared-memory ring), so
-// ragged chunks balance across the SMs.  All barrier phases are driven by running counters: the producer
-// already loads the next item's K/V tiles (and, once the last score MMA has been issued, its query tiles) while
-// the current item drains, and the epilogue of an item overlaps the first MMAs of the next one.
+// ragged chunks balance across the SMs.  All barrier phases are driven by running counters: the producers
+// already load the next item's K/V tiles (and the MMA warps, once an item's last score MMA has completed, request
+// its query tiles) while the current item drains, and the epilogue of an item overlaps the first MMAs of the next.
 // kBoxRows: rows of a K/V TMA box — 16, or the block size when blocks hold 8 or 4 tokens (a 16-key row group of a
 // tile is then two or four boxes; the 128-byte swizzle follows the shared-memory address, so the tile in shared
 // memory is the same).  A template parameter because the producer warps share their sub-partitions' issue slots
@@ -407,7 +408,7 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
     // group (two TMA warps, two MMA warps) gives up 56 per thread and the epilogue group 24 — 65 536 in all.
     if (warp == 8 || warp == 11) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-        // =========================== TMA producers: warp 8 (query tiles, K tiles), warp 11 (V tiles) ===========================
+        // =========================== TMA producers: warp 8 (K tiles), warp 11 (V tiles) ===========================
         // A K or V tile is 16 boxes of 2 KiB (16-key row groups x 64-element slabs; 32 boxes of 1 KiB with blocks
         // of 8 tokens, 64 of 512 B with blocks of 4), one box per lane, issued by ONE instruction of the warp per 32.  Issuing tiled copies costs the
         // issuing warp about 50 clocks per box plus several hundred per instruction, whatever the box holds, while
@@ -441,7 +442,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
         uint64_t *full = k_role ? ctrl->k_full : ctrl->v_full, *empty = k_role ? ctrl->k_empty : ctrl->v_empty;
         const int stages = k_role ? kStagesK : kStagesV;
         int stage = 0, round = 0;                               // ring position of the next tile
-        int q_loads[2] = {0, 0};                                // per query tile: items loaded so far (phases of q_empty)
         NPD_TRACE_DECL
         bool ok = true;
         for (int k = 0; ok; ++k) {
@@ -474,25 +474,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (item < 0) break;
                 it = ctrl->sched_desc[k % kSchedSlots];
             }
-            // ---- query tiles: box (64 elements, G heads, TQ tokens) per half -> rows (token, head) at 128 B pitch.
-            //      Each tile has its own barriers, so a tile that finishes an item early moves on alone.  Tile B's
-            //      rows are requested after the first K tile: tile A, half a step ahead, needs that one first.
-            auto load_q = [&](int x) {
-                if (it.tq_valid[x] <= 0) return true;
-                bool good = true;
-                if (q_loads[x] > 0) good = wait_or_abort(smem_u32(&ctrl->q_empty[x]), (q_loads[x] - 1) & 1, abort_flag, p.status);
-                if (!__all_sync(0xffffffffu, good)) return false;
-                ++q_loads[x];
-                if (lane == 0) {
-                    const uint32_t qbar = smem_u32(&ctrl->q_full[x]);
-                    mbar_expect_tx(qbar, static_cast<uint32_t>(kHalves * p.tq * p.group * 128));
-                    for (int h2 = 0; h2 < kHalves; ++h2)
-                        tma_load_3d(smem_u32(q_tiles + x * kQTileBytes + h2 * kQHalfBytes), &tm_q, qbar, h2 * 64,
-                                    it.h * p.group, it.qoff + it.tok0[x]);
-                }
-                return true;
-            };
-            if (k_role && !(ok = load_q(0))) break;
             const int32_t *table = p.block_tables + (long long)it.c * p.bt_row_stride;
             // A box lies in one block: 16 keys of a block of 16 or 32, or all keys of a block of 8 or 4.
             auto lookup = [&](int t, int i) {
@@ -542,7 +523,6 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     stage = 0;
                     ++round;
                 }
-                if (k_role && kQueryTiles > 1 && t == 0 && !(ok = load_q(1))) break;
             }
             ok = __all_sync(0xffffffffu, ok);
         }
@@ -605,6 +585,48 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
             int g = 0;         // key tiles seen so far (ring position of the item's first key tile)
             int c = 0;         // own half-steps so far: buffer c & 1, phase c >> 1 of that buffer's barriers
             int items_done = 0;   // items in which this query tile had work (phases of q_full and o_free)
+            // The query tile's rows are requested by the warp that reads them: box (64 elements, G heads, TQ tokens)
+            // per 64-element slab -> rows (token, head) at 128 B pitch.  The rows of the NEXT item can be requested
+            // once the last score MMA of this one has completed (q_empty), two half-steps before the item ends; this
+            // warp is the one that knows when that is, and it has time — while the producer warp, which used to do
+            // it, is held for ~1800 clocks by every K tile it issues and kept the request waiting behind them.
+            int q_requests = 0;   // items whose rows have been requested so far (phases of q_empty)
+            int q_item = -1;      // index (k) of the last item whose rows have been requested or need none
+            // 1 = requested, 0 = the previous rows are still being read (only when !blocking), -1 = abort
+            auto request_q = [&](const Item &qi, bool blocking) {
+                if (q_requests > 0) {
+                    uint64_t *bar = &ctrl->q_empty[x];
+                    const uint32_t par = (q_requests - 1) & 1;
+                    if (blocking) {
+                        if (!wait_all(bar, par)) return -1;
+                    } else if (!__all_sync(0xffffffffu, mbar_test_wait(smem_u32(bar), par))) {
+                        return 0;
+                    }
+                }
+                ++q_requests;
+                if (elect_one()) {
+                    const uint32_t qbar = smem_u32(&ctrl->q_full[x]);
+                    mbar_expect_tx(qbar, static_cast<uint32_t>(kHalves * p.tq * p.group * 128));
+                    for (int h2 = 0; h2 < kHalves; ++h2)
+                        tma_load_3d(smem_u32(q_tiles + x * kQTileBytes + h2 * kQHalfBytes), &tm_q, qbar, h2 * 64,
+                                    qi.h * p.group, qi.qoff + qi.tok0[x]);
+                }
+                __syncwarp();
+                return 1;
+            };
+            // The next item's rows, if that item has been published and the rows of this one are no longer read.
+            auto request_next_q = [&](int k) {
+                const int slot = (k + 1) % kSchedSlots;
+                if (!__all_sync(0xffffffffu, mbar_test_wait(smem_u32(&ctrl->sched_full[slot]), ((k + 1) / kSchedSlots) & 1)))
+                    return true;
+                if (*reinterpret_cast<volatile int *>(&ctrl->sched_item[slot]) < 0 || ctrl->sched_desc[slot].nhalf[x] <= 0) {
+                    q_item = k + 1;                                // nothing to request for it
+                    return true;
+                }
+                const int r = request_q(ctrl->sched_desc[slot], false);
+                if (r > 0) q_item = k + 1;
+                return r >= 0;
+            };
             NPD_TRACE_DECL
             bool ok = true;
             for (int k = 0; ok; ++k) {
@@ -612,6 +634,13 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                 if (!__all_sync(0xffffffffu, ok) || item < 0) break;
                 const Item it = ctrl->sched_desc[k % kSchedSlots];
                 const int U = it.nhalf[x], my_tiles = it.ntiles[x];
+                if (U > 0 && q_item < k) {
+                    if (request_q(it, true) < 0) {
+                        ok = false;
+                        break;
+                    }
+                    q_item = k;
+                }
                 // Half-step u of the item lies in K/V tile u / kHPT (half u % kHPT of it).  A score batch is followed by
                 // the release of its K tile when it was the last one to read it.
                 auto scores = [&](int u, int buf) {
@@ -647,6 +676,8 @@ paged_prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap 
                     if (h == kHPT - 1 || u == U - 1) commit(&ctrl->v_empty[stage]);
                     // S(u+2) goes into the buffer P(u) sits in; it executes after the PV MMAs above
                     if (u + 2 < U && !(ok = scores(u + 2, buf))) break;
+                    // the item's last score MMA has been issued: the next item's rows as soon as it has completed
+                    if (u + 3 >= U && q_item <= k && !(ok = request_next_q(k))) break;
                 }
                 for (int t = my_tiles; ok && t < it.n_kv; ++t) {
                     // a key tile only the other query tile needs: observe it so that ring phases stay in step
